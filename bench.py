@@ -1,0 +1,393 @@
+#!/usr/bin/env python
+"""Benchmark of the fused-kernel layer chain.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+One "step" is one decode step of the gpt-oss-20b chain (embedding gather, first norm,
+24 x [qkv bias + RoPE, residual add + RMSNorm, router top-4 + softmax, SwiGLU, expert
+combine + residual + next norm], greedy argmax over the vocabulary) for 4096 tokens per
+GPU in bf16-activation mode, with seeded synthetic tensors of the real shapes standing in
+for the GEMM and attention outputs.  Rank 0 prints one JSON line:
+
+  value       tokens/s over all GPUs, inputs resident in HBM, K CUDA-graph replays timed
+              with CUDA events on the launching stream, max over ranks
+  e2e         the same through the engine-step call (gptoss_chain_step): token ids and
+              positions copied from pinned host memory and the picked tokens copied back
+              inside the timed region every step (what the reference engine moves per
+              step, gpu_engine.hpp:781-798), wall clock, max over ranks
+  roofline    the dominant kernel: algorithmic bytes per launch / mean launch time from
+              CUDA event pairs around every launch, against the measured HBM copy peak
+  kernels     the same for every kernel kind
+  cpu_baseline  the reference's CPU code (OpenMP over tokens, all host threads) on a
+              bounded sample of the same workload; rank 0 at N = 1 only
+
+--impl reference times only that CPU implementation, on the same config.
+"""
+from __future__ import annotations
+
+import argparse
+import importlib
+import json
+import os
+import subprocess
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+PKG = "optimize_inference_gpt-oss_b200"
+
+FALLBACK_HBM_GBS = 6650.0  # an earlier measurement on this pool, used only without MEASURED_PEAKS.json
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", type=int, default=20, choices=[20, 120])
+    ap.add_argument("--tokens-per-gpu", type=int, default=4096)
+    ap.add_argument("--standin-sets", type=int, default=0, help="distinct per-layer input sets (0 = one per layer)")
+    ap.add_argument("--seed", type=int, default=1)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-seconds", type=float, default=8.0, help="minimum CPU time of the baseline sample")
+    ap.add_argument("--profile-steps", type=int, default=10)
+    return ap.parse_args()
+
+
+def hbm_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        return float(json.load(open(p))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback (no MEASURED_PEAKS.json)"
+
+
+def ncu_traffic(kind: str):
+    """DRAM bytes per launch from the committed ncu capture, if one has been taken."""
+    try:
+        return json.load(open(os.path.join(ROOT, "profiles", "ncu_traffic.json"))).get(kind)
+    except Exception:
+        return None
+
+
+# ---- clocks ------------------------------------------------------------------------------
+
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+        self.marks = []
+
+    def mark(self):
+        self.marks.append(time.time())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "note": "nvidia-smi not available"}
+        time.sleep(0.15)
+        self.proc.terminate()  # the exact process started above
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        sm, mx, pw, reasons = [], [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for ln in out.splitlines():
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 8:
+                continue
+            try:
+                sm.append(float(f[1])), mx.append(float(f[2])), pw.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, v in zip(names, f[4:8]):
+                if v == "Active":
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "note": "no samples"}
+        # under load = the upper half of the samples by power draw (the sampler also sees idle gaps)
+        order = np.argsort(pw)
+        busy = [sm[i] for i in order[len(order) // 2:]]
+        return {"sm_mhz": float(np.median(busy)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons),
+                "samples": len(sm), "power_w_max": float(max(pw))}
+
+
+def visible_gpu_index(local_rank: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_rank])
+        except Exception:
+            pass
+    return local_rank
+
+
+# ---- the CPU implementation (cpu_baseline leg and --impl reference) ----------------------
+
+class CpuChain:
+    """The reference's CPU functions looped over a sample of tokens, OpenMP over tokens.
+
+    rmsnorm, compute_cos_sin + apply_rotary_emb, topk + softmax and sample_argmax are the
+    reference's own compiled functions when oracle/_ref/libgptoss_ref.so is present; the
+    loops that exist only inline in forward() (embedding copy, bias add, SwiGLU, expert
+    combine, residual adds) come from the restated oracle, as they do when it is absent."""
+
+    def __init__(self, pkg, model: int, tokens: int, seed: int, sets: int = 2):
+        import oracle
+        if not os.path.exists(oracle.ORACLE_SO):
+            oracle.build(ref=None)
+        self.orc = oracle.Oracle()
+        self.ref = oracle.Reference() if oracle.have_reference() else None
+        self.kind = "reference" if self.ref is not None else "port"
+        self.fn = self.ref if self.ref is not None else self.orc
+        self.threads = self.fn.max_threads()
+        c = pkg.chain_config(model, pkg.BF16, 4096)
+        self.c, self.T, self.sets = c, tokens, sets
+        T, K, H = tokens, c.top_k, c.hidden
+
+        def normal(shape, sid, mean=0.0, sd=1.0):  # bf16 values widened exactly to fp32
+            bits = pkg.synth_normal(int(np.prod(shape)), pkg.BF16, seed + 977, sid, mean, sd)
+            return pkg.from_bf16_bits(bits).reshape(shape)
+
+        self.vocab_rows = min(c.vocab, 8192)  # the gather only touches the sampled rows
+        self.emb = normal((self.vocab_rows, H), 0, 0.0, 0.02)
+        self.tokens = pkg.synth_uniform_int(T, seed, 1, 0, self.vocab_rows)
+        self.pos = pkg.synth_uniform_int(T, seed, 2, 0, 4096)
+        self.gain = (1 + 0.1 * normal((3, H), 3)).astype(np.float32)
+        self.bias = normal((c.qkv_dim,), 4, 0.0, 0.02)
+        self.proj = [normal((T, H), 10 + s) for s in range(sets)]
+        self.qkv = [normal((T, c.qkv_dim), 20 + s) for s in range(sets)]
+        self.router = [normal((T, c.n_experts), 30 + s) for s in range(sets)]
+        self.mlp1 = [normal((K * T, 2 * c.inter), 40 + s, 0.0, 2.0) for s in range(sets)]
+        self.expert = [normal((K * T, H), 50 + s) for s in range(sets)]
+        self.logits = normal((T, c.vocab), 60, 0.0, 3.0)
+        self.ident = np.arange(T * K, dtype=np.int32).reshape(T, K)
+
+    def step(self):
+        c, fn, orc, th = self.c, self.fn, self.orc, 0
+        x = orc.embed_rows(self.emb, self.tokens, threads=th)
+        fn.add_rmsnorm_rows(x, None, self.gain[0], threads=th)
+        for l in range(c.n_layers):
+            s = l % self.sets
+            fn.bias_rope_rows(self.qkv[s], self.bias, self.pos, c.n_q_heads, c.n_kv_heads, c.head_dim, threads=th)
+            x, _ = fn.add_rmsnorm_rows(x, self.proj[s], self.gain[1], threads=th)
+            w, e = fn.router_rows(self.router[s], c.top_k, threads=th)
+            orc.swiglu_rows(self.mlp1[s], c.swiglu_limit, threads=th)
+            x = orc.combine_rows(x, self.expert[s], self.ident, w, e, c.n_experts, threads=th)
+            fn.add_rmsnorm_rows(x, None, self.gain[2], threads=th)
+        return fn.argmax_rows(self.logits, threads=th)
+
+    def describe(self):
+        return (f"{self.T} tokens through the whole {self.c.n_layers}-layer chain per pass, fp32 on the host, "
+                f"OpenMP over tokens; rmsnorm/rope/top-k/softmax/argmax "
+                f"{'are the reference functions compiled from run.cpp (-O3 -fopenmp)' if self.ref else 'from the restated oracle'}"
+                f", SwiGLU/combine/bias/residual loops (inline in forward()) from the restated oracle")
+
+
+def run_cpu(pkg, args, min_seconds: float, steps: int | None, warmup: int):
+    """Times the CPU chain.  steps=None: repeat passes until min_seconds have gone by."""
+    threads = os.cpu_count() or 1
+    tokens = int(min(args.tokens_per_gpu, max(128, 8 * threads)))
+    cpu = CpuChain(pkg, args.model, tokens, args.seed)
+    for _ in range(max(1, warmup)):
+        cpu.step()
+    t0 = time.perf_counter()
+    n = 0
+    while True:
+        cpu.step()
+        n += 1
+        el = time.perf_counter() - t0
+        if (steps is not None and n >= steps) or (steps is None and el >= min_seconds):
+            break
+    return cpu, n, el
+
+
+def reference_arm(pkg, args, rank: int):
+    if rank != 0:
+        return
+    cpu, n, el = run_cpu(pkg, args, 0.0, args.steps, args.warmup)
+    value = cpu.T * n / el
+    line = {
+        "impl": "reference", "metric": "layer_chain_tokens_per_s", "value": value, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": n, "warmup": args.warmup, "ms_per_step": 1e3 * el / n,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args, cpu.c),
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cpu.threads, "kind": cpu.kind,
+                         "sample": cpu.describe()},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, c):
+    return {
+        "workload": f"gpt-oss-{args.model}b decode chain: {c.n_layers} layers, {c.n_experts} experts top-{c.top_k}, "
+                    f"hidden {c.hidden}, bf16 activations, fp32 residual, {args.tokens_per_gpu} tokens per GPU, "
+                    f"positions uniform in [0,4096)",
+        "tokens_per_gpu": args.tokens_per_gpu, "layers": c.n_layers, "experts": c.n_experts,
+        "parallelism": f"dp{args.gpus} (token shards, no collective)",
+        "l2": "inputs larger than L2: every layer reads its own seeded tensors, several GB per step",
+    }
+
+
+# ---- our arm -------------------------------------------------------------------------------
+
+def main():
+    args = parse_args()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.gpus > 1 and world == 1:
+        # launched by hand without torchrun: start one process per GPU
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+               "--master-addr", "127.0.0.1", "--master-port", "29533", os.path.abspath(__file__), *sys.argv[1:]]
+        sys.exit(subprocess.call(cmd))
+
+    pkg = importlib.import_module(PKG)
+    pkg.load()
+
+    if args.impl == "reference":
+        reference_arm(pkg, args, rank)
+        return
+
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    assert pkg.device_count() > local_rank, "no CUDA device for this rank"
+    pkg.set_device(local_rank)
+    sharding = importlib.import_module(PKG + ".sharding")
+
+    def barrier():
+        pkg.synchronize()
+        if dist is not None:
+            dist.barrier()
+        pkg.synchronize()
+
+    T = args.tokens_per_gpu
+    c = pkg.chain_config(args.model, pkg.BF16, 4096)
+    sets = args.standin_sets or c.n_layers
+    t_setup = time.perf_counter()
+    chain = pkg.Chain(c, T, sets)
+    chain.fill_synthetic(T, seed=args.seed + 7919 * rank)
+    # this rank's shard of the batch: its own token ids and positions
+    tok = pkg.PinnedArray(T, np.int32)
+    pos = pkg.PinnedArray(T, np.int32)
+    nxt = pkg.PinnedArray(T, np.int32)
+    tok.array[:] = pkg.synth_uniform_int(T, args.seed, 100 + rank, 0, c.vocab)
+    pos.array[:] = pkg.synth_uniform_int(T, args.seed, 200 + rank, 0, 4096)
+    chain.upload(pkg.BUF_TOKENS, 0, tok.array)
+    chain.upload(pkg.BUF_POS, 0, pos.array)
+    setup_s = time.perf_counter() - t_setup
+
+    lib = pkg.load()
+    import ctypes as C
+    ev = [C.c_void_p(), C.c_void_p()]
+    for e in ev:
+        pkg.check(lib.gptoss_event_create(C.byref(e)))
+    stream = chain.stream
+
+    sampler = ClockSampler(visible_gpu_index(local_rank)) if rank == 0 else None
+
+    # ---- value: K graph replays, inputs resident, CUDA events on the launching stream
+    for _ in range(max(3, args.warmup)):
+        chain.enqueue(T, True)
+    barrier()
+    pkg.check(lib.gptoss_event_record(ev[0], stream))
+    for _ in range(args.steps):
+        chain.enqueue(T, True)
+    pkg.check(lib.gptoss_event_record(ev[1], stream))
+    barrier()
+    ms = C.c_float()
+    pkg.check(lib.gptoss_event_elapsed_ms(ev[0], ev[1], C.byref(ms)))
+    ms_total = sharding.max_over_ranks(ms.value, dist)
+    ms_per_step = ms_total / args.steps
+    value = world * T * args.steps / (ms_total * 1e-3)
+
+    # ---- e2e: the engine-step call with host buffers, wall clock
+    for _ in range(3):
+        chain.step(tok.array, pos.array, nxt.array)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        chain.step(tok.array, pos.array, nxt.array)
+    e2e_s = time.perf_counter() - t0
+    barrier()
+    e2e_s = sharding.max_over_ranks(e2e_s, dist)
+    e2e_value = world * T * args.steps / e2e_s
+    clocks = sampler.stop() if sampler else None
+
+    # ---- per-kernel device times: an event pair around every launch, same stream
+    prof = chain.profile(T, max(1, min(args.profile_steps, args.steps)))
+    peak, peak_src = hbm_peak()
+    kernels = {}
+    chain_bytes = 0
+    for kind, (kms, n) in prof.items():
+        if n == 0:
+            continue
+        per_step = n // max(1, min(args.profile_steps, args.steps))
+        b = chain.kernel_bytes(kind, T)
+        us = 1e3 * kms / n
+        gbs = b / (us * 1e-6) / 1e9
+        kernels[kind] = {"launches_per_step": per_step, "us_per_launch": round(us, 3), "bytes_per_launch": b,
+                         "achieved_gbs": round(gbs, 1), "frac": round(gbs / peak, 4),
+                         "share_of_step": None}
+        chain_bytes += b * per_step
+    tot = sum(k["us_per_launch"] * k["launches_per_step"] for k in kernels.values())
+    for k in kernels.values():
+        k["share_of_step"] = round(k["us_per_launch"] * k["launches_per_step"] / tot, 4)
+    top = max(kernels, key=lambda k: kernels[k]["share_of_step"])
+    roofline = {"kernel": top, "bound": "hbm", "achieved": kernels[top]["achieved_gbs"], "peak": peak,
+                "unit": "GB/s", "frac": kernels[top]["frac"], "traffic": ncu_traffic(top),
+                "peak_source": peak_src,
+                "chain": {"bytes_per_step": chain_bytes,
+                          "achieved_gbs": round(chain_bytes / (ms_per_step * 1e-3) / 1e9, 1),
+                          "frac": round(chain_bytes / (ms_per_step * 1e-3) / 1e9 / peak, 4)}}
+
+    line = {
+        "metric": "layer_chain_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded, host-generated)",
+        "config": workload_config(args, c),
+        "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": 8 * T, "d2h_bytes_per_step": 4 * T,
+                "ms_per_step": 1e3 * e2e_s / args.steps,
+                "what": "gptoss_chain_step: token ids + positions from pinned host memory in, picked tokens out, "
+                        "stream synchronised every step; activations standing in for GEMM outputs stay on the device"},
+        "gpu_launches": chain.launches_per_step(T) * args.steps,
+        "launches_per_step": chain.launches_per_step(T),
+        "roofline": roofline, "kernels": kernels, "clocks": clocks,
+        "device": pkg.device_name(local_rank), "device_bytes": chain.device_bytes, "setup_s": round(setup_s, 1),
+    }
+
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu, n, el = run_cpu(pkg, args, args.cpu_seconds, None, 1)
+        line["cpu_baseline"] = {"value": cpu.T * n / el, "unit": "tokens/s", "cores": cpu.threads, "kind": cpu.kind,
+                                "sample": f"{n} passes in {el:.1f} s; " + cpu.describe()}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    chain.close()
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

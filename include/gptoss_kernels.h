@@ -1,0 +1,212 @@
+/*
+ * gptoss_kernels.h -- C ABI of the fused per-layer kernels of the gpt-oss engine,
+ * built for NVIDIA B200 (sm_100a).
+ *
+ * One entry point per launch site of the reference engine's forward loop
+ * (getp-csrc/engine/gpu_engine.hpp:461-621 of n30nd/Optimize_Inference_GPT-OSS).
+ * Each comment names the reference launcher or kernel the entry point stands in
+ * for.  Conventions, the same as the reference's launchers:
+ *
+ *   - every pointer is a DEVICE pointer owned by the caller; nothing here
+ *     allocates, frees or synchronises; work is queued on `stream` and returns;
+ *   - tensors are row-major and contiguous unless a row stride is an argument;
+ *   - the residual stream `x` is fp32 and is updated in place;
+ *   - `T` is the number of token rows (the reference's `B`); T == 0 is a no-op.
+ *
+ * Unlike the reference (which aborts the process in HIP_CHECK,
+ * gpu_engine.hpp:41-49) every call returns a status: GPTOSS_OK, or an error for
+ * bad arguments / unsupported shapes (checked before anything is queued) or a
+ * failed launch.  There is no CPU fallback: without a CUDA device every compute
+ * entry point returns GPTOSS_ERR_CUDA.
+ *
+ * Arithmetic modes (flags):
+ *   GPTOSS_EXACT  follow the CPU program's rounding sequence (run.cpp): double
+ *                 sum of squares, glibc's expf algorithm, products and sums
+ *                 rounded separately, experts combined in increasing expert
+ *                 number.  Meant for fp32 tensors ("fp32 mode").
+ *   (default)     the reference's fast path: fp32 math with fused multiply-adds,
+ *                 tree sums, fast exponential; bf16 where a result feeds a matrix
+ *                 multiply ("bf16-activation mode").
+ *   GPTOSS_FMA    with GPTOSS_EXACT: contract x1*c - x2*s, x2*c + x1*s and
+ *                 agg += z*w into fused multiply-adds, as a CPU build with
+ *                 -march=native and the reference's *_exact HIP kernels do.
+ */
+#ifndef GPTOSS_KERNELS_H
+#define GPTOSS_KERNELS_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define GPTOSS_API __attribute__((visibility("default")))
+#else
+#define GPTOSS_API
+#endif
+
+/* Opaque CUDA stream handle (a cudaStream_t); NULL is the default stream. */
+typedef void *gptoss_stream_t;
+
+typedef enum {
+  GPTOSS_F32 = 0,  /* IEEE binary32 */
+  GPTOSS_BF16 = 1, /* bfloat16, stored as the upper 16 bits of a binary32 */
+} gptoss_dtype_t;
+
+enum {
+  GPTOSS_OK = 0,
+  GPTOSS_ERR_BAD_ARG = 1,     /* null pointer, negative size, misaligned base */
+  GPTOSS_ERR_UNSUPPORTED = 2, /* a shape or dtype the kernels do not cover */
+  GPTOSS_ERR_CUDA = 3,        /* launch failed or no usable device; see gptoss_last_cuda_error */
+};
+
+enum {
+  GPTOSS_EXACT = 1u,
+  GPTOSS_FMA = 2u,
+};
+
+#define GPTOSS_MAX_TOPK 8      /* k of the router and of the combine */
+#define GPTOSS_MAX_EXPERTS 256 /* E of the router */
+#define GPTOSS_RMS_EPS 1e-5f   /* the reference hard-codes this (run.cpp:327) */
+
+/* Library version, "major.minor.patch". */
+GPTOSS_API const char *gptoss_version(void);
+/* Text for a status code. */
+GPTOSS_API const char *gptoss_status_string(int status);
+/* The cudaError_t (as int) of the last failed CUDA call made by this thread in
+ * this library, 0 if none. */
+GPTOSS_API int gptoss_last_cuda_error(void);
+
+/*
+ * Token-embedding gather: x[t,:] = table[ids[t],:].
+ * Replaces embed_kernel (kernels/misc.hpp:16-23; launch gpu_engine.hpp:461-464)
+ * and the CPU's memcpy (run.cpp:544-545).  A bf16 table may be widened to fp32
+ * (bits << 16) or copied as bf16; an fp32 table is copied as fp32.  Rows are
+ * copied bit for bit.  An id outside [0, V) yields a row of zeros.
+ */
+GPTOSS_API int gptoss_embed(gptoss_stream_t stream, int T, const void *table,
+                            gptoss_dtype_t table_dtype, int V, const int *ids, void *x,
+                            gptoss_dtype_t x_dtype, int H);
+
+/*
+ * Residual add fused with RMSNorm (eps 1e-5):
+ *     if (y) x[t,:] += y[t,:];   out[t,:] = weight * x[t,:] / sqrt(mean(x^2) + eps)
+ * With y: replaces add_rmsnorm_bf16 (kernels/fast_misc.hpp:237-267; launch
+ * gpu_engine.hpp:503-504) and, with GPTOSS_EXACT, add_inplace_kernel +
+ * rmsnorm_exact (kernels/misc.hpp:88-93, 28-50; launches gpu_engine.hpp:507, 519)
+ * = run.cpp:653-658.  Without y (NULL): replaces rmsnorm_bf16_kernel
+ * (fast_misc.hpp:12-31; launch gpu_engine.hpp:491-492) / rmsnorm_exact
+ * (gpu_engine.hpp:479, 615) = rmsnorm() run.cpp:320-333; x is then only read and
+ * out may alias x when out_dtype is fp32 (the final norm, run.cpp:751).
+ */
+GPTOSS_API int gptoss_add_rmsnorm(gptoss_stream_t stream, int T, float *x, const void *y,
+                                  gptoss_dtype_t y_dtype, const float *weight, void *out,
+                                  gptoss_dtype_t out_dtype, int H, unsigned flags);
+
+/*
+ * QKV bias add fused with YaRN RoPE:
+ *     row = qkv_in[t,:] (+ bias);  the n_q_heads query heads and the n_kv_heads
+ *     key heads are rotated (pairs (i, i + head_dim/2)) by the angles of row
+ *     pos[t] of the cos/sin tables; the value heads only get the bias.
+ * Replaces the bias add of the QKV GEMM epilogue (kernels/fast_gemm.hpp:295-300,
+ * 338-354; run.cpp:568-570) plus rope_exact (kernels/misc.hpp:55-70; launch
+ * gpu_engine.hpp:481) and the rotation of rope_kv_bf16 / rope_pair
+ * (kernels/fast_misc.hpp:48-127, kernels/fast_common.hpp:25-28; launch
+ * gpu_engine.hpp:495-496) = apply_rotary_emb run.cpp:506-526, 591-592.
+ * cos_tab / sin_tab: [n_pos, head_dim/2] fp32, built on the host (the engine
+ * does so with compute_cos_sin, gpu_engine.hpp:388-396; see
+ * gptoss_build_rope_tables).  pos: one position per row; NULL means every row
+ * is at position pos_scalar (the engine's one position per step,
+ * gpu_engine.hpp:476).  Positions are clamped into [0, n_pos).  bias may be
+ * NULL.  qkv_out may be qkv_in (same dtype and stride) for in-place use.  Row
+ * strides are in elements.  head_dim must be a multiple of 16.
+ */
+GPTOSS_API int gptoss_qkv_bias_rope(gptoss_stream_t stream, int T, const void *qkv_in,
+                                    gptoss_dtype_t in_dtype, long in_row_stride,
+                                    const float *bias, const int *pos, int pos_scalar,
+                                    const float *cos_tab, const float *sin_tab, int n_pos,
+                                    int n_q_heads, int n_kv_heads, int head_dim, void *qkv_out,
+                                    gptoss_dtype_t out_dtype, long out_row_stride,
+                                    unsigned flags);
+
+/*
+ * Router: the k largest of each row's E logits in descending order (equal
+ * values: lower expert first; -0 equals +0), then softmax over those k.
+ * Replaces router_topk_wave_kernel / router_topk_exact (kernels/moe.hpp:64-136,
+ * 15-52; launch gpu_engine.hpp:524-529) = topk() + softmax() run.cpp:387-420,
+ * 335-353, 671-674.  The softmax always follows the CPU's rounding sequence
+ * (the reference uses one kernel for both of its paths).  done (may be NULL):
+ * rows with done[t] != 0 get expert -1 and weight 0 for all k choices.
+ * slot_of (may be NULL): topk_e receives slot_of[e] instead of e.
+ * E <= GPTOSS_MAX_EXPERTS, 1 <= k <= min(E, GPTOSS_MAX_TOPK).  A NaN logit is
+ * never selected ahead of a number.
+ */
+GPTOSS_API int gptoss_router_topk(gptoss_stream_t stream, int T, const void *logits,
+                                  gptoss_dtype_t logits_dtype, int E, int k, float *topk_w,
+                                  int *topk_e, const int *done, const int *slot_of);
+
+/*
+ * Clamped SwiGLU on R rows of interleaved gate/up values:
+ *     g = min(Y[r,2j], limit); u = clamp(Y[r,2j+1], -limit, limit);
+ *     G[r,j] = g * sigmoid(1.702 g) * (u + 1)
+ * Replaces swiglu_bf16_kernel (kernels/fast_misc.hpp:130-141; launch
+ * gpu_engine.hpp:571-572), the same arithmetic in the mlp1 GEMM epilogue
+ * (kernels/fast_moe_gemm.hpp:546-571) and, with GPTOSS_EXACT, swiglu_exact
+ * (kernels/moe.hpp:186-205; launch gpu_engine.hpp:554) = run.cpp:701-724.
+ */
+GPTOSS_API int gptoss_swiglu(gptoss_stream_t stream, const void *Y, gptoss_dtype_t y_dtype,
+                             void *G, gptoss_dtype_t g_dtype, size_t R, int I, float limit,
+                             unsigned flags);
+
+/*
+ * Weighted expert combine fused with the residual, optionally with the next
+ * RMSNorm:
+ *     x[t,:] += sum_j topk_w[t,j] * Z[own_row[t*k+j],:];
+ *     if (norm_w) out[t,:] = RMSNorm(x[t,:]) * norm_w
+ * Replaces moe_combine_rmsnorm (kernels/moe_ep.hpp:479-515, 571-580; launch
+ * gpu_engine.hpp:596-603), moe_combine_kernel (kernels/fast_misc.hpp:154-166)
+ * and, with GPTOSS_EXACT, moe_combine_exact / moe_combine_ep_kernel<true>
+ * (kernels/moe.hpp:210-236, kernels/moe_ep.hpp:286-332; launch
+ * gpu_engine.hpp:590-593) = run.cpp:677-748.  Default mode adds the choices in
+ * choice order j = 0..k-1 with fused multiply-adds; GPTOSS_EXACT adds them in
+ * increasing expert number (phys_of, may be NULL, maps renumbered experts back
+ * for that order).  A row whose first expert is negative is a finished request:
+ * x is left as it is, but the row still gets its norm.  own_row NULL means row
+ * t*k+j.  norm_w NULL skips the norm (out is then ignored).
+ */
+GPTOSS_API int gptoss_moe_combine(gptoss_stream_t stream, int T, float *x, const void *Z,
+                                  gptoss_dtype_t z_dtype, const int *own_row,
+                                  const float *topk_w, const int *topk_e, int k, int H,
+                                  const int *phys_of, const float *norm_w, void *out,
+                                  gptoss_dtype_t out_dtype, unsigned flags);
+
+/*
+ * Greedy pick: out[t] = index of the largest of logits[t, 0..V), the lowest
+ * index on ties (-0 equals +0), exactly as sample_argmax (run.cpp:778-789)
+ * decides: a NaN is never picked over a number, and a row whose element 0 is
+ * NaN, or that holds no number above -inf, gives 0.
+ * Replaces argmax_kernel (kernels/misc.hpp:97-129; launch gpu_engine.hpp:617)
+ * and the key merge of gemm_bf16_argmax (kernels/fast_gemm.hpp:94-104, 706-714,
+ * 901-926; launch gpu_engine.hpp:619).  Each row may be scanned by several
+ * thread blocks that merge through 64-bit keys (order-preserving value bits,
+ * then ~index) with atomicMax: keys is scratch of T 64-bit words that must be
+ * zero on entry and is left zero, like the reference's `keys` argument.  keys
+ * may be NULL: each row is then scanned by a single block.  row_stride in
+ * elements.
+ */
+GPTOSS_API int gptoss_argmax(gptoss_stream_t stream, int T, const void *logits,
+                             gptoss_dtype_t logits_dtype, long V, long row_stride,
+                             unsigned long long *keys, int *out);
+
+/* How many slices (thread blocks) gptoss_argmax cuts each row into for T rows
+ * of V logits on the current device; has_keys = 0 describes a call with
+ * keys == NULL (always 1).  More than one slice means a second, tiny launch
+ * decodes the merged keys. */
+GPTOSS_API int gptoss_argmax_slices(int T, long V, gptoss_dtype_t logits_dtype, int has_keys);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GPTOSS_KERNELS_H */

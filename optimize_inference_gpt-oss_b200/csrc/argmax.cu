@@ -1,0 +1,222 @@
+// Greedy vocabulary argmax (gptoss_argmax).
+//
+// The one op on the path with real volume: V = 201,088 logits per row.  Each
+// row is cut into `splits` contiguous slices, one thread block per slice, so a
+// small batch still fills every SM.  A thread streams 128-bit pieces of its
+// slice (kUnroll of them in flight), keeps only a running maximum and its
+// index, and touches the index bookkeeping in a rarely taken branch: for each
+// 16-byte piece it first reduces the 8 (bf16) or 4 (fp32) values to their
+// maximum with packed max instructions and compares once.  Blocks merge through
+// a 64-bit key, order-preserving value bits above the complemented index, so
+// the larger value wins and, among equal values, the lower index; slices merge
+// with atomicMax on one key per row, and a second tiny kernel turns keys into
+// indices and zeroes them again.
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+
+namespace gptoss {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kUnroll = 4;
+
+// Larger value => larger key; equal values => lower index wins; -0 == +0.
+// idx < 2^31.  Never 0 for a number, so 0 can mean "nothing seen".
+__device__ __forceinline__ unsigned long long pick_key(float v, unsigned idx) {
+  uint32_t u = v == 0.0f ? 0u : __float_as_uint(v);
+  u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+  return ((unsigned long long)u << 32) | (unsigned)~idx;
+}
+
+// Maximum of the values of one 16-byte piece; NaNs are ignored unless every
+// value is NaN.
+template <typename LT> __device__ __forceinline__ float piece_max(uint4 q) {
+  if constexpr (sizeof(LT) == 2) {
+    __nv_bfloat162 a = *reinterpret_cast<__nv_bfloat162 *>(&q.x);
+    __nv_bfloat162 b = *reinterpret_cast<__nv_bfloat162 *>(&q.y);
+    __nv_bfloat162 c = *reinterpret_cast<__nv_bfloat162 *>(&q.z);
+    __nv_bfloat162 d = *reinterpret_cast<__nv_bfloat162 *>(&q.w);
+    a = __hmax2(__hmax2(a, b), __hmax2(c, d));
+    const uint32_t m = *reinterpret_cast<uint32_t *>(&a);
+    return fmaxf(bf16_lo(m), bf16_hi(m));
+  } else {
+    return fmaxf(fmaxf(__uint_as_float(q.x), __uint_as_float(q.y)),
+                 fmaxf(__uint_as_float(q.z), __uint_as_float(q.w)));
+  }
+}
+
+// Position (0-based, within the piece) of the first value equal to m.
+template <typename LT> __device__ __forceinline__ int piece_first(uint4 q, float m) {
+  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+  if constexpr (sizeof(LT) == 2) {
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      if (bf16_lo(w[i]) == m)
+        return 2 * i;
+      if (bf16_hi(w[i]) == m)
+        return 2 * i + 1;
+    }
+    return 0;
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+      if (__uint_as_float(w[i]) == m)
+        return i;
+    return 0;
+  }
+}
+
+// Block-wide maximum key; valid in thread 0.
+__device__ __forceinline__ unsigned long long block_max_key(unsigned long long key,
+                                                            unsigned long long *scratch) {
+  key = warp_max_u64(key);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0)
+    scratch[warp] = key;
+  __syncthreads();
+  unsigned long long best = 0;
+  if (warp == 0) {
+    best = lane < (int)(blockDim.x >> 5) ? scratch[lane] : 0ull;
+    best = warp_max_u64(best);
+  }
+  return best;
+}
+
+// The CPU's answer for a row given the merged key (run.cpp:778-789): element 0
+// being NaN keeps index 0; no number above -inf also leaves index 0.
+template <typename LT>
+__device__ __forceinline__ int decode_pick(unsigned long long key, const LT *row) {
+  const float first = load1(row);
+  if (first != first || key == 0ull)
+    return 0;
+  return (int)~(unsigned)(key & 0xffffffffull);
+}
+
+// grid = (splits, T).  Vector path: V_vec elements per row, a multiple of the
+// piece width, start 16-byte aligned; the scalar tail [V_vec, V) is scanned by
+// the block of the last slice.
+template <typename LT>
+__global__ void __launch_bounds__(kThreads)
+    argmax_slices(const LT *__restrict__ logits, long V, long row_stride, long pieces_per_row,
+                  long pieces_per_slice, unsigned long long *keys, int *__restrict__ out) {
+  constexpr int kPer = 16 / sizeof(LT); // values per 16-byte piece
+  __shared__ unsigned long long scratch[kThreads / 32];
+  const int row = blockIdx.y;
+  const LT *r = logits + (size_t)row * row_stride;
+  const long p0 = (long)blockIdx.x * pieces_per_slice;
+  long p1 = p0 + pieces_per_slice;
+  if (p1 > pieces_per_row)
+    p1 = pieces_per_row;
+
+  float best = __int_as_float(0xff800000); // -inf: only values above it are recorded
+  long best_idx = -1;
+  for (long p = p0 + threadIdx.x; p < p1; p += (long)kThreads * kUnroll) {
+    uint4 q[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; u++) {
+      const long pp = p + (long)u * kThreads;
+      // past the slice: re-read its first piece; the strict '>' below makes a repeat harmless
+      q[u] = ld_stream(r + (pp < p1 ? pp : p0) * kPer);
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; u++) {
+      const float m = piece_max<LT>(q[u]);
+      if (m > best) { // rare after the first few pieces
+        const long pp = p + (long)u * kThreads;
+        best = m;
+        best_idx = (pp < p1 ? pp : p0) * kPer + piece_first<LT>(q[u], m);
+      }
+    }
+  }
+  // scalar tail of the row, by the last slice's block
+  if (blockIdx.x == gridDim.x - 1)
+    for (long i = pieces_per_row * kPer + threadIdx.x; i < V; i += kThreads) {
+      const float v = load1(r + i);
+      if (v > best) {
+        best = v;
+        best_idx = i;
+      }
+    }
+  unsigned long long key = best_idx >= 0 ? pick_key(best, (unsigned)best_idx) : 0ull;
+  key = block_max_key(key, scratch);
+  if (threadIdx.x == 0) {
+    if (keys)
+      atomicMax(keys + row, key);
+    else
+      out[row] = decode_pick(key, r);
+  }
+}
+
+template <typename LT>
+__global__ void argmax_finish(unsigned long long *keys, const LT *__restrict__ logits,
+                              long row_stride, int T, int *__restrict__ out) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= T)
+    return;
+  out[row] = decode_pick(keys[row], logits + (size_t)row * row_stride);
+  keys[row] = 0ull;
+}
+
+// Slices per row: enough blocks to fill the machine several times over, each
+// slice at least 2048 pieces (32 KB), at most 64 slices.
+int plan_slices(int T, long pieces, bool has_keys) {
+  if (!has_keys || T <= 0)
+    return 1;
+  long want = ((long)sm_count() * 8 + T - 1) / T;
+  const long by_size = pieces / 2048 > 0 ? pieces / 2048 : 1;
+  if (want > by_size)
+    want = by_size;
+  if (want > 64)
+    want = 64;
+  return want < 1 ? 1 : (int)want;
+}
+
+template <typename LT>
+int launch(cudaStream_t s, int T, const void *logits, long V, long row_stride,
+           unsigned long long *keys, int *out) {
+  const LT *lp = static_cast<const LT *>(logits);
+  constexpr long kPer = 16 / sizeof(LT);
+  const bool vec = aligned16(logits) && (row_stride * sizeof(LT)) % 16 == 0;
+  const long pieces = vec ? V / kPer : 0;
+  const int splits = plan_slices(T, pieces, keys != nullptr);
+  if (T > 65535)
+    return GPTOSS_ERR_UNSUPPORTED;
+  long per_slice = (pieces + splits - 1) / splits;
+  if (per_slice < 1)
+    per_slice = 1;
+  unsigned long long *merge = splits > 1 ? keys : nullptr;
+  argmax_slices<LT><<<dim3(splits, T), kThreads, 0, s>>>(lp, V, row_stride, pieces, per_slice, merge,
+                                                        out);
+  int st = launch_status();
+  if (st != GPTOSS_OK || !merge)
+    return st;
+  argmax_finish<LT><<<(T + 255) / 256, 256, 0, s>>>(keys, lp, row_stride, T, out);
+  return launch_status();
+}
+
+} // namespace
+} // namespace gptoss
+
+extern "C" int gptoss_argmax(gptoss_stream_t stream, int T, const void *logits,
+                             gptoss_dtype_t logits_dtype, long V, long row_stride,
+                             unsigned long long *keys, int *out) {
+  using namespace gptoss;
+  if (T < 0 || V <= 0 || V > 0x7fffffffL || row_stride < V || !valid_dtype(logits_dtype))
+    return GPTOSS_ERR_BAD_ARG;
+  if (T == 0)
+    return GPTOSS_OK;
+  if (!logits || !out)
+    return GPTOSS_ERR_BAD_ARG;
+  cudaStream_t s = as_stream(stream);
+  return logits_dtype == GPTOSS_F32 ? launch<float>(s, T, logits, V, row_stride, keys, out)
+                                    : launch<uint16_t>(s, T, logits, V, row_stride, keys, out);
+}
+
+extern "C" int gptoss_argmax_slices(int T, long V, gptoss_dtype_t logits_dtype, int has_keys) {
+  using namespace gptoss;
+  if (T <= 0 || V <= 0 || !valid_dtype(logits_dtype))
+    return 1;
+  const long per = logits_dtype == GPTOSS_F32 ? 4 : 8;
+  return plan_slices(T, V / per, has_keys != 0);
+}

@@ -1,0 +1,521 @@
+// The layer-chain driver (include/gptoss_engine.h): owns the device buffers of
+// one GPU and issues the fused kernels in the order of the reference engine's
+// decode step (step_embed, layer_attention, layer_route, layer_experts,
+// layer_combine, step_logits: getp-csrc/engine/gpu_engine.hpp:461-621), with a
+// caller-filled stand-in tensor wherever that engine runs a GEMM or attention.
+#include <string.h>
+
+#include <map>
+#include <new>
+#include <vector>
+
+#include "../../include/gptoss_engine.h"
+#include "common.cuh"
+
+namespace gptoss {
+int cuda_status(cudaError_t e);
+}
+using namespace gptoss;
+
+struct gptoss_chain {
+  gptoss_chain_config_t cfg;
+  int max_tokens = 0, n_sets = 0, device = 0;
+  cudaStream_t stream = nullptr;
+  size_t total_bytes = 0;
+  std::vector<void *> allocs;
+  // weights
+  void *embedding = nullptr;
+  float *gain_attn = nullptr, *gain_ffn = nullptr, *gain_out = nullptr, *qkv_bias = nullptr;
+  float *cos_tab = nullptr, *sin_tab = nullptr;
+  // stand-ins, n_sets of each (logits: one)
+  void *attn_proj = nullptr, *qkv = nullptr, *router = nullptr, *mlp1 = nullptr, *expert = nullptr,
+       *logits = nullptr;
+  // state
+  int *tokens = nullptr, *pos = nullptr, *next = nullptr, *topk_e = nullptr;
+  float *x = nullptr, *topk_w = nullptr;
+  void *normed = nullptr, *qkv_out = nullptr, *swiglu = nullptr;
+  unsigned long long *keys = nullptr;
+  void *flush = nullptr;
+  size_t flush_bytes = 0;
+  std::map<int, cudaGraphExec_t> graphs;
+  std::vector<cudaEvent_t> events;
+
+  size_t act() const { return cfg.act_dtype == GPTOSS_F32 ? 4 : 2; }
+  int qkv_dim() const { return (cfg.n_q_heads + 2 * cfg.n_kv_heads) * cfg.head_dim; }
+};
+
+namespace {
+
+template <typename P> int dev_alloc(gptoss_chain *c, P **p, size_t bytes) {
+  void *q = nullptr;
+  const int st = cuda_status(cudaMalloc(&q, bytes ? bytes : 16));
+  if (st != GPTOSS_OK)
+    return st;
+  c->allocs.push_back(q);
+  c->total_bytes += bytes;
+  *p = static_cast<P *>(q);
+  return GPTOSS_OK;
+}
+
+struct BufInfo {
+  void *base;
+  size_t bytes_per_layer; // size of one layer's (or the only) instance
+  int layered;            // 0: single, 1: per model layer, 2: per stand-in set
+};
+
+BufInfo buf_info(const gptoss_chain *c, gptoss_chain_buffer_t which) {
+  const gptoss_chain_config_t &g = c->cfg;
+  const size_t T = (size_t)c->max_tokens, H = (size_t)g.hidden, a = c->act(), K = (size_t)g.top_k;
+  const size_t half = (size_t)g.head_dim / 2;
+  switch (which) {
+  case GPTOSS_BUF_EMBEDDING: return {c->embedding, (size_t)g.vocab * H * a, 0};
+  case GPTOSS_BUF_GAIN_ATTN: return {c->gain_attn, H * 4, 1};
+  case GPTOSS_BUF_GAIN_FFN: return {c->gain_ffn, H * 4, 1};
+  case GPTOSS_BUF_GAIN_OUT: return {c->gain_out, H * 4, 0};
+  case GPTOSS_BUF_QKV_BIAS: return {c->qkv_bias, (size_t)c->qkv_dim() * 4, 1};
+  case GPTOSS_BUF_COS: return {c->cos_tab, (size_t)g.max_pos * half * 4, 0};
+  case GPTOSS_BUF_SIN: return {c->sin_tab, (size_t)g.max_pos * half * 4, 0};
+  case GPTOSS_BUF_ATTN_PROJ: return {c->attn_proj, T * H * a, 2};
+  case GPTOSS_BUF_QKV: return {c->qkv, T * (size_t)c->qkv_dim() * a, 2};
+  case GPTOSS_BUF_ROUTER: return {c->router, T * (size_t)g.n_experts * a, 2};
+  case GPTOSS_BUF_MLP1: return {c->mlp1, K * T * 2 * (size_t)g.inter * a, 2};
+  case GPTOSS_BUF_EXPERT: return {c->expert, K * T * H * a, 2};
+  case GPTOSS_BUF_LOGITS: return {c->logits, T * (size_t)g.vocab * a, 0};
+  case GPTOSS_BUF_TOKENS: return {c->tokens, T * 4, 0};
+  case GPTOSS_BUF_POS: return {c->pos, T * 4, 0};
+  case GPTOSS_BUF_X: return {c->x, T * H * 4, 0};
+  case GPTOSS_BUF_NORMED: return {c->normed, T * H * a, 0};
+  case GPTOSS_BUF_QKV_OUT: return {c->qkv_out, T * (size_t)c->qkv_dim() * a, 0};
+  case GPTOSS_BUF_TOPK_W: return {c->topk_w, T * K * 4, 0};
+  case GPTOSS_BUF_TOPK_E: return {c->topk_e, T * K * 4, 0};
+  case GPTOSS_BUF_SWIGLU: return {c->swiglu, K * T * (size_t)g.inter * a, 0};
+  case GPTOSS_BUF_NEXT: return {c->next, T * 4, 0};
+  default: return {nullptr, 0, 0};
+  }
+}
+
+char *layer_ptr(const gptoss_chain *c, gptoss_chain_buffer_t which, int layer) {
+  const BufInfo b = buf_info(c, which);
+  size_t idx = 0;
+  if (b.layered == 1)
+    idx = (size_t)layer;
+  else if (b.layered == 2)
+    idx = (size_t)(layer % c->n_sets);
+  return static_cast<char *>(b.base) + idx * b.bytes_per_layer;
+}
+
+// Called around every launch of a step; used by the profiler.
+struct Hook {
+  virtual void before(gptoss_chain_kernel_t) {}
+  virtual void after(gptoss_chain_kernel_t) {}
+  virtual ~Hook() {}
+};
+
+#define STEP(kind, call)                                                                          \
+  do {                                                                                            \
+    if (hook)                                                                                     \
+      hook->before(kind);                                                                         \
+    const int st_ = (call);                                                                       \
+    if (hook)                                                                                     \
+      hook->after(kind);                                                                          \
+    if (st_ != GPTOSS_OK)                                                                         \
+      return st_;                                                                                 \
+  } while (0)
+
+// Issues every kernel of one step for T rows on s.
+int issue_step(gptoss_chain *c, int T, cudaStream_t s, Hook *hook) {
+  const gptoss_chain_config_t &g = c->cfg;
+  const gptoss_dtype_t a = (gptoss_dtype_t)g.act_dtype;
+  const int H = g.hidden, L = g.n_layers, K = g.top_k, QKV = c->qkv_dim();
+  gptoss_stream_t gs = s;
+  // step_embed: x = embedding[tokens]
+  STEP(GPTOSS_K_EMBED, gptoss_embed(gs, T, c->embedding, a, g.vocab, c->tokens, c->x, GPTOSS_F32, H));
+  // layer 0's attention norm; later layers get theirs from the previous combine
+  STEP(GPTOSS_K_NORM, gptoss_add_rmsnorm(gs, T, c->x, nullptr, a, c->gain_attn, c->normed, a, H, g.flags));
+  for (int l = 0; l < L; l++) {
+    // [QKV GEMM of `normed`] -> stand-in qkv; bias + RoPE
+    STEP(GPTOSS_K_ROPE,
+         gptoss_qkv_bias_rope(gs, T, layer_ptr(c, GPTOSS_BUF_QKV, l), a, QKV,
+                              (const float *)layer_ptr(c, GPTOSS_BUF_QKV_BIAS, l), c->pos, 0,
+                              c->cos_tab, c->sin_tab, g.max_pos, g.n_q_heads, g.n_kv_heads,
+                              g.head_dim, c->qkv_out, a, QKV, g.flags));
+    // [attention + output GEMM] -> stand-in projection; residual add + MoE norm
+    STEP(GPTOSS_K_ADD_NORM,
+         gptoss_add_rmsnorm(gs, T, c->x, layer_ptr(c, GPTOSS_BUF_ATTN_PROJ, l), a,
+                            (const float *)layer_ptr(c, GPTOSS_BUF_GAIN_FFN, l), c->normed, a, H,
+                            g.flags));
+    // [router GEMM] -> stand-in logits; top-k + softmax
+    STEP(GPTOSS_K_ROUTER, gptoss_router_topk(gs, T, layer_ptr(c, GPTOSS_BUF_ROUTER, l), a,
+                                             g.n_experts, K, c->topk_w, c->topk_e, nullptr, nullptr));
+    // [mlp1 GEMM] -> stand-in gate/up rows; SwiGLU
+    STEP(GPTOSS_K_SWIGLU, gptoss_swiglu(gs, layer_ptr(c, GPTOSS_BUF_MLP1, l), a, c->swiglu, a,
+                                        (size_t)K * T, g.inter, g.swiglu_limit, g.flags));
+    // [mlp2 GEMM] -> stand-in expert rows; combine + residual + next norm
+    const float *next_gain = l + 1 < L ? (const float *)layer_ptr(c, GPTOSS_BUF_GAIN_ATTN, l + 1)
+                                       : c->gain_out;
+    STEP(GPTOSS_K_COMBINE,
+         gptoss_moe_combine(gs, T, c->x, layer_ptr(c, GPTOSS_BUF_EXPERT, l), a, nullptr, c->topk_w,
+                            c->topk_e, K, H, nullptr, next_gain, c->normed, a, g.flags));
+  }
+  // [LM-head GEMM of `normed`] -> stand-in logits; greedy pick
+  STEP(GPTOSS_K_ARGMAX, gptoss_argmax(gs, T, c->logits, a, g.vocab, g.vocab, c->keys, c->next));
+  return GPTOSS_OK;
+}
+
+struct ProfileHook : Hook {
+  gptoss_chain *c;
+  cudaStream_t s;
+  bool flush;
+  size_t n = 0;
+  std::vector<gptoss_chain_kernel_t> kinds;
+  ProfileHook(gptoss_chain *c_, cudaStream_t s_, bool f) : c(c_), s(s_), flush(f) {}
+  cudaEvent_t event(size_t i) {
+    while (c->events.size() <= i) {
+      cudaEvent_t e = nullptr;
+      cudaEventCreate(&e);
+      c->events.push_back(e);
+    }
+    return c->events[i];
+  }
+  void before(gptoss_chain_kernel_t k) override {
+    if (flush)
+      gptoss_flush_l2(c->flush, c->flush_bytes, s);
+    kinds.push_back(k);
+    cudaEventRecord(event(2 * n), s);
+  }
+  void after(gptoss_chain_kernel_t) override {
+    cudaEventRecord(event(2 * n + 1), s);
+    n++;
+  }
+};
+
+} // namespace
+
+extern "C" {
+
+int gptoss_chain_config_gpt_oss(int which, gptoss_dtype_t act_dtype, int max_pos,
+                                gptoss_chain_config_t *cfg) {
+  if (!cfg || (which != 20 && which != 120) || !valid_dtype(act_dtype) || max_pos <= 0)
+    return GPTOSS_ERR_BAD_ARG;
+  memset(cfg, 0, sizeof *cfg);
+  cfg->vocab = 201088;
+  cfg->hidden = 2880;
+  cfg->n_experts = which == 20 ? 32 : 128;
+  cfg->top_k = 4;
+  cfg->inter = 2880;
+  cfg->n_layers = which == 20 ? 24 : 36;
+  cfg->head_dim = 64;
+  cfg->n_q_heads = 64;
+  cfg->n_kv_heads = 8;
+  cfg->max_pos = max_pos;
+  cfg->orig_ctx = 4096.0f;
+  cfg->theta = 150000.0f;
+  cfg->factor = 32.0f;
+  cfg->beta_fast = 32.0f;
+  cfg->beta_slow = 1.0f;
+  cfg->swiglu_limit = 7.0f;
+  cfg->act_dtype = act_dtype;
+  cfg->flags = act_dtype == GPTOSS_F32 ? GPTOSS_EXACT : 0u;
+  return GPTOSS_OK;
+}
+
+int gptoss_chain_create(const gptoss_chain_config_t *cfg, int max_tokens, int n_standin_layers,
+                        gptoss_chain_t **out) {
+  if (!cfg || !out || max_tokens <= 0 || cfg->n_layers <= 0 || n_standin_layers <= 0 ||
+      n_standin_layers > cfg->n_layers || cfg->hidden <= 0 || cfg->vocab <= 0 || cfg->inter <= 0 ||
+      cfg->top_k <= 0 || cfg->top_k > GPTOSS_MAX_TOPK || cfg->n_experts < cfg->top_k ||
+      cfg->n_experts > GPTOSS_MAX_EXPERTS || cfg->head_dim <= 0 || cfg->head_dim % 2 != 0 ||
+      cfg->max_pos <= 0 || !valid_dtype((gptoss_dtype_t)cfg->act_dtype))
+    return GPTOSS_ERR_BAD_ARG;
+  *out = nullptr;
+  gptoss_chain *c = new (std::nothrow) gptoss_chain;
+  if (!c)
+    return GPTOSS_ERR_BAD_ARG;
+  c->cfg = *cfg;
+  c->max_tokens = max_tokens;
+  c->n_sets = n_standin_layers;
+  int st = cuda_status(cudaGetDevice(&c->device));
+  if (st == GPTOSS_OK)
+    st = cuda_status(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+  const size_t T = (size_t)max_tokens, H = (size_t)cfg->hidden, a = c->act(), K = (size_t)cfg->top_k;
+  const size_t L = (size_t)cfg->n_layers, S = (size_t)c->n_sets, QKV = (size_t)c->qkv_dim();
+  const size_t half = (size_t)cfg->head_dim / 2;
+#define ALLOC(field, bytes)                                                                       \
+  if (st == GPTOSS_OK)                                                                            \
+  st = dev_alloc(c, &c->field, (bytes))
+  ALLOC(embedding, (size_t)cfg->vocab * H * a);
+  ALLOC(gain_attn, L * H * 4);
+  ALLOC(gain_ffn, L * H * 4);
+  ALLOC(gain_out, H * 4);
+  ALLOC(qkv_bias, L * QKV * 4);
+  ALLOC(cos_tab, (size_t)cfg->max_pos * half * 4);
+  ALLOC(sin_tab, (size_t)cfg->max_pos * half * 4);
+  ALLOC(attn_proj, S * T * H * a);
+  ALLOC(qkv, S * T * QKV * a);
+  ALLOC(router, S * T * (size_t)cfg->n_experts * a);
+  ALLOC(mlp1, S * K * T * 2 * (size_t)cfg->inter * a);
+  ALLOC(expert, S * K * T * H * a);
+  ALLOC(logits, T * (size_t)cfg->vocab * a);
+  ALLOC(tokens, T * 4);
+  ALLOC(pos, T * 4);
+  ALLOC(next, T * 4);
+  ALLOC(x, T * H * 4);
+  ALLOC(normed, T * H * a);
+  ALLOC(qkv_out, T * QKV * a);
+  ALLOC(topk_w, T * K * 4);
+  ALLOC(topk_e, T * K * 4);
+  ALLOC(swiglu, K * T * (size_t)cfg->inter * a);
+  ALLOC(keys, T * 8);
+  c->flush_bytes = (size_t)256 << 20;
+  ALLOC(flush, c->flush_bytes);
+#undef ALLOC
+  if (st == GPTOSS_OK)
+    st = cuda_status(cudaMemsetAsync(c->keys, 0, T * 8, c->stream));
+  if (st == GPTOSS_OK)
+    st = cuda_status(cudaMemsetAsync(c->tokens, 0, T * 4, c->stream));
+  if (st == GPTOSS_OK)
+    st = cuda_status(cudaMemsetAsync(c->pos, 0, T * 4, c->stream));
+  if (st == GPTOSS_OK) {
+    std::vector<float> cs((size_t)cfg->max_pos * half), sn((size_t)cfg->max_pos * half);
+    st = gptoss_build_rope_tables(cfg->max_pos, cfg->head_dim, cfg->theta, cfg->factor,
+                                  cfg->orig_ctx, cfg->beta_fast, cfg->beta_slow, cs.data(),
+                                  sn.data());
+    if (st == GPTOSS_OK)
+      st = cuda_status(cudaMemcpy(c->cos_tab, cs.data(), cs.size() * 4, cudaMemcpyHostToDevice));
+    if (st == GPTOSS_OK)
+      st = cuda_status(cudaMemcpy(c->sin_tab, sn.data(), sn.size() * 4, cudaMemcpyHostToDevice));
+  }
+  if (st == GPTOSS_OK)
+    st = cuda_status(cudaStreamSynchronize(c->stream));
+  if (st != GPTOSS_OK) {
+    gptoss_chain_destroy(c);
+    return st;
+  }
+  *out = c;
+  return GPTOSS_OK;
+}
+
+int gptoss_chain_destroy(gptoss_chain_t *c) {
+  if (!c)
+    return GPTOSS_OK;
+  if (c->stream)
+    (void)cudaStreamSynchronize(c->stream);
+  for (auto &kv : c->graphs)
+    (void)cudaGraphExecDestroy(kv.second);
+  for (cudaEvent_t e : c->events)
+    (void)cudaEventDestroy(e);
+  for (void *p : c->allocs)
+    (void)cudaFree(p);
+  if (c->stream)
+    (void)cudaStreamDestroy(c->stream);
+  delete c;
+  return GPTOSS_OK;
+}
+
+size_t gptoss_chain_device_bytes(const gptoss_chain_t *c) { return c ? c->total_bytes : 0; }
+
+gptoss_stream_t gptoss_chain_stream(const gptoss_chain_t *c) { return c ? c->stream : nullptr; }
+
+int gptoss_chain_buffer(const gptoss_chain_t *c, gptoss_chain_buffer_t which, int layer,
+                        void **device_ptr, size_t *bytes) {
+  if (!c || which < 0 || which >= GPTOSS_BUF_COUNT || layer < 0 || layer >= c->cfg.n_layers)
+    return GPTOSS_ERR_BAD_ARG;
+  const BufInfo b = buf_info(c, which);
+  if (device_ptr)
+    *device_ptr = layer_ptr(c, which, layer);
+  if (bytes)
+    *bytes = b.bytes_per_layer;
+  return GPTOSS_OK;
+}
+
+int gptoss_chain_fill_synthetic(gptoss_chain_t *c, int T, uint64_t seed, int threads) {
+  if (!c || T <= 0 || T > c->max_tokens)
+    return GPTOSS_ERR_BAD_ARG;
+  const gptoss_chain_config_t &g = c->cfg;
+  const gptoss_dtype_t a = (gptoss_dtype_t)g.act_dtype;
+  const size_t H = (size_t)g.hidden, K = (size_t)g.top_k, QKV = (size_t)c->qkv_dim(), el = c->act();
+  // One host staging buffer, reused for every tensor, cut into pieces so the
+  // host generates piece i+1 while piece i is on its way to the device.
+  const size_t piece_elems = (size_t)32 << 20;
+  void *stage[2] = {nullptr, nullptr};
+  int st = cuda_status(cudaMallocHost(&stage[0], piece_elems * 4));
+  if (st == GPTOSS_OK)
+    st = cuda_status(cudaMallocHost(&stage[1], piece_elems * 4));
+  cudaEvent_t done[2] = {nullptr, nullptr};
+  if (st == GPTOSS_OK)
+    st = cuda_status(cudaEventCreate(&done[0]));
+  if (st == GPTOSS_OK)
+    st = cuda_status(cudaEventCreate(&done[1]));
+  int turn = 0;
+  uint64_t stream_id = 0;
+  // Rows of a stand-in are generated for T rows although the buffer holds
+  // max_tokens: the chain indexes rows, so a prefix is all a T-row step reads.
+  auto fill = [&](void *dev, gptoss_dtype_t dt, size_t count, float mean, float sd) {
+    const size_t esz = dt == GPTOSS_F32 ? 4 : 2;
+    const uint64_t sid = stream_id++;
+    for (size_t off = 0; off < count && st == GPTOSS_OK; off += piece_elems) {
+      const size_t n = count - off < piece_elems ? count - off : piece_elems;
+      st = cuda_status(cudaEventSynchronize(done[turn]));
+      if (st != GPTOSS_OK)
+        break;
+      // a piece is its own sub-stream so pieces are independent of piece size
+      st = gptoss_synth_normal(stage[turn], dt, n, seed, sid * 4096 + off / piece_elems, mean, sd,
+                               threads);
+      if (st != GPTOSS_OK)
+        break;
+      st = cuda_status(cudaMemcpyAsync((char *)dev + off * esz, stage[turn], n * esz,
+                                       cudaMemcpyHostToDevice, c->stream));
+      if (st == GPTOSS_OK)
+        st = cuda_status(cudaEventRecord(done[turn], c->stream));
+      turn ^= 1;
+    }
+  };
+  if (st == GPTOSS_OK) {
+    fill(c->embedding, a, (size_t)g.vocab * H, 0.0f, 0.02f);
+    fill(c->gain_attn, GPTOSS_F32, (size_t)g.n_layers * H, 1.0f, 0.1f);
+    fill(c->gain_ffn, GPTOSS_F32, (size_t)g.n_layers * H, 1.0f, 0.1f);
+    fill(c->gain_out, GPTOSS_F32, H, 1.0f, 0.1f);
+    fill(c->qkv_bias, GPTOSS_F32, (size_t)g.n_layers * QKV, 0.0f, 0.02f);
+    for (int l = 0; l < c->n_sets; l++) {
+      fill(layer_ptr(c, GPTOSS_BUF_ATTN_PROJ, l), a, (size_t)T * H, 0.0f, 1.0f);
+      fill(layer_ptr(c, GPTOSS_BUF_QKV, l), a, (size_t)T * QKV, 0.0f, 1.0f);
+      fill(layer_ptr(c, GPTOSS_BUF_ROUTER, l), a, (size_t)T * g.n_experts, 0.0f, 1.0f);
+      fill(layer_ptr(c, GPTOSS_BUF_MLP1, l), a, K * T * 2 * (size_t)g.inter, 0.0f, 2.0f);
+      fill(layer_ptr(c, GPTOSS_BUF_EXPERT, l), a, K * T * H, 0.0f, 1.0f);
+    }
+    fill(c->logits, a, (size_t)T * g.vocab, 0.0f, 3.0f);
+  }
+  (void)el;
+  if (st == GPTOSS_OK)
+    st = cuda_status(cudaStreamSynchronize(c->stream));
+  if (done[0])
+    (void)cudaEventDestroy(done[0]);
+  if (done[1])
+    (void)cudaEventDestroy(done[1]);
+  if (stage[0])
+    (void)cudaFreeHost(stage[0]);
+  if (stage[1])
+    (void)cudaFreeHost(stage[1]);
+  return st;
+}
+
+int gptoss_chain_enqueue(gptoss_chain_t *c, int T, int use_graph) {
+  if (!c || T < 0 || T > c->max_tokens)
+    return GPTOSS_ERR_BAD_ARG;
+  if (T == 0)
+    return GPTOSS_OK;
+  if (!use_graph)
+    return issue_step(c, T, c->stream, nullptr);
+  auto it = c->graphs.find(T);
+  if (it == c->graphs.end()) {
+    // Warm every kernel once outside capture (occupancy queries, lazy module load).
+    int st = issue_step(c, T, c->stream, nullptr);
+    if (st != GPTOSS_OK)
+      return st;
+    st = cuda_status(cudaStreamSynchronize(c->stream));
+    if (st != GPTOSS_OK)
+      return st;
+    st = cuda_status(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
+    if (st != GPTOSS_OK)
+      return st;
+    const int issued = issue_step(c, T, c->stream, nullptr);
+    cudaGraph_t graph = nullptr;
+    st = cuda_status(cudaStreamEndCapture(c->stream, &graph));
+    if (issued != GPTOSS_OK || st != GPTOSS_OK) {
+      if (graph)
+        (void)cudaGraphDestroy(graph);
+      return issued != GPTOSS_OK ? issued : st;
+    }
+    cudaGraphExec_t exec = nullptr;
+    st = cuda_status(cudaGraphInstantiate(&exec, graph, 0));
+    (void)cudaGraphDestroy(graph);
+    if (st != GPTOSS_OK)
+      return st;
+    it = c->graphs.emplace(T, exec).first;
+  }
+  return cuda_status(cudaGraphLaunch(it->second, c->stream));
+}
+
+int gptoss_chain_step(gptoss_chain_t *c, int T, const int *tokens_host, const int *pos_host,
+                      int *next_host) {
+  if (!c || T < 0 || T > c->max_tokens || (T > 0 && (!tokens_host || !pos_host || !next_host)))
+    return GPTOSS_ERR_BAD_ARG;
+  if (T == 0)
+    return GPTOSS_OK;
+  int st = cuda_status(cudaMemcpyAsync(c->tokens, tokens_host, (size_t)T * 4, cudaMemcpyHostToDevice, c->stream));
+  if (st == GPTOSS_OK)
+    st = cuda_status(cudaMemcpyAsync(c->pos, pos_host, (size_t)T * 4, cudaMemcpyHostToDevice, c->stream));
+  if (st == GPTOSS_OK)
+    st = gptoss_chain_enqueue(c, T, 1);
+  if (st == GPTOSS_OK)
+    st = cuda_status(cudaMemcpyAsync(next_host, c->next, (size_t)T * 4, cudaMemcpyDeviceToHost, c->stream));
+  if (st == GPTOSS_OK)
+    st = cuda_status(cudaStreamSynchronize(c->stream));
+  return st;
+}
+
+int gptoss_chain_profile(gptoss_chain_t *c, int T, int steps, int flush_l2, double *ms_per_kind,
+                         long *launches_per_kind) {
+  if (!c || T <= 0 || T > c->max_tokens || steps <= 0 || !ms_per_kind || !launches_per_kind)
+    return GPTOSS_ERR_BAD_ARG;
+  for (int k = 0; k < GPTOSS_K_COUNT; k++) {
+    ms_per_kind[k] = 0.0;
+    launches_per_kind[k] = 0;
+  }
+  for (int s = 0; s < steps; s++) {
+    ProfileHook hook(c, c->stream, flush_l2 != 0);
+    int st = issue_step(c, T, c->stream, &hook);
+    if (st != GPTOSS_OK)
+      return st;
+    st = cuda_status(cudaStreamSynchronize(c->stream));
+    if (st != GPTOSS_OK)
+      return st;
+    for (size_t i = 0; i < hook.n; i++) {
+      float ms = 0.0f;
+      st = cuda_status(cudaEventElapsedTime(&ms, c->events[2 * i], c->events[2 * i + 1]));
+      if (st != GPTOSS_OK)
+        return st;
+      ms_per_kind[hook.kinds[i]] += ms;
+      launches_per_kind[hook.kinds[i]]++;
+    }
+  }
+  return GPTOSS_OK;
+}
+
+size_t gptoss_chain_kernel_bytes(const gptoss_chain_t *c, gptoss_chain_kernel_t kind, int T) {
+  if (!c || T <= 0)
+    return 0;
+  const gptoss_chain_config_t &g = c->cfg;
+  const size_t t = (size_t)T, H = (size_t)g.hidden, a = c->act(), K = (size_t)g.top_k;
+  const size_t QKV = (size_t)c->qkv_dim();
+  switch (kind) {
+  case GPTOSS_K_EMBED: // id + table row in + fp32 row out
+    return t * (4 + H * a + H * 4);
+  case GPTOSS_K_NORM: // x in, normed out, gain once
+    return t * (H * 4 + H * a) + H * 4;
+  case GPTOSS_K_ROPE: // qkv in and out, position; bias once; cos/sin rows stay in cache
+    return t * (2 * QKV * a + 4) + QKV * 4;
+  case GPTOSS_K_ADD_NORM: // x in/out, delta in, normed out, gain once
+    return t * (2 * H * 4 + 2 * H * a) + H * 4;
+  case GPTOSS_K_ROUTER: // logits in, k indices and k weights out
+    return t * ((size_t)g.n_experts * a + K * 8);
+  case GPTOSS_K_SWIGLU: // k rows of 2I in, k rows of I out
+    return t * K * 3 * (size_t)g.inter * a;
+  case GPTOSS_K_COMBINE: // k expert rows, k indices and weights, x in/out, normed out, gain once
+    return t * (K * H * a + K * 8 + 2 * H * 4 + H * a) + H * 4;
+  case GPTOSS_K_ARGMAX: // logits in, one index out
+    return t * ((size_t)g.vocab * a + 4);
+  default:
+    return 0;
+  }
+}
+
+int gptoss_chain_launches_per_step(const gptoss_chain_t *c, int T) {
+  if (!c || T <= 0)
+    return 0;
+  // embed, first norm, 5 per layer, argmax scan (+ its key decode when rows are split)
+  const int slices = gptoss_argmax_slices(T, c->cfg.vocab, (gptoss_dtype_t)c->cfg.act_dtype, 1);
+  return 2 + 5 * c->cfg.n_layers + (slices > 1 ? 2 : 1);
+}
+
+} // extern "C"

@@ -1,0 +1,227 @@
+// Shared device helpers of the fused gpt-oss kernels (sm_100a): 128-bit global
+// loads and stores, bf16 packing, warp and block reductions, launch plumbing.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <type_traits>
+
+#include "../../include/gptoss_kernels.h"
+
+namespace gptoss {
+
+constexpr int kWarp = 32;
+
+// ---- host-side plumbing -----------------------------------------------------
+
+// Remembers the last CUDA error seen by this thread (gptoss_last_cuda_error).
+void note_cuda_error(cudaError_t e);
+
+// Streaming multiprocessors of the current device (cached per device).
+int sm_count();
+
+inline cudaStream_t as_stream(gptoss_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
+
+// After a launch: GPTOSS_OK or GPTOSS_ERR_CUDA.
+inline int launch_status() {
+  const cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess)
+    return GPTOSS_OK;
+  note_cuda_error(e);
+  return GPTOSS_ERR_CUDA;
+}
+
+// Thread blocks of `kernel` that fit on one SM at `threads` threads per block.
+// Cached per call site (the static lives in the caller's template instance).
+template <typename K> inline int blocks_per_sm(K kernel, int threads, int *cache_slot) {
+  if (*cache_slot > 0)
+    return *cache_slot;
+  int n = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, 0) != cudaSuccess || n < 1)
+    n = 1;
+  *cache_slot = n;
+  return n;
+}
+
+// Grid for a row-strided kernel: every SM full, never more blocks than rows.
+inline int row_grid(long rows, int per_sm) {
+  const long full = (long)sm_count() * per_sm;
+  return (int)(rows < full ? rows : full);
+}
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline bool valid_dtype(gptoss_dtype_t d) { return d == GPTOSS_F32 || d == GPTOSS_BF16; }
+inline size_t dtype_size(gptoss_dtype_t d) { return d == GPTOSS_F32 ? 4 : 2; }
+
+// ---- 128-bit memory access ----------------------------------------------------
+
+// Read-once data (activations streamed through the kernel): do not keep the
+// line in L1.  A coherent load, so in-place operation (the same thread later
+// overwrites what it read) stays well defined.
+__device__ __forceinline__ uint4 ld_stream(const void *p) {
+  uint4 v;
+  asm volatile("ld.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+// Data that is read, then written back by the same thread (the residual row):
+// plain coherent load.
+__device__ __forceinline__ uint4 ld_plain(const void *p) {
+  return *reinterpret_cast<const uint4 *>(p);
+}
+
+// Small tables shared by every row (gains, bias, cos/sin): keep them cached.
+__device__ __forceinline__ uint4 ld_table(const void *p) {
+  return __ldg(reinterpret_cast<const uint4 *>(p));
+}
+
+// Written once, not read again by this kernel.
+__device__ __forceinline__ void st_stream(void *p, uint4 v) {
+  asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w)
+               : "memory");
+}
+
+__device__ __forceinline__ void st_stream8(void *p, uint2 v) {
+  asm volatile("st.global.cs.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
+}
+
+// ---- bf16 <-> fp32 --------------------------------------------------------------
+
+__device__ __forceinline__ float bf16_lo(uint32_t pair) { return __uint_as_float(pair << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t pair) {
+  return __uint_as_float(pair & 0xffff0000u);
+}
+
+// Round to nearest even on the upper 16 bits; a NaN stays a (quiet) NaN.
+__device__ __forceinline__ uint32_t f32_to_bf16_bits(float f) {
+  uint32_t u = __float_as_uint(f);
+  if ((u & 0x7fffffffu) > 0x7f800000u)
+    return (u >> 16) | 0x40u;
+  u += 0x7fffu + ((u >> 16) & 1u);
+  return u >> 16;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  return f32_to_bf16_bits(lo) | (f32_to_bf16_bits(hi) << 16);
+}
+
+// Eight consecutive values of a row held by one thread.
+struct Vec8 {
+  float v[8];
+};
+
+enum { kStream = 0, kPlain = 1, kTable = 2 };
+
+template <int KIND> __device__ __forceinline__ uint4 ld16(const void *p) {
+  if (KIND == kStream)
+    return ld_stream(p);
+  if (KIND == kPlain)
+    return ld_plain(p);
+  return ld_table(p);
+}
+
+template <int KIND> __device__ __forceinline__ Vec8 load8_f32(const float *base, size_t e) {
+  const uint4 a = ld16<KIND>(base + e), b = ld16<KIND>(base + e + 4);
+  Vec8 r;
+  r.v[0] = __uint_as_float(a.x), r.v[1] = __uint_as_float(a.y), r.v[2] = __uint_as_float(a.z),
+  r.v[3] = __uint_as_float(a.w), r.v[4] = __uint_as_float(b.x), r.v[5] = __uint_as_float(b.y),
+  r.v[6] = __uint_as_float(b.z), r.v[7] = __uint_as_float(b.w);
+  return r;
+}
+
+__device__ __forceinline__ Vec8 widen8(uint4 a) {
+  Vec8 r;
+  r.v[0] = bf16_lo(a.x), r.v[1] = bf16_hi(a.x), r.v[2] = bf16_lo(a.y), r.v[3] = bf16_hi(a.y),
+  r.v[4] = bf16_lo(a.z), r.v[5] = bf16_hi(a.z), r.v[6] = bf16_lo(a.w), r.v[7] = bf16_hi(a.w);
+  return r;
+}
+
+template <int KIND> __device__ __forceinline__ Vec8 load8_bf16(const uint16_t *base, size_t e) {
+  return widen8(ld16<KIND>(base + e));
+}
+
+// dtype-generic: T is float or uint16_t (bf16 bits).
+template <int KIND, typename T> __device__ __forceinline__ Vec8 load8(const T *base, size_t e) {
+  if constexpr (sizeof(T) == 4)
+    return load8_f32<KIND>(reinterpret_cast<const float *>(base), e);
+  else
+    return load8_bf16<KIND>(reinterpret_cast<const uint16_t *>(base), e);
+}
+
+__device__ __forceinline__ void store8_f32(float *base, size_t e, const Vec8 &r, bool stream) {
+  const uint4 a = make_uint4(__float_as_uint(r.v[0]), __float_as_uint(r.v[1]),
+                             __float_as_uint(r.v[2]), __float_as_uint(r.v[3]));
+  const uint4 b = make_uint4(__float_as_uint(r.v[4]), __float_as_uint(r.v[5]),
+                             __float_as_uint(r.v[6]), __float_as_uint(r.v[7]));
+  if (stream) {
+    st_stream(base + e, a);
+    st_stream(base + e + 4, b);
+  } else {
+    *reinterpret_cast<uint4 *>(base + e) = a;
+    *reinterpret_cast<uint4 *>(base + e + 4) = b;
+  }
+}
+
+__device__ __forceinline__ void store8_bf16(uint16_t *base, size_t e, const Vec8 &r) {
+  st_stream(base + e, make_uint4(pack_bf16(r.v[0], r.v[1]), pack_bf16(r.v[2], r.v[3]),
+                                 pack_bf16(r.v[4], r.v[5]), pack_bf16(r.v[6], r.v[7])));
+}
+
+template <typename T>
+__device__ __forceinline__ void store8(T *base, size_t e, const Vec8 &r, bool stream = true) {
+  if constexpr (sizeof(T) == 4)
+    store8_f32(reinterpret_cast<float *>(base), e, r, stream);
+  else
+    store8_bf16(reinterpret_cast<uint16_t *>(base), e, r);
+}
+
+// Scalar element access for the generic (unaligned / odd-sized) kernels.
+template <typename T> __device__ __forceinline__ float load1(const T *p) {
+  if constexpr (sizeof(T) == 4)
+    return *reinterpret_cast<const float *>(p);
+  else
+    return __uint_as_float((uint32_t)*reinterpret_cast<const uint16_t *>(p) << 16);
+}
+template <typename T> __device__ __forceinline__ void store1(T *p, float v) {
+  if constexpr (sizeof(T) == 4)
+    *reinterpret_cast<float *>(p) = v;
+  else
+    *reinterpret_cast<uint16_t *>(p) = (uint16_t)f32_to_bf16_bits(v);
+}
+
+// ---- reductions ---------------------------------------------------------------
+
+template <typename T> __device__ __forceinline__ T warp_sum(T v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1)
+    v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// Sum over the block; every thread receives it.  scratch: 32 values of T in
+// shared memory, reusable after the next __syncthreads().
+template <typename T> __device__ __forceinline__ T block_sum(T v, T *scratch) {
+  v = warp_sum(v);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = (blockDim.x + 31) >> 5;
+  if (lane == 0)
+    scratch[warp] = v;
+  __syncthreads();
+  T t = lane < n_warps ? scratch[lane] : T(0);
+  t = warp_sum(t);
+  return t;
+}
+
+__device__ __forceinline__ unsigned long long warp_max_u64(unsigned long long v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const unsigned long long other = __shfl_xor_sync(0xffffffffu, v, o);
+    v = other > v ? other : v;
+  }
+  return v;
+}
+
+} // namespace gptoss

@@ -1,0 +1,113 @@
+// Token-embedding gather (gptoss_embed): x[t,:] = table[ids[t],:].
+//
+// Pure data movement: per token one id, one table row in, one row out.  Work is
+// cut into chunks of 8 elements; every thread fetches kUnroll chunks with
+// 128-bit loads before it stores any of them, so a warp keeps 2 KB (bf16 table)
+// to 4 KB (fp32 table) of reads in flight.  Rows are random, but each row is a
+// contiguous multi-kilobyte run, so DRAM pages are still used whole.
+#include "common.cuh"
+
+namespace gptoss {
+namespace {
+
+constexpr int kUnroll = 4;
+
+// WIDEN = false: rows are copied as raw 16-byte pieces (table and x have the
+// same element type; row_bytes = H * element size).  WIDEN = true: each 16-byte
+// piece holds 8 bf16 values that leave as 8 fp32 values (bits << 16).
+template <bool WIDEN>
+__global__ void embed_rows(const unsigned char *__restrict__ table, const int *__restrict__ ids,
+                           unsigned char *__restrict__ x, long total_chunks, int chunks_per_row,
+                           size_t row_bytes, int V) {
+  const long stride = (long)gridDim.x * blockDim.x;
+  for (long base = (long)blockIdx.x * blockDim.x + threadIdx.x; base < total_chunks;
+       base += stride * kUnroll) {
+    uint4 v[kUnroll];
+    bool live[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; u++) {
+      const long unit = base + u * stride;
+      live[u] = unit < total_chunks;
+      v[u] = make_uint4(0u, 0u, 0u, 0u);
+      if (live[u]) {
+        const int row = (int)(unit / chunks_per_row), c = (int)(unit % chunks_per_row);
+        const int id = __ldg(ids + row);
+        if (id >= 0 && id < V)
+          v[u] = ld_stream(table + (size_t)id * row_bytes + (size_t)c * 16);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; u++)
+      if (live[u]) {
+        const size_t unit = (size_t)(base + u * stride);
+        if (WIDEN) {
+          st_stream(x + unit * 32, make_uint4(v[u].x << 16, v[u].x & 0xffff0000u, v[u].y << 16,
+                                              v[u].y & 0xffff0000u));
+          st_stream(x + unit * 32 + 16, make_uint4(v[u].z << 16, v[u].z & 0xffff0000u,
+                                                   v[u].w << 16, v[u].w & 0xffff0000u));
+        } else {
+          st_stream(x + unit * 16, v[u]);
+        }
+      }
+  }
+}
+
+// Any H and alignment: one element per thread step.
+template <typename TT, typename OT>
+__global__ void embed_rows_generic(const TT *__restrict__ table, const int *__restrict__ ids,
+                                   OT *__restrict__ x, int T, int H, int V) {
+  for (int row = blockIdx.x; row < T; row += gridDim.x) {
+    const int id = ids[row];
+    const bool ok = id >= 0 && id < V;
+    for (int j = threadIdx.x; j < H; j += blockDim.x) {
+      if constexpr (sizeof(TT) == sizeof(OT)) // same type: move the bits untouched
+        x[(size_t)row * H + j] = ok ? table[(size_t)id * H + j] : OT(0);
+      else
+        store1(x + (size_t)row * H + j, ok ? load1(table + (size_t)id * H + j) : 0.0f);
+    }
+  }
+}
+
+template <typename TT, typename OT>
+int launch(cudaStream_t s, int T, const void *table, int V, const int *ids, void *x, int H) {
+  constexpr bool widen = sizeof(TT) != sizeof(OT);
+  const size_t row_bytes = (size_t)H * sizeof(TT);
+  if (row_bytes % 16 != 0 || !aligned16(table) || !aligned16(x)) {
+    embed_rows_generic<TT, OT><<<row_grid(T, 8), 256, 0, s>>>(
+        static_cast<const TT *>(table), ids, static_cast<OT *>(x), T, H, V);
+    return launch_status();
+  }
+  const int cpr = (int)(row_bytes / 16);
+  const long total = (long)T * cpr;
+  constexpr int threads = 256;
+  static int occ = 0;
+  auto k = embed_rows<widen>;
+  const long want = (total + (long)threads * kUnroll - 1) / ((long)threads * kUnroll);
+  k<<<row_grid(want, blocks_per_sm(k, threads, &occ)), threads, 0, s>>>(
+      static_cast<const unsigned char *>(table), ids, static_cast<unsigned char *>(x), total, cpr,
+      row_bytes, V);
+  return launch_status();
+}
+
+} // namespace
+} // namespace gptoss
+
+extern "C" int gptoss_embed(gptoss_stream_t stream, int T, const void *table,
+                            gptoss_dtype_t table_dtype, int V, const int *ids, void *x,
+                            gptoss_dtype_t x_dtype, int H) {
+  using namespace gptoss;
+  if (T < 0 || H <= 0 || V <= 0 || !valid_dtype(table_dtype) || !valid_dtype(x_dtype))
+    return GPTOSS_ERR_BAD_ARG;
+  if (T == 0)
+    return GPTOSS_OK;
+  if (!table || !ids || !x)
+    return GPTOSS_ERR_BAD_ARG;
+  cudaStream_t s = as_stream(stream);
+  if (table_dtype == GPTOSS_BF16 && x_dtype == GPTOSS_F32)
+    return launch<uint16_t, float>(s, T, table, V, ids, x, H);
+  if (table_dtype == GPTOSS_BF16 && x_dtype == GPTOSS_BF16)
+    return launch<uint16_t, uint16_t>(s, T, table, V, ids, x, H);
+  if (table_dtype == GPTOSS_F32 && x_dtype == GPTOSS_F32)
+    return launch<float, float>(s, T, table, V, ids, x, H);
+  return GPTOSS_ERR_UNSUPPORTED; // narrowing an fp32 table would not be a bit-exact copy
+}

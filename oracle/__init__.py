@@ -1,0 +1,270 @@
+"""ctypes bindings for the CPU checkers.  TEST INFRASTRUCTURE ONLY.
+
+Two libraries live here:
+
+* ``libgptoss_oracle.so`` -- the restated CPU oracle (``gptoss_oracle.c``), built by
+  ``make -C oracle oracle``.  Always available (gcc is the only requirement).
+* ``_ref/libgptoss_ref.so`` -- the reference's own CPU functions compiled from its
+  checkout (``make -C oracle ref``).  Only buildable where the reference checkout is
+  present; the built file is carried along to machines that do not have it.
+
+Only the test suite, the smoke check and the bench's CPU-baseline legs import this
+package.  The shipped library never does.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+ORACLE_SO = os.path.join(_HERE, "libgptoss_oracle.so")
+REF_SO = os.path.join(_HERE, "_ref", "libgptoss_ref.so")
+REFERENCE_CHECKOUT = os.environ.get("GPTOSS_REFERENCE", "/root/reference")
+
+_f32p = np.ctypeslib.ndpointer(dtype=np.float32, flags="C_CONTIGUOUS")
+_i32p = np.ctypeslib.ndpointer(dtype=np.int32, flags="C_CONTIGUOUS")
+_opt = C.c_void_p  # optional array arguments are passed as raw addresses
+
+
+def build(ref: bool | None = None) -> None:
+    """Compile the oracle, and the reference checker when its checkout is present."""
+    subprocess.run(["make", "-s", "-C", _HERE, "oracle"], check=True)
+    if ref is None:
+        ref = os.path.exists(os.path.join(REFERENCE_CHECKOUT, "run.cpp"))
+    if ref:
+        subprocess.run(["make", "-s", "-C", _HERE, "ref", f"REF={REFERENCE_CHECKOUT}"], check=True)
+
+
+def _addr(a):
+    return None if a is None else a.ctypes.data
+
+
+class OrcConfig(C.Structure):
+    """Byte image shared by the oracle's orc_config_t and the reference's Config."""
+
+    _fields_ = [
+        ("vocab", C.c_int), ("hidden", C.c_int), ("n_experts", C.c_int), ("top_k", C.c_int),
+        ("inter", C.c_int), ("n_layers", C.c_int), ("head_dim", C.c_int), ("n_q_heads", C.c_int),
+        ("n_kv_heads", C.c_int), ("seq_len", C.c_int), ("orig_ctx", C.c_int),
+        ("theta", C.c_float), ("factor", C.c_float), ("window", C.c_int), ("limit", C.c_float),
+    ]
+
+
+def flat_weight_count(c: OrcConfig) -> int:
+    """Number of floats memory_map_weights() walks over for this config."""
+    qkv = (c.n_q_heads + 2 * c.n_kv_heads) * c.head_dim
+    L, H, E, I, V = c.n_layers, c.hidden, c.n_experts, c.inter, c.vocab
+    return (2 * V * H + 2 * L * H + H + L * H * qkv + L * qkv + L * c.n_q_heads * c.head_dim * H
+            + L * H + L * c.n_q_heads + L * H * E + L * E + L * E * 2 * I * H + L * E * 2 * I
+            + L * E * H * I + L * E * H)
+
+
+class _Lib:
+    def __init__(self, path: str, prefix: str):
+        if not os.path.exists(path):
+            raise FileNotFoundError(f"{path} is not built (run `make -C oracle`)")
+        self.lib = C.CDLL(path)
+        self.p = prefix
+        L = self.lib
+        p = prefix
+
+        def sig(name, res, *args):
+            fn = getattr(L, p + name)
+            fn.restype = res
+            fn.argtypes = list(args)
+            return fn
+
+        self._rmsnorm = sig("rmsnorm", None, _f32p, _f32p, _f32p, C.c_int)
+        self._softmax = sig("softmax", None, _f32p, C.c_int)
+        self._topk = sig("topk", None if p == "ref_" else C.c_int, _f32p, _i32p, _f32p, C.c_int, C.c_int)
+        self._inv_freq = sig("yarn_inv_freq", None, C.c_float, C.c_int, C.c_float, C.c_float,
+                             C.c_float, C.c_float, C.POINTER(C.c_float), _f32p)
+        self._cos_sin = sig("yarn_cos_sin", None, C.c_int, C.c_float, C.c_int, C.c_float, C.c_float,
+                            C.c_float, C.c_float, _f32p, _f32p)
+        self._rotate = sig("rotate_heads", None, _f32p, _f32p, _f32p, C.c_int, C.c_int)
+        self._argmax = sig("argmax", C.c_int, _f32p, C.c_int)
+        self._add_rmsnorm_rows = sig("add_rmsnorm_rows", None, _f32p, _opt, _f32p, _f32p, C.c_int,
+                                     C.c_int, C.c_int)
+        self._bias_rope_rows = sig("bias_rope_rows", None, _f32p, _opt, _i32p, C.c_int, C.c_int,
+                                   C.c_int, C.c_int, C.c_float, C.c_float, C.c_float, C.c_float,
+                                   C.c_float, C.c_int)
+        self._router_rows = sig("router_rows", None, _f32p, _i32p, _f32p, C.c_int, C.c_int, C.c_int,
+                                C.c_int)
+        self._argmax_rows = sig("argmax_rows", None, _i32p, _f32p, C.c_int, C.c_long, C.c_int)
+        self._forward_seq = sig("forward_seq", C.c_int, C.c_void_p, _f32p, _i32p, C.c_int, _f32p)
+        self._max_threads = sig("max_threads", C.c_int)
+
+    # -- single-row primitives ------------------------------------------------
+    def max_threads(self) -> int:
+        return int(self._max_threads())
+
+    def rmsnorm(self, x, gain):
+        x = np.ascontiguousarray(x, np.float32)
+        out = np.empty_like(x)
+        self._rmsnorm(out, x, np.ascontiguousarray(gain, np.float32), x.size)
+        return out
+
+    def softmax(self, x):
+        x = np.array(x, np.float32, copy=True)
+        self._softmax(x, x.size)
+        return x
+
+    def topk(self, scores, k):
+        scores = np.array(scores, np.float32, copy=True)
+        v = np.empty(k, np.float32)
+        i = np.empty(k, np.int32)
+        self._topk(v, i, scores, scores.size, k)
+        return v, i
+
+    def yarn_inv_freq(self, theta=150000.0, head_dim=64, factor=32.0, orig_ctx=4096.0,
+                      beta_fast=32.0, beta_slow=1.0):
+        conc = C.c_float()
+        inv = np.empty(head_dim // 2, np.float32)
+        self._inv_freq(theta, head_dim, factor, orig_ctx, beta_fast, beta_slow, C.byref(conc), inv)
+        return float(conc.value), inv
+
+    def yarn_cos_sin(self, pos, theta=150000.0, head_dim=64, factor=32.0, orig_ctx=4096.0,
+                     beta_fast=32.0, beta_slow=1.0):
+        c = np.empty(head_dim // 2, np.float32)
+        s = np.empty(head_dim // 2, np.float32)
+        self._cos_sin(pos, theta, head_dim, factor, orig_ctx, beta_fast, beta_slow, c, s)
+        return c, s
+
+    def rotate_heads(self, x, cos_row, sin_row, n_heads, head_dim):
+        x = np.array(x, np.float32, copy=True)
+        self._rotate(x, np.ascontiguousarray(cos_row, np.float32),
+                     np.ascontiguousarray(sin_row, np.float32), n_heads, head_dim)
+        return x
+
+    def argmax(self, p):
+        p = np.ascontiguousarray(p, np.float32)
+        return int(self._argmax(p, p.size))
+
+    # -- row-batched forms ------------------------------------------------------
+    def add_rmsnorm_rows(self, x, delta, gain, threads=1, inplace_norm=False):
+        """Returns (x_after_add, normed).  delta may be None (norm only)."""
+        x = np.array(x, np.float32, copy=True)
+        T, H = x.shape
+        d = None if delta is None else np.ascontiguousarray(delta, np.float32)
+        normed = x if inplace_norm else np.empty_like(x)
+        self._add_rmsnorm_rows(x, _addr(d), np.ascontiguousarray(gain, np.float32), normed, T, H, threads)
+        return x, normed
+
+    def bias_rope_rows(self, qkv, bias, pos, n_q=64, n_kv=8, head_dim=64, theta=150000.0,
+                       factor=32.0, orig_ctx=4096.0, beta_fast=32.0, beta_slow=1.0, threads=1):
+        qkv = np.array(qkv, np.float32, copy=True)
+        b = None if bias is None else np.ascontiguousarray(bias, np.float32)
+        pos = np.ascontiguousarray(pos, np.int32)
+        self._bias_rope_rows(qkv, _addr(b), pos, qkv.shape[0], n_q, n_kv, head_dim, theta, factor,
+                             orig_ctx, beta_fast, beta_slow, threads)
+        return qkv
+
+    def router_rows(self, scores, k=4, threads=1):
+        scores = np.array(scores, np.float32, copy=True)
+        T, E = scores.shape
+        w = np.empty((T, k), np.float32)
+        e = np.empty((T, k), np.int32)
+        self._router_rows(w, e, scores, T, E, k, threads)
+        return w, e
+
+    def argmax_rows(self, logits, threads=1):
+        logits = np.ascontiguousarray(logits, np.float32)
+        T, V = logits.shape
+        out = np.empty(T, np.int32)
+        self._argmax_rows(out, logits, T, V, threads)
+        return out
+
+    def forward_seq(self, cfg: OrcConfig, flat_weights, tokens):
+        flat_weights = np.ascontiguousarray(flat_weights, np.float32)
+        assert flat_weights.size == flat_weight_count(cfg)
+        tokens = np.ascontiguousarray(tokens, np.int32)
+        out = np.empty((tokens.size, cfg.vocab), np.float32)
+        rc = self._forward_seq(C.addressof(cfg), flat_weights, tokens, tokens.size, out)
+        assert rc == 0
+        return out
+
+
+class Oracle(_Lib):
+    """The restated CPU oracle, plus the row loops that only it has."""
+
+    def __init__(self):
+        super().__init__(ORACLE_SO, "orc_")
+        L = self.lib
+        L.orc_embed_rows.restype = None
+        L.orc_embed_rows.argtypes = [_f32p, _f32p, _i32p, C.c_int, C.c_int, C.c_int]
+        L.orc_swiglu_rows.restype = None
+        L.orc_swiglu_rows.argtypes = [_f32p, _f32p, C.c_long, C.c_int, C.c_float, C.c_int]
+        L.orc_combine_rows.restype = None
+        L.orc_combine_rows.argtypes = [_f32p, _f32p, _i32p, _f32p, _i32p, C.c_int, C.c_int, C.c_int,
+                                       C.c_int, C.c_int]
+        L.orc_bias_rope_rows_table.restype = None
+        L.orc_bias_rope_rows_table.argtypes = [_f32p, _opt, _i32p, C.c_int, C.c_int, C.c_int, C.c_int,
+                                               _f32p, _f32p, C.c_int]
+        L.orc_yarn_table.restype = None
+        L.orc_yarn_table.argtypes = [_f32p, _f32p, C.c_int, C.c_float, C.c_int, C.c_float, C.c_float,
+                                     C.c_float, C.c_float, C.c_int]
+        L.orc_expf_array.restype = None
+        L.orc_expf_array.argtypes = [_f32p, _f32p, C.c_long]
+
+    def embed_rows(self, table, ids, threads=1):
+        table = np.ascontiguousarray(table, np.float32)
+        ids = np.ascontiguousarray(ids, np.int32)
+        out = np.empty((ids.size, table.shape[1]), np.float32)
+        self.lib.orc_embed_rows(out, table, ids, ids.size, table.shape[1], threads)
+        return out
+
+    def swiglu_rows(self, gate_up, limit=7.0, threads=1):
+        gate_up = np.ascontiguousarray(gate_up, np.float32)
+        R, two_i = gate_up.shape
+        out = np.empty((R, two_i // 2), np.float32)
+        self.lib.orc_swiglu_rows(out, gate_up, R, two_i // 2, limit, threads)
+        return out
+
+    def combine_rows(self, x, Z, row_of, weights, experts, n_experts, threads=1):
+        x = np.array(x, np.float32, copy=True)
+        T, H = x.shape
+        k = weights.shape[1]
+        self.lib.orc_combine_rows(x, np.ascontiguousarray(Z, np.float32),
+                                  np.ascontiguousarray(row_of, np.int32),
+                                  np.ascontiguousarray(weights, np.float32),
+                                  np.ascontiguousarray(experts, np.int32), T, k, H, n_experts, threads)
+        return x
+
+    def bias_rope_rows_table(self, qkv, bias, pos, cos_tab, sin_tab, n_q=64, n_kv=8, head_dim=64,
+                             threads=1):
+        qkv = np.array(qkv, np.float32, copy=True)
+        b = None if bias is None else np.ascontiguousarray(bias, np.float32)
+        self.lib.orc_bias_rope_rows_table(qkv, _addr(b), np.ascontiguousarray(pos, np.int32),
+                                          qkv.shape[0], n_q, n_kv, head_dim,
+                                          np.ascontiguousarray(cos_tab, np.float32),
+                                          np.ascontiguousarray(sin_tab, np.float32), threads)
+        return qkv
+
+    def yarn_table(self, n_pos, theta=150000.0, head_dim=64, factor=32.0, orig_ctx=4096.0,
+                   beta_fast=32.0, beta_slow=1.0, threads=0):
+        c = np.empty((n_pos, head_dim // 2), np.float32)
+        s = np.empty((n_pos, head_dim // 2), np.float32)
+        self.lib.orc_yarn_table(c, s, n_pos, theta, head_dim, factor, orig_ctx, beta_fast, beta_slow,
+                                threads)
+        return c, s
+
+    def expf(self, x):
+        x = np.ascontiguousarray(x, np.float32)
+        out = np.empty_like(x)
+        self.lib.orc_expf_array(out, x, x.size)
+        return out
+
+
+class Reference(_Lib):
+    """The reference's own compiled CPU functions (present only when built)."""
+
+    def __init__(self):
+        super().__init__(REF_SO, "ref_")
+        assert self.lib.ref_config_size() == C.sizeof(OrcConfig)
+
+
+def have_reference() -> bool:
+    return os.path.exists(REF_SO)

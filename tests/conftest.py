@@ -1,0 +1,84 @@
+"""Shared fixtures.  Tests marked ``gpu`` need a CUDA device and the built library; the
+rest run on a CPU-only box (oracle vs golden vectors, host logic, ABI surface)."""
+from __future__ import annotations
+
+import importlib
+import os
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests", "golden"))
+
+PKG_NAME = "optimize_inference_gpt-oss_b200"
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box)")
+
+
+@pytest.fixture(scope="session")
+def pkg():
+    """The ctypes binding; building the library first if nvcc is around and it is stale."""
+    mod = importlib.import_module(PKG_NAME)
+    if not os.path.exists(mod.LIB_PATH):
+        build = importlib.import_module(PKG_NAME + ".build")
+        build.build()
+    mod.load()
+    return mod
+
+
+@pytest.fixture(scope="session")
+def orc():
+    import oracle
+    if not os.path.exists(oracle.ORACLE_SO):
+        oracle.build(ref=None)
+    return oracle.Oracle()
+
+
+@pytest.fixture(scope="session")
+def ref():
+    """The reference's own compiled CPU functions; skipped where never built."""
+    import oracle
+    if not oracle.have_reference():
+        if os.path.exists(os.path.join(oracle.REFERENCE_CHECKOUT, "run.cpp")):
+            oracle.build(ref=True)
+        else:
+            pytest.skip("oracle/_ref/libgptoss_ref.so not built and no reference checkout here")
+    return oracle.Reference()
+
+
+@pytest.fixture(scope="session")
+def golden():
+    return np.load(os.path.join(ROOT, "tests", "golden", "golden.npz"))
+
+
+@pytest.fixture(scope="session")
+def gpu(pkg):
+    """Selects device 0; fails (does not skip) when a gpu-marked test finds no device."""
+    n = pkg.device_count()
+    assert n > 0, "gpu-marked test without a CUDA device"
+    pkg.set_device(0)
+    return pkg
+
+
+def bits(a):
+    a = np.ascontiguousarray(a)
+    return a.view({4: np.uint32, 2: np.uint16, 8: np.uint64}[a.dtype.itemsize])
+
+
+def assert_bit_equal(a, b, what=""):
+    a, b = np.ascontiguousarray(a), np.ascontiguousarray(b)
+    assert a.shape == b.shape, (what, a.shape, b.shape)
+    ne = bits(a) != bits(b)
+    assert not ne.any(), f"{what}: {int(ne.sum())} of {ne.size} elements differ; first at {np.argwhere(ne)[0]}"
+
+
+def rel_err(got, want, floor):
+    """max |got - want| / max(|want|, floor)."""
+    got = np.asarray(got, np.float64)
+    want = np.asarray(want, np.float64)
+    return float(np.max(np.abs(got - want) / np.maximum(np.abs(want), floor))) if got.size else 0.0

@@ -1,0 +1,116 @@
+"""Inputs of the golden known-answer cases.
+
+Every input is derived from integer hashing and IEEE division only, so the same bits
+come out on any machine and numpy version; the fixture files then only need to hold the
+expected OUTPUTS, which ``make_golden.py`` obtained from the reference's own compiled
+CPU functions.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+_M = np.uint64(0xFFFFFFFFFFFFFFFF)
+
+
+def splitmix64(x: np.ndarray) -> np.ndarray:
+    with np.errstate(over="ignore"):
+        z = (x.astype(np.uint64) + np.uint64(0x9E3779B97F4A7C15)) & _M
+        z = ((z ^ (z >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)) & _M
+        z = ((z ^ (z >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)) & _M
+        return z ^ (z >> np.uint64(31))
+
+
+def hashed(seed: int, n: int) -> np.ndarray:
+    with np.errstate(over="ignore"):
+        base = splitmix64(np.array([seed], np.uint64))[0]
+        return splitmix64(np.arange(n, dtype=np.uint64) * np.uint64(0xD1342543DE82EF95) + base)
+
+
+def uniform(seed: int, shape, scale: float = 1.0, levels: int = 200001) -> np.ndarray:
+    """fp32 values on a grid of `levels` points spanning [-scale, scale]."""
+    n = int(np.prod(shape))
+    h = hashed(seed, n) % np.uint64(levels)
+    half = (levels - 1) // 2
+    v = (h.astype(np.int64) - half).astype(np.float64) * (scale / half)
+    return v.astype(np.float32).reshape(shape)
+
+
+def small_ints(seed: int, shape, lo: int, hi: int) -> np.ndarray:
+    n = int(np.prod(shape))
+    return (lo + (hashed(seed, n) % np.uint64(hi - lo)).astype(np.int64)).astype(np.int32).reshape(shape)
+
+
+def coarse(seed: int, shape, step: float = 0.125, span: int = 128) -> np.ndarray:
+    """Multiples of `step` in [-span*step, span*step): few distinct values, so ties abound
+    and every value is exact in bf16."""
+    n = int(np.prod(shape))
+    h = hashed(seed, n) % np.uint64(2 * span)
+    return ((h.astype(np.int64) - span).astype(np.float32) * np.float32(step)).reshape(shape)
+
+
+# ---- the cases --------------------------------------------------------------------
+
+H, QKV, E20, E120, V = 2880, 5120, 32, 128, 201088
+
+
+def case_rmsnorm():
+    x = uniform(11, (4, H), 3.0)
+    delta = uniform(12, (4, H), 1.0)
+    gain = (1.0 + uniform(13, (H,), 0.3)).astype(np.float32)
+    return x, delta, gain
+
+
+def case_rope():
+    qkv = uniform(21, (4, QKV), 2.0)
+    bias = uniform(22, (QKV,), 0.05)
+    pos = np.array([0, 37, 1023, 4095], np.int32)
+    return qkv, bias, pos
+
+
+def case_router():
+    a = uniform(31, (48, E20), 2.0)
+    b = uniform(32, (16, E120), 2.0)
+    for s in (a, b):  # planted ties, signed zeros, many-equal rows
+        T, E = s.shape
+        for t in range(T):
+            if t % 3 == 0:
+                s[t, E - 1] = s[t, (7 * t) % (E - 1)]
+            if t % 5 == 0:
+                s[t, 1], s[t, E // 2] = 0.0, -0.0
+                s[t, 0] = s[t, E - 2] = 50.0
+            if t % 7 == 0:
+                s[t] = np.trunc(s[t] * 2)
+    return a, b
+
+
+def case_swiglu():
+    y = uniform(41, (4, 2 * H), 12.0)  # beyond the clamp at 7 on both sides
+    y[0, :8] = [7.0, 7.0, -7.0, -7.0, 7.5, -7.5, 0.0, -0.0]
+    return y
+
+
+def case_combine():
+    T, k = 6, 4
+    x = uniform(51, (T, H), 2.0)
+    Z = uniform(52, (T * k, H), 1.5)
+    w = np.abs(uniform(53, (T, k), 1.0)) + np.float32(0.01)
+    w = (w / w.sum(axis=1, keepdims=True)).astype(np.float32)
+    e = np.stack([np.argsort(hashed(60 + t, E20))[:k] for t in range(T)]).astype(np.int32)
+    row_of = np.argsort(hashed(54, T * k)).astype(np.int32).reshape(T, k)  # a permutation
+    return x, Z, row_of, w, e
+
+
+def case_argmax():
+    lg = coarse(61, (3, V))
+    lg[1, 777] = lg[1, 150000] = 99.0   # planted tie across far-apart columns
+    lg[2, :] = 0.0                      # all equal: column 0
+    lg[2, 5] = -0.0
+    return lg
+
+
+def tiny_model():
+    """A 2-layer model small enough for the CPU forward pass (field order of run.cpp's Config)."""
+    cfg = dict(vocab=97, hidden=64, n_experts=8, top_k=4, inter=48, n_layers=2, head_dim=64,
+               n_q_heads=4, n_kv_heads=2, seq_len=16, orig_ctx=4096, theta=150000.0, factor=32.0,
+               window=4, limit=7.0)
+    return cfg

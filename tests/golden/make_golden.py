@@ -1,0 +1,75 @@
+"""Regenerates tests/golden/golden.npz.
+
+Run where the reference checkout is available (it builds oracle/_ref/libgptoss_ref.so
+from the reference's own run.cpp and calls the reference's functions):
+
+    python tests/golden/make_golden.py
+
+Inputs come from golden_inputs.py (integer hashing, reproducible anywhere); the file
+stores the expected outputs:
+
+  * rmsnorm / add, rope (bias + per-token YaRN cos/sin + rotation), router top-4 + softmax,
+    argmax, YaRN anchors: produced by the REFERENCE's compiled functions;
+  * logits of a tiny 2-layer model over 10 decode steps: the REFERENCE's forward(), which
+    is what pins the loops that only exist inline in it (bias add, SwiGLU, expert combine,
+    residual);
+  * SwiGLU rows and combine rows: produced by the restated oracle (the reference has no
+    callable form of those loops); they are regression vectors for the oracle, whose
+    agreement with forward() is checked separately.
+"""
+from __future__ import annotations
+
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+import golden_inputs as gi  # noqa: E402
+import oracle  # noqa: E402
+
+
+def main():
+    oracle.build(ref=True)
+    ref, orc = oracle.Reference(), oracle.Oracle()
+    out = {}
+
+    x, delta, gain = gi.case_rmsnorm()
+    xa, normed = ref.add_rmsnorm_rows(x, delta, gain)
+    out["rmsnorm_x"], out["rmsnorm_out"] = xa, normed
+    out["rmsnorm_only"] = ref.add_rmsnorm_rows(x, None, gain)[1]
+
+    qkv, bias, pos = gi.case_rope()
+    out["rope_out"] = ref.bias_rope_rows(qkv, bias, pos)
+    conc, inv = ref.yarn_inv_freq()
+    out["yarn_conc"], out["yarn_inv_freq"] = np.float32(conc), inv
+    cs = [ref.yarn_cos_sin(int(p)) for p in pos]
+    out["yarn_cos"] = np.stack([c for c, _ in cs])
+    out["yarn_sin"] = np.stack([s for _, s in cs])
+
+    a, b = gi.case_router()
+    out["router20_w"], out["router20_e"] = ref.router_rows(a)
+    out["router120_w"], out["router120_e"] = ref.router_rows(b)
+
+    out["argmax"] = ref.argmax_rows(gi.case_argmax())
+
+    m = gi.tiny_model()
+    cfg = oracle.OrcConfig(*m.values())
+    w = gi.uniform(71, (oracle.flat_weight_count(cfg),), 0.35)
+    toks = gi.small_ints(72, (10,), 0, m["vocab"])
+    out["forward_logits"] = ref.forward_seq(cfg, w, toks)
+
+    out["swiglu_out"] = orc.swiglu_rows(gi.case_swiglu())
+    xc, Z, row_of, wt, e = gi.case_combine()
+    out["combine_x"] = orc.combine_rows(xc, Z, row_of, wt, e, gi.E20)
+
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden.npz")
+    np.savez_compressed(path, **out)
+    print(path, os.path.getsize(path), "bytes;", ", ".join(f"{k}{list(np.shape(v))}" for k, v in out.items()))
+
+
+if __name__ == "__main__":
+    main()

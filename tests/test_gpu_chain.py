@@ -1,0 +1,158 @@
+"""The C++ layer-chain driver against the oracle's ops strung together in the same order
+(embedding -> per layer: bias+RoPE, add+norm, top-4, SwiGLU, combine+next norm -> argmax),
+in fp32 mode and in bf16-activation mode, at a small size and at the full depth and width
+of the gpt-oss-20b decode shard (24 layers, 512 tokens per GPU)."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+
+from gpu_util import TOL_BF16, TOL_F32, n_bit_diff, rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+def _np_dtype(pkg, dt):
+    return np.float32 if dt == pkg.F32 else np.uint16
+
+
+def _as_f32(pkg, a, dt):
+    return a if dt == pkg.F32 else pkg.from_bf16_bits(a).reshape(a.shape)
+
+
+def _fetch_inputs(pkg, ch, T, n_sets):
+    """Downloads weights and stand-ins back from the chain (as the fp32 values the kernels see)."""
+    c, dt = ch.cfg, ch.cfg.act_dtype
+    nd = _np_dtype(pkg, dt)
+    K, H, QKV, E, I = c.top_k, c.hidden, c.qkv_dim, c.n_experts, c.inter
+    got = {
+        "emb": _as_f32(pkg, ch.download(pkg.BUF_EMBEDDING, 0, nd, (c.vocab, H)), dt),
+        "gain_attn": [ch.download(pkg.BUF_GAIN_ATTN, l, np.float32, (H,)) for l in range(c.n_layers)],
+        "gain_ffn": [ch.download(pkg.BUF_GAIN_FFN, l, np.float32, (H,)) for l in range(c.n_layers)],
+        "gain_out": ch.download(pkg.BUF_GAIN_OUT, 0, np.float32, (H,)),
+        "bias": [ch.download(pkg.BUF_QKV_BIAS, l, np.float32, (QKV,)) for l in range(c.n_layers)],
+        "cos": ch.download(pkg.BUF_COS, 0, np.float32, (c.max_pos, c.head_dim // 2)),
+        "sin": ch.download(pkg.BUF_SIN, 0, np.float32, (c.max_pos, c.head_dim // 2)),
+        "logits": _as_f32(pkg, ch.download(pkg.BUF_LOGITS, 0, nd, (T, c.vocab)), dt),
+    }
+    for name, which, shape in (("proj", pkg.BUF_ATTN_PROJ, (T, H)), ("qkv", pkg.BUF_QKV, (T, QKV)),
+                               ("router", pkg.BUF_ROUTER, (T, E)), ("mlp1", pkg.BUF_MLP1, (K * T, 2 * I)),
+                               ("expert", pkg.BUF_EXPERT, (K * T, H))):
+        got[name] = [_as_f32(pkg, ch.download(which, s, nd, shape), dt) for s in range(n_sets)]
+    return got
+
+
+def _oracle_chain(orc, c, inp, tokens, pos, n_sets):
+    T, K = tokens.size, c.top_k
+    ident = np.arange(T * K, dtype=np.int32).reshape(T, K)
+    x = orc.embed_rows(inp["emb"], tokens, threads=0)
+    normed = orc.add_rmsnorm_rows(x, None, inp["gain_attn"][0], threads=0)[1]
+    first_normed = normed
+    for l in range(c.n_layers):
+        s = l % n_sets
+        qkv_out = orc.bias_rope_rows_table(inp["qkv"][s], inp["bias"][l], pos, inp["cos"], inp["sin"],
+                                           c.n_q_heads, c.n_kv_heads, c.head_dim, threads=0)
+        x, normed = orc.add_rmsnorm_rows(x, inp["proj"][s], inp["gain_ffn"][l], threads=0)
+        w, e = orc.router_rows(inp["router"][s], K, threads=0)
+        act = orc.swiglu_rows(inp["mlp1"][s], c.swiglu_limit, threads=0)
+        x = orc.combine_rows(x, inp["expert"][s], ident, w, e, c.n_experts, threads=0)
+        gain = inp["gain_attn"][l + 1] if l + 1 < c.n_layers else inp["gain_out"]
+        normed = orc.add_rmsnorm_rows(x, None, gain, threads=0)[1]
+    nxt = orc.argmax_rows(inp["logits"], threads=0)
+    return dict(x=x, normed=normed, qkv_out=qkv_out, w=w, e=e, act=act, next=nxt, first_normed=first_normed)
+
+
+def _run_and_compare(pkg, orc, c, T, n_sets, tol, seed):
+    ch = pkg.Chain(c, T, n_sets)
+    try:
+        ch.fill_synthetic(T, seed=seed)
+        tokens = pkg.synth_uniform_int(T, seed, 1000, 0, c.vocab)
+        pos = pkg.synth_uniform_int(T, seed, 1001, 0, c.max_pos)
+        nxt = np.full(T, -7, np.int32)
+        ch.step(tokens, pos, nxt)
+        want = _oracle_chain(orc, c, _fetch_inputs(pkg, ch, T, n_sets), tokens, pos, n_sets)
+        dt, nd = c.act_dtype, _np_dtype(pkg, c.act_dtype)
+        K, H = c.top_k, c.hidden
+        got_x = ch.download(pkg.BUF_X, 0, np.float32, (T, H))
+        got_e = ch.download(pkg.BUF_TOPK_E, 0, np.int32, (T, K))
+        got_w = ch.download(pkg.BUF_TOPK_W, 0, np.float32, (T, K))
+        got_n = _as_f32(pkg, ch.download(pkg.BUF_NORMED, 0, nd, (T, H)), dt)
+        got_q = _as_f32(pkg, ch.download(pkg.BUF_QKV_OUT, 0, nd, (T, c.qkv_dim)), dt)
+        got_a = _as_f32(pkg, ch.download(pkg.BUF_SWIGLU, 0, nd, (K * T, c.inter)), dt)
+        assert np.array_equal(nxt, want["next"]), "picked tokens"
+        assert np.array_equal(ch.download(pkg.BUF_NEXT, 0, np.int32, (T,)), want["next"])
+        assert np.array_equal(got_e, want["e"]), "expert indices of the last layer"
+        assert n_bit_diff(got_w, want["w"]) == 0
+        assert rel_err(got_x, want["x"]) <= (TOL_F32 if dt == pkg.F32 else 10 * TOL_F32), "residual stream"
+        assert rel_err(got_n, want["normed"]) <= tol
+        assert rel_err(got_q, want["qkv_out"]) <= tol
+        assert rel_err(got_a, want["act"]) <= tol
+        # the same step, replayed from the captured graph and kernel by kernel
+        nxt2 = np.empty(T, np.int32)
+        ch.step(tokens, pos, nxt2)
+        assert np.array_equal(nxt2, nxt)
+        assert n_bit_diff(ch.download(pkg.BUF_X, 0, np.float32, (T, H)), got_x) == 0
+        ch.enqueue(T, use_graph=False)
+        assert n_bit_diff(ch.download(pkg.BUF_X, 0, np.float32, (T, H)), got_x) == 0
+        assert ch.launches_per_step(T) in (2 + 5 * c.n_layers + 1, 2 + 5 * c.n_layers + 2)
+        prof = ch.profile(T, 1)
+        assert prof["swiglu"][1] == c.n_layers and prof["embed"][1] == 1 and prof["argmax"][0] > 0
+        return got_x, want
+    finally:
+        ch.close()
+
+
+def _small_config(pkg, dt):
+    c = pkg.chain_config(20, dt, max_pos=4096)
+    c.n_layers, c.vocab = 3, 5000
+    return c
+
+
+def test_chain_fp32_mode_small(gpu, orc):
+    """Config 0's shapes (T = 64, fp32 everywhere, CPU rounding order): tokens and expert
+    indices exact, floats within 1e-5."""
+    pkg = gpu
+    c = _small_config(pkg, pkg.F32)
+    assert c.flags & pkg.EXACT
+    got_x, want = _run_and_compare(pkg, orc, c, 64, 3, TOL_F32, seed=11)
+    assert n_bit_diff(got_x, want["x"]) <= got_x.size // 1000
+
+
+def test_chain_bf16_mode_small(gpu, orc):
+    pkg = gpu
+    _run_and_compare(pkg, orc, _small_config(pkg, pkg.BF16), 64, 3, TOL_BF16, seed=12)
+
+
+def test_chain_120b_router_width(gpu, orc):
+    pkg = gpu
+    c = pkg.chain_config(120, pkg.BF16, max_pos=4096)
+    assert c.n_experts == 128 and c.n_layers == 36
+    c.n_layers, c.vocab = 2, 3000
+    _run_and_compare(pkg, orc, c, 33, 2, TOL_BF16, seed=13)
+
+
+def test_chain_full_depth_decode_shard(gpu, orc):
+    """gpt-oss-20b decode, one GPU's shard: 24 layers, 512 tokens, full vocabulary, bf16
+    activations, positions uniform in [0, 4096).  Two stand-in sets keep the host side of
+    the check to a few seconds; every layer still runs."""
+    pkg = gpu
+    c = pkg.chain_config(20, pkg.BF16, max_pos=4096)
+    assert (c.n_layers, c.n_experts, c.hidden, c.vocab) == (24, 32, 2880, 201088)
+    _run_and_compare(pkg, orc, c, 512, 2, TOL_BF16, seed=14)
+
+
+def test_chain_rejects_bad_sizes(gpu):
+    pkg = gpu
+    c = _small_config(pkg, pkg.BF16)
+    ch = pkg.Chain(c, 8, 1)
+    try:
+        with pytest.raises(pkg.GptossError):
+            ch.enqueue(9)
+        with pytest.raises(pkg.GptossError):
+            ch.fill_synthetic(0)
+        ch.enqueue(0)
+    finally:
+        ch.close()
+    c.top_k = 9
+    with pytest.raises(pkg.GptossError):
+        pkg.Chain(c, 8, 1)

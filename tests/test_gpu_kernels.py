@@ -1,0 +1,447 @@
+"""Parity of every CUDA kernel, called through the C ABI, with the CPU oracle on the same
+seeded inputs.  Integer outputs (embedding rows, expert indices, token ids) must match
+bit for bit; float outputs within 1e-5 (fp32 mode) / 2e-2 (bf16 mode) relative -- and in
+fp32 mode the kernels that follow the CPU's rounding sequence are also required to be
+bit-identical.  Shapes include the odd ones the reference tests use (H 64/1000/4096,
+head mixes 8+1 / 32+4, k 2..8, E 16..200) and every output buffer sits between canaries."""
+from __future__ import annotations
+
+import zlib
+
+import numpy as np
+import pytest
+
+import golden_inputs as gi
+from gpu_util import Dev, TOL_BF16, TOL_F32, n_bit_diff, rel_err, widen
+
+pytestmark = pytest.mark.gpu
+
+H, QKV, V = 2880, 5120, 201088
+
+
+def rng_of(*key):
+    """A generator seeded by the case's name and shape (stable across processes)."""
+    return np.random.default_rng(zlib.crc32(repr(key).encode()))
+
+
+# ---- a1: embedding gather -----------------------------------------------------------
+
+@pytest.mark.parametrize("T", [1, 7, 64, 8192])
+@pytest.mark.parametrize("Hd", [2880, 64, 1000, 77])
+def test_embed_bf16_table(gpu, orc, T, Hd):
+    pkg, d = gpu, Dev(gpu)
+    Vs = 5003
+    r = rng_of("embed", T, Hd)
+    table_bits = pkg.to_bf16_bits((0.02 * r.standard_normal((Vs, Hd))).astype(np.float32))
+    table_bits[17, :4] = [0x7FC1, 0xFF80, 0x8000, 0x0001]  # NaN payload, -inf, -0, denormal
+    ids = r.integers(0, Vs, T).astype(np.int32)
+    ids[0] = 17
+    want = orc.embed_rows(pkg.from_bf16_bits(table_bits).reshape(Vs, Hd), ids)
+    tb, ib = d.put(table_bits), d.put(ids)
+    x32, x16 = d.out((T, Hd), pkg.F32), d.out((T, Hd), pkg.BF16)
+    pkg.embed(T, tb, pkg.BF16, Vs, ib, x32, pkg.F32, Hd)
+    pkg.embed(T, tb, pkg.BF16, Vs, ib, x16, pkg.BF16, Hd)
+    assert n_bit_diff(x32.get(), want) == 0
+    assert np.array_equal(x16.get(as_f32=False), table_bits[ids])
+
+
+def test_embed_fp32_table_and_bad_ids(gpu, orc):
+    pkg, d = gpu, Dev(gpu)
+    r = rng_of("embed32")
+    table = (0.02 * r.standard_normal((999, H))).astype(np.float32)
+    ids = r.integers(0, 999, 64).astype(np.int32)
+    x = d.out((64, H), pkg.F32)
+    pkg.embed(64, d.put(table), pkg.F32, 999, d.put(ids), x, pkg.F32, H)
+    assert n_bit_diff(x.get(), orc.embed_rows(table, ids)) == 0
+    bad = ids.copy()
+    bad[3], bad[9] = -1, 999
+    pkg.embed(64, d.put(table), pkg.F32, 999, d.put(bad), x, pkg.F32, H)
+    got = x.get()
+    assert not got[3].any() and not got[9].any()
+    ok = np.ones(64, bool)
+    ok[[3, 9]] = False
+    assert n_bit_diff(got[ok], table[bad[ok]]) == 0
+
+
+# ---- a2: residual add + RMSNorm -----------------------------------------------------
+
+@pytest.mark.parametrize("T", [1, 7, 512])
+@pytest.mark.parametrize("Hd", [2880, 64, 1000, 4096, 8200, 77])
+def test_add_rmsnorm_fp32_mode(gpu, orc, T, Hd):
+    pkg, d = gpu, Dev(gpu)
+    r = rng_of("norm32", T, Hd)
+    x = r.standard_normal((T, Hd)).astype(np.float32)
+    y = r.standard_normal((T, Hd)).astype(np.float32)
+    w = (1 + 0.1 * r.standard_normal(Hd)).astype(np.float32)
+    want_x, want_o = orc.add_rmsnorm_rows(x, y, w)
+    xb, o = d.put_inout(x), d.out((T, Hd), pkg.F32)
+    pkg.add_rmsnorm(T, xb, d.put(y), pkg.F32, d.put(w), o, pkg.F32, Hd, flags=pkg.EXACT)
+    assert n_bit_diff(xb.get(), want_x) == 0, "x + y is a single fp32 add"
+    got = o.get()
+    assert rel_err(got, want_o) <= TOL_F32
+    # the double-precision sum is only reassociated; allow a stray last-bit difference
+    assert n_bit_diff(got, want_o) <= max(1, got.size // 1000)
+    # norm only, and in place as the final norm is (run.cpp:751)
+    o2 = d.out((T, Hd), pkg.F32)
+    pkg.add_rmsnorm(T, d.put(x), None, pkg.F32, d.put(w), o2, pkg.F32, Hd, flags=pkg.EXACT)
+    want_only = orc.add_rmsnorm_rows(x, None, w)[1]
+    assert rel_err(o2.get(), want_only) <= TOL_F32
+    xi = d.put_inout(x)
+    pkg.add_rmsnorm(T, xi, None, pkg.F32, d.put(w), xi, pkg.F32, Hd, flags=pkg.EXACT)
+    assert rel_err(xi.get(), want_only) <= TOL_F32
+
+
+@pytest.mark.parametrize("T", [1, 7, 512])
+@pytest.mark.parametrize("Hd", [2880, 64, 1000, 4096, 77])
+@pytest.mark.parametrize("ydt", ["bf16", "f32"])
+def test_add_rmsnorm_bf16_mode(gpu, orc, T, Hd, ydt):
+    """bf16 (or, as in the reference's fast path, fp32) delta in, bf16 normalised rows out."""
+    pkg, d = gpu, Dev(gpu)
+    ydt = pkg.BF16 if ydt == "bf16" else pkg.F32
+    r = rng_of("norm16", T, Hd)
+    x = r.standard_normal((T, Hd)).astype(np.float32)
+    y = widen(pkg, r.standard_normal((T, Hd)), ydt)
+    w = (1 + 0.1 * r.standard_normal(Hd)).astype(np.float32)
+    want_x, want_o = orc.add_rmsnorm_rows(x, y, w)
+    xb, o = d.put_inout(x), d.out((T, Hd), pkg.BF16)
+    pkg.add_rmsnorm(T, xb, d.put(y, ydt), ydt, d.put(w), o, pkg.BF16, Hd)
+    assert n_bit_diff(xb.get(), want_x) == 0
+    assert rel_err(o.get(), want_o) <= TOL_BF16
+    o2 = d.out((T, Hd), pkg.BF16)
+    pkg.add_rmsnorm(T, d.put(x), None, pkg.F32, d.put(w), o2, pkg.BF16, Hd)
+    assert rel_err(o2.get(), orc.add_rmsnorm_rows(x, None, w)[1]) <= TOL_BF16
+
+
+# ---- a3: qkv bias + YaRN RoPE ---------------------------------------------------------
+
+@pytest.mark.parametrize("T", [1, 37, 512])
+@pytest.mark.parametrize("heads", [(64, 8, 64), (8, 1, 64), (32, 4, 64), (4, 2, 128), (3, 1, 24)])
+def test_bias_rope_fp32_mode_is_bit_exact(gpu, orc, T, heads):
+    pkg, d = gpu, Dev(gpu)
+    nq, nkv, hd = heads
+    row, n_pos = (nq + 2 * nkv) * hd, 4096
+    r = rng_of("rope32", T, heads)
+    qkv = r.standard_normal((T, row)).astype(np.float32)
+    bias = (0.02 * r.standard_normal(row)).astype(np.float32)
+    pos = r.integers(0, n_pos, T).astype(np.int32)
+    pos[0] = n_pos - 1
+    ct, st = pkg.build_rope_tables(n_pos, head_dim=hd)
+    want = orc.bias_rope_rows_table(qkv, bias, pos, ct, st, nq, nkv, hd)
+    cb, sb = d.put(ct), d.put(st)
+    o = d.out((T, row), pkg.F32)
+    pkg.qkv_bias_rope(T, d.put(qkv), pkg.F32, row, d.put(bias), d.put(pos), 0, cb, sb, n_pos, nq, nkv, hd,
+                      o, pkg.F32, row, flags=pkg.EXACT)
+    assert n_bit_diff(o.get(), want) == 0
+    if hd == 64:  # the same answer as computing the angles per token the way forward() does
+        assert n_bit_diff(want, orc.bias_rope_rows(qkv, bias, pos, nq, nkv, hd)) == 0
+    # in place, no bias, one position for the whole batch (the engine's call shape)
+    qb = d.put_inout(qkv)
+    pkg.qkv_bias_rope(T, qb, pkg.F32, row, None, None, 517, cb, sb, n_pos, nq, nkv, hd, qb, pkg.F32, row,
+                      flags=pkg.EXACT)
+    want1 = orc.bias_rope_rows_table(qkv, None, np.full(T, 517, np.int32), ct, st, nq, nkv, hd)
+    assert n_bit_diff(qb.get(), want1) == 0
+    # contracted form (the reference's own GPU rounding): same values within fp32 noise
+    o3 = d.out((T, row), pkg.F32)
+    pkg.qkv_bias_rope(T, d.put(qkv), pkg.F32, row, d.put(bias), d.put(pos), 0, cb, sb, n_pos, nq, nkv, hd,
+                      o3, pkg.F32, row, flags=pkg.EXACT | pkg.FMA)
+    assert rel_err(o3.get(), want) <= TOL_F32
+
+
+def test_bias_rope_strided_rows_and_position_clamp(gpu, orc):
+    pkg, d = gpu, Dev(gpu)
+    T, nq, nkv, hd, n_pos = 9, 64, 8, 64, 128
+    row, stride_in, stride_out = QKV, QKV + 64, QKV + 16
+    r = rng_of("ropestride")
+    wide = r.standard_normal((T, stride_in)).astype(np.float32)
+    bias = (0.02 * r.standard_normal(row)).astype(np.float32)
+    pos = np.array([0, 5, 127, 128, 4000, -3, 64, 1, 2], np.int32)
+    ct, st = pkg.build_rope_tables(n_pos)
+    want = orc.bias_rope_rows_table(wide[:, :row], bias, np.clip(pos, 0, n_pos - 1), ct, st, nq, nkv, hd)
+    o = d.out((T, stride_out), pkg.F32)
+    pkg.qkv_bias_rope(T, d.put(wide), pkg.F32, stride_in, d.put(bias), d.put(pos), 0, d.put(ct), d.put(st),
+                      n_pos, nq, nkv, hd, o, pkg.F32, stride_out, flags=pkg.EXACT)
+    got = o.get()
+    assert n_bit_diff(got[:, :row], want) == 0
+    assert (got[:, row:].view(np.uint8) == 0x55).all(), "padding between rows must stay untouched"
+
+
+@pytest.mark.parametrize("T", [1, 37, 512])
+@pytest.mark.parametrize("heads", [(64, 8, 64), (8, 1, 64), (32, 4, 64)])
+def test_bias_rope_bf16_mode(gpu, orc, T, heads):
+    pkg, d = gpu, Dev(gpu)
+    nq, nkv, hd = heads
+    row, n_pos = (nq + 2 * nkv) * hd, 4096
+    r = rng_of("rope16", T, heads)
+    qkv = pkg.bf16_round(r.standard_normal((T, row)).astype(np.float32)).reshape(T, row)
+    bias = pkg.bf16_round((0.02 * r.standard_normal(row)).astype(np.float32))
+    pos = r.integers(0, n_pos, T).astype(np.int32)
+    ct, st = pkg.build_rope_tables(n_pos, head_dim=hd)
+    want = orc.bias_rope_rows_table(qkv, bias, pos, ct, st, nq, nkv, hd)
+    o = d.out((T, row), pkg.BF16)
+    pkg.qkv_bias_rope(T, d.put(qkv, pkg.BF16), pkg.BF16, row, d.put(bias), d.put(pos), 0, d.put(ct), d.put(st),
+                      n_pos, nq, nkv, hd, o, pkg.BF16, row)
+    assert rel_err(o.get(), want) <= TOL_BF16
+    # fp32 GEMM output in, bf16 out (the reference's fast-path dtypes)
+    o2 = d.out((T, row), pkg.BF16)
+    pkg.qkv_bias_rope(T, d.put(qkv), pkg.F32, row, d.put(bias), d.put(pos), 0, d.put(ct), d.put(st),
+                      n_pos, nq, nkv, hd, o2, pkg.BF16, row)
+    assert rel_err(o2.get(), want) <= TOL_BF16
+
+
+# ---- a4: router top-k + softmax ---------------------------------------------------------
+
+def _router_scores(r, T, E):
+    s = r.standard_normal((T, E)).astype(np.float32)
+    for t in range(T):  # the reference's planted cases: ties, signed zeros, many equal scores
+        if t % 3 == 0:
+            s[t, E - 1] = s[t, r.integers(0, E - 1)]
+        if t % 5 == 0:
+            s[t, 1], s[t, E // 2] = 0.0, -0.0
+            s[t, 0] = s[t, E - 2] = 50.0
+        if t % 7 == 0:
+            s[t] = np.trunc(s[t] * 2)
+    return s
+
+
+@pytest.mark.parametrize("T,E,k", [(512, 32, 4), (512, 128, 4), (512, 200, 4), (7, 32, 2), (7, 128, 2),
+                                   (33, 16, 8), (65, 256, 8), (1, 32, 4), (4096, 32, 4)])
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+def test_router_topk(gpu, orc, T, E, k, dt):
+    pkg, d = gpu, Dev(gpu)
+    dt = pkg.F32 if dt == "f32" else pkg.BF16
+    s = widen(pkg, _router_scores(rng_of("router", T, E, k), T, E), dt).reshape(T, E)
+    want_w, want_e = orc.router_rows(s, k)
+    wb, eb = d.out((T, k), pkg.F32), d.out((T, k), np.int32)
+    pkg.router_topk(T, d.put(s, dt), dt, E, k, wb, eb)
+    assert np.array_equal(eb.get(), want_e)
+    assert n_bit_diff(wb.get(), want_w) == 0, "softmax follows the CPU rounding sequence"
+    # finished rows and renumbering
+    done = np.zeros(T, np.int32)
+    done[::11] = 1
+    slot = ((np.arange(E) * 37 + 5) % E).astype(np.int32)
+    pkg.router_topk(T, d.put(s, dt), dt, E, k, wb, eb, done=d.put(done), slot_of=d.put(slot))
+    ge, gw = eb.get(), wb.get()
+    live = done == 0
+    assert (ge[~live] == -1).all() and (gw[~live] == 0).all()
+    assert np.array_equal(ge[live], slot[want_e[live]])
+    assert n_bit_diff(gw[live], want_w[live]) == 0
+
+
+# ---- a5: clamped SwiGLU -----------------------------------------------------------------
+
+@pytest.mark.parametrize("R,I", [(256, 2880), (1, 2880), (33, 1000), (5, 77), (2048, 2880)])
+def test_swiglu_fp32_mode_is_bit_exact(gpu, orc, R, I):
+    pkg, d = gpu, Dev(gpu)
+    y = (2.0 * rng_of("swiglu32", R, I).standard_normal((R, 2 * I))).astype(np.float32)
+    y[0, :8] = [7.0, 7.0, -7.0, -7.0, 7.5, -7.5, 0.0, -0.0]
+    y[0, 8:12] = [-60.0, 3.0, 1e30, -1e30]
+    g = d.out((R, I), pkg.F32)
+    pkg.swiglu(d.put(y), pkg.F32, g, pkg.F32, R, I, 7.0, flags=pkg.EXACT)
+    assert n_bit_diff(g.get(), orc.swiglu_rows(y)) == 0
+
+
+def test_device_expf_matches_libm_on_a_dense_sweep(gpu, orc):
+    """The SwiGLU gate path evaluates expf(-1.702 g): sweep g finely over the whole range
+    where the result is not saturated, plus huge magnitudes, and require identical bits."""
+    pkg, d = gpu, Dev(gpu)
+    g = np.concatenate([np.linspace(-70, 7.5, 1 << 20), -np.logspace(-30, 38, 4096),
+                        np.logspace(-40, 1, 4096)]).astype(np.float32)
+    y = np.zeros((1, 2 * g.size), np.float32)
+    y[0, 0::2] = g
+    out = d.out((1, g.size), pkg.F32)
+    pkg.swiglu(d.put(y), pkg.F32, out, pkg.F32, 1, g.size, 1e38, flags=pkg.EXACT)
+    assert n_bit_diff(out.get(), orc.swiglu_rows(y, limit=1e38)) == 0
+
+
+@pytest.mark.parametrize("R,I", [(256, 2880), (33, 1000), (5, 77)])
+@pytest.mark.parametrize("gdt", ["bf16", "f32"])
+def test_swiglu_bf16_mode(gpu, orc, R, I, gdt):
+    pkg, d = gpu, Dev(gpu)
+    gdt = pkg.BF16 if gdt == "bf16" else pkg.F32
+    y = pkg.bf16_round((2.0 * rng_of("swiglu16", R, I).standard_normal((R, 2 * I))).astype(np.float32)).reshape(R, 2 * I)
+    g = d.out((R, I), gdt)
+    pkg.swiglu(d.put(y, pkg.BF16), pkg.BF16, g, gdt, R, I, 7.0)
+    assert rel_err(g.get(), orc.swiglu_rows(y)) <= TOL_BF16
+
+
+def test_swiglu_unaligned_buffers_take_the_scalar_path(gpu, orc):
+    pkg, d = gpu, Dev(gpu)
+    R, I = 3, 1000
+    y = (2.0 * rng_of("swigluU").standard_normal((R, 2 * I))).astype(np.float32)
+    buf = d.put(np.concatenate([np.zeros(1, np.float32), y.ravel()]))  # payload starts 4 bytes in
+    g = d.out((R, I), pkg.F32)
+    pkg.swiglu(buf.ptr + 4, pkg.F32, g, pkg.F32, R, I, 7.0, flags=pkg.EXACT)
+    assert n_bit_diff(g.get(), orc.swiglu_rows(y)) == 0
+
+
+# ---- a6: weighted combine + residual (+ next norm) --------------------------------------
+
+def _routing(r, T, E, k, finished_every=0):
+    e = np.stack([r.permutation(E)[:k] for _ in range(T)]).astype(np.int32)
+    w = r.random((T, k)).astype(np.float32) + 0.01
+    w = (w / w.sum(1, keepdims=True)).astype(np.float32)
+    if finished_every:
+        e[::finished_every] = -1
+        w[::finished_every] = 0
+    return w, e
+
+
+@pytest.mark.parametrize("T,k,Hd", [(1, 4, 2880), (9, 4, 2880), (512, 4, 2880), (33, 2, 1000), (33, 6, 1000),
+                                    (33, 8, 4096), (5, 4, 77), (6, 4, 8200)])
+def test_combine_fp32_mode_is_bit_exact(gpu, orc, T, k, Hd):
+    pkg, d = gpu, Dev(gpu)
+    r = rng_of("comb32", T, k, Hd)
+    E = 32
+    x = r.standard_normal((T, Hd)).astype(np.float32)
+    Z = r.standard_normal((T * k, Hd)).astype(np.float32)
+    w, e = _routing(r, T, E, k, finished_every=5 if T > 5 else 0)
+    row_of = r.permutation(T * k).astype(np.int32).reshape(T, k)
+    want = orc.combine_rows(x, Z, row_of, w, e, E)
+    xb = d.put_inout(x)
+    pkg.moe_combine(T, xb, d.put(Z), pkg.F32, d.put(row_of), d.put(w), d.put(e), k, Hd, flags=pkg.EXACT)
+    assert n_bit_diff(xb.get(), want) == 0
+    # fused with the next norm == combine, then the norm
+    gain = (1 + 0.1 * r.standard_normal(Hd)).astype(np.float32)
+    xb2, o = d.put_inout(x), d.out((T, Hd), pkg.F32)
+    pkg.moe_combine(T, xb2, d.put(Z), pkg.F32, d.put(row_of), d.put(w), d.put(e), k, Hd, norm_w=d.put(gain),
+                    out=o, out_dtype=pkg.F32, flags=pkg.EXACT)
+    assert n_bit_diff(xb2.get(), want) == 0
+    assert rel_err(o.get(), orc.add_rmsnorm_rows(want, None, gain)[1]) <= TOL_F32
+    # identity row map; renumbered experts with phys_of restoring the order
+    want_id = orc.combine_rows(x, Z, np.arange(T * k, dtype=np.int32).reshape(T, k), w, e, E)
+    xb3 = d.put_inout(x)
+    pkg.moe_combine(T, xb3, d.put(Z), pkg.F32, None, d.put(w), d.put(e), k, Hd, flags=pkg.EXACT)
+    assert n_bit_diff(xb3.get(), want_id) == 0
+    slot = ((np.arange(E) * 37 + 5) % E).astype(np.int32)
+    phys = np.empty(E, np.int32)
+    phys[slot] = np.arange(E)
+    e_slot = np.where(e >= 0, slot[np.maximum(e, 0)], -1).astype(np.int32)
+    xb4 = d.put_inout(x)
+    pkg.moe_combine(T, xb4, d.put(Z), pkg.F32, None, d.put(w), d.put(e_slot), k, Hd, phys_of=d.put(phys),
+                    flags=pkg.EXACT)
+    assert n_bit_diff(xb4.get(), want_id) == 0
+    # contracted form: same within fp32 noise
+    xb5 = d.put_inout(x)
+    pkg.moe_combine(T, xb5, d.put(Z), pkg.F32, d.put(row_of), d.put(w), d.put(e), k, Hd, flags=pkg.EXACT | pkg.FMA)
+    assert rel_err(xb5.get(), want) <= TOL_F32
+
+
+@pytest.mark.parametrize("T,k,Hd", [(1, 4, 2880), (9, 4, 2880), (512, 4, 2880), (33, 2, 1000), (33, 8, 4096), (5, 4, 77)])
+@pytest.mark.parametrize("zdt", ["bf16", "f32"])
+def test_combine_bf16_mode(gpu, orc, T, k, Hd, zdt):
+    pkg, d = gpu, Dev(gpu)
+    zdt = pkg.BF16 if zdt == "bf16" else pkg.F32
+    r = rng_of("comb16", T, k, Hd)
+    E = 128
+    x = r.standard_normal((T, Hd)).astype(np.float32)
+    Z = widen(pkg, r.standard_normal((T * k, Hd)), zdt).reshape(T * k, Hd)
+    w, e = _routing(r, T, E, k, finished_every=4 if T > 4 else 0)
+    gain = (1 + 0.1 * r.standard_normal(Hd)).astype(np.float32)
+    want_x = orc.combine_rows(x, Z, np.arange(T * k, dtype=np.int32).reshape(T, k), w, e, E)
+    want_o = orc.add_rmsnorm_rows(want_x, None, gain)[1]
+    xb, o = d.put_inout(x), d.out((T, Hd), pkg.BF16)
+    pkg.moe_combine(T, xb, d.put(Z, zdt), zdt, None, d.put(w), d.put(e), k, Hd, norm_w=d.put(gain), out=o,
+                    out_dtype=pkg.BF16)
+    got_x = xb.get()
+    assert rel_err(got_x, want_x) <= TOL_F32 * 10  # fp32 math, only the summation order differs
+    assert rel_err(o.get(), want_o) <= TOL_BF16
+    dead = e[:, 0] < 0
+    assert n_bit_diff(got_x[dead], x[dead]) == 0, "finished rows keep x (and still get their norm)"
+    xb2 = d.put_inout(x)
+    pkg.moe_combine(T, xb2, d.put(Z, zdt), zdt, None, d.put(w), d.put(e), k, Hd)
+    assert n_bit_diff(xb2.get(), got_x) == 0, "with or without the fused norm, x is the same"
+
+
+# ---- a7: greedy argmax -------------------------------------------------------------------
+
+def _logits(r, T, Vv, dt, pkg):
+    lg = widen(pkg, 3.0 * r.standard_normal((T, Vv)), dt).reshape(T, Vv)
+    if T > 1 and Vv > 200:
+        lg[1, 77], lg[1, Vv - 3] = 99.0, 99.0     # tie far apart: lower column wins
+    if T > 2 and Vv > 200:
+        lg[2, 160], lg[2, 161] = 88.0, 88.0       # tie inside one 16-byte piece
+    if T > 3:
+        lg[3, :] = 0.0                            # all equal
+        lg[3, min(5, Vv - 1)] = -0.0
+    if T > 4:
+        lg[4, :] = -np.inf                        # nothing above -inf: index 0
+    if T > 5:
+        lg[5, 0] = np.nan                         # NaN in front sticks (run.cpp:781-783)
+    if T > 6:
+        lg[6, 1:Vv:3] = np.nan                    # NaNs elsewhere are never picked
+    if T > 7:
+        lg[7, :] = -5.0
+        lg[7, Vv - 1] = -4.0                      # the very last column
+    return lg
+
+
+@pytest.mark.parametrize("T,Vv", [(1, 201088), (33, 201088), (512, 201088), (9, 1000), (9, 50001), (9, 7), (200, 32000)])
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
+def test_argmax(gpu, orc, T, Vv, dt):
+    pkg, d = gpu, Dev(gpu)
+    dt = pkg.BF16 if dt == "bf16" else pkg.F32
+    if T == 512 and dt == pkg.F32:
+        pytest.skip("412 MB of host logits; the bf16 case covers the shape")
+    lg = _logits(rng_of("argmax", T, Vv), T, Vv, dt, pkg)
+    want = orc.argmax_rows(lg, threads=0)
+    lb = d.put(lg, dt)
+    keys = d.put(np.zeros(T, np.uint64))
+    out = d.out((T,), np.int32)
+    for rep in range(2):  # second run proves the keys were handed back zeroed
+        pkg.argmax(T, lb, dt, Vv, Vv, keys, out)
+        assert np.array_equal(out.get(), want), f"run {rep}"
+        assert not keys.numpy(np.uint64, T).any()
+    out2 = d.out((T,), np.int32)
+    pkg.argmax(T, lb, dt, Vv, Vv, None, out2)  # one block per row, no scratch
+    assert np.array_equal(out2.get(), want)
+
+
+def test_argmax_row_stride(gpu, orc):
+    pkg, d = gpu, Dev(gpu)
+    T, Vv, stride = 5, 1000, 1024
+    wide = (3.0 * rng_of("argstride").standard_normal((T, stride))).astype(np.float32)
+    wide[:, Vv:] = 1e9  # beyond V: must be ignored
+    out = d.out((T,), np.int32)
+    pkg.argmax(T, d.put(wide), pkg.F32, Vv, stride, d.put(np.zeros(T, np.uint64)), out)
+    assert np.array_equal(out.get(), orc.argmax_rows(np.ascontiguousarray(wide[:, :Vv])))
+
+
+# ---- golden vectors (produced by the reference's compiled CPU functions) -------------------
+
+def test_golden_vectors_through_the_gpu(gpu, golden):
+    pkg, d = gpu, Dev(gpu)
+    x, delta, gain = gi.case_rmsnorm()
+    xb, o = d.put_inout(x), d.out(x.shape, pkg.F32)
+    pkg.add_rmsnorm(4, xb, d.put(delta), pkg.F32, d.put(gain), o, pkg.F32, gi.H, flags=pkg.EXACT)
+    assert n_bit_diff(xb.get(), golden["rmsnorm_x"]) == 0
+    assert rel_err(o.get(), golden["rmsnorm_out"]) <= TOL_F32
+
+    qkv, bias, pos = gi.case_rope()
+    ct, st = pkg.build_rope_tables(4096)
+    o = d.out(qkv.shape, pkg.F32)
+    pkg.qkv_bias_rope(4, d.put(qkv), pkg.F32, gi.QKV, d.put(bias), d.put(pos), 0, d.put(ct), d.put(st), 4096,
+                      64, 8, 64, o, pkg.F32, gi.QKV, flags=pkg.EXACT)
+    assert n_bit_diff(o.get(), golden["rope_out"]) == 0
+
+    for s, tag in zip(gi.case_router(), ("router20", "router120")):
+        T, E = s.shape
+        wb, eb = d.out((T, 4), pkg.F32), d.out((T, 4), np.int32)
+        pkg.router_topk(T, d.put(s), pkg.F32, E, 4, wb, eb)
+        assert np.array_equal(eb.get(), golden[tag + "_e"])
+        assert n_bit_diff(wb.get(), golden[tag + "_w"]) == 0
+
+    y = gi.case_swiglu()
+    g = d.out((4, gi.H), pkg.F32)
+    pkg.swiglu(d.put(y), pkg.F32, g, pkg.F32, 4, gi.H, 7.0, flags=pkg.EXACT)
+    assert n_bit_diff(g.get(), golden["swiglu_out"]) == 0
+
+    xc, Z, row_of, w, e = gi.case_combine()
+    xb = d.put_inout(xc)
+    pkg.moe_combine(6, xb, d.put(Z), pkg.F32, d.put(row_of), d.put(w), d.put(e), 4, gi.H, flags=pkg.EXACT)
+    assert n_bit_diff(xb.get(), golden["combine_x"]) == 0
+
+    lg = gi.case_argmax()
+    for dt in (pkg.F32, pkg.BF16):  # the coarse grid is exact in bf16
+        out = d.out((3,), np.int32)
+        pkg.argmax(3, d.put(lg, dt), dt, gi.V, gi.V, d.put(np.zeros(3, np.uint64)), out)
+        assert np.array_equal(out.get(), golden["argmax"])

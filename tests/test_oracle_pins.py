@@ -1,0 +1,187 @@
+"""Pins the restated CPU oracle: (1) against the golden vectors the reference's compiled
+functions produced (always), (2) against the reference's functions themselves, bit for
+bit, on seeded inputs (where oracle/_ref/libgptoss_ref.so is present)."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+
+import golden_inputs as gi
+import oracle
+from conftest import assert_bit_equal
+
+
+# ---- (1) golden known answers -------------------------------------------------------
+
+def test_golden_rmsnorm(orc, golden):
+    x, delta, gain = gi.case_rmsnorm()
+    xa, normed = orc.add_rmsnorm_rows(x, delta, gain)
+    assert_bit_equal(xa, golden["rmsnorm_x"], "x after add")
+    assert_bit_equal(normed, golden["rmsnorm_out"], "normed")
+    assert_bit_equal(orc.add_rmsnorm_rows(x, None, gain)[1], golden["rmsnorm_only"], "norm only")
+
+
+def test_golden_yarn_and_rope(orc, golden):
+    conc, inv = orc.yarn_inv_freq()
+    assert np.float32(conc) == golden["yarn_conc"]
+    assert_bit_equal(inv, golden["yarn_inv_freq"], "inv_freq")
+    # anchors of the YaRN blend (gpt-oss parameters): concentration, the last
+    # pure-extrapolation pair (8) and the first pure-interpolation pair (18)
+    assert float(conc).hex() == "0x1.58b90c0000000p+0"
+    assert float(inv[0]) == 1.0
+    assert float(inv[8]).hex() == "0x1.a043280000000p-5"
+    assert float(inv[18]).hex() == "0x1.415b8c0000000p-15"
+    assert float(inv[31]).hex() == "0x1.44a5a60000000p-22"
+    qkv, bias, pos = gi.case_rope()
+    for i, p in enumerate(pos):
+        c, s = orc.yarn_cos_sin(int(p))
+        assert_bit_equal(c, golden["yarn_cos"][i], f"cos pos {p}")
+        assert_bit_equal(s, golden["yarn_sin"][i], f"sin pos {p}")
+    assert_bit_equal(orc.bias_rope_rows(qkv, bias, pos), golden["rope_out"], "rope")
+    # the table form (what the GPU engine uses) gives the same bits
+    ct, st = orc.yarn_table(4096)
+    assert_bit_equal(orc.bias_rope_rows_table(qkv, bias, pos, ct, st), golden["rope_out"], "rope via table")
+
+
+def test_golden_router(orc, golden):
+    a, b = gi.case_router()
+    w, e = orc.router_rows(a)
+    assert np.array_equal(e, golden["router20_e"])
+    assert_bit_equal(w, golden["router20_w"], "weights E=32")
+    w, e = orc.router_rows(b)
+    assert np.array_equal(e, golden["router120_e"])
+    assert_bit_equal(w, golden["router120_w"], "weights E=128")
+
+
+def test_golden_argmax(orc, golden):
+    lg = gi.case_argmax()
+    got = orc.argmax_rows(lg)
+    assert np.array_equal(got, golden["argmax"])
+    assert got[1] == 777 and got[2] == 0
+
+
+def test_golden_forward(orc, golden):
+    m = gi.tiny_model()
+    cfg = oracle.OrcConfig(*m.values())
+    w = gi.uniform(71, (oracle.flat_weight_count(cfg),), 0.35)
+    toks = gi.small_ints(72, (10,), 0, m["vocab"])
+    assert_bit_equal(orc.forward_seq(cfg, w, toks), golden["forward_logits"], "tiny-model logits")
+
+
+def test_golden_swiglu_combine_regression(orc, golden):
+    assert_bit_equal(orc.swiglu_rows(gi.case_swiglu()), golden["swiglu_out"], "swiglu")
+    x, Z, row_of, w, e = gi.case_combine()
+    assert_bit_equal(orc.combine_rows(x, Z, row_of, w, e, gi.E20), golden["combine_x"], "combine")
+
+
+def test_topk_ties_go_to_the_lowest_index(orc):
+    """Guards the one place the CPU program leans on the C library: qsort leaving equal
+    scores in index order."""
+    v, i = orc.topk(np.array([1, 3, 3, -0.0, 0, 3, 2, 2], np.float32), 4)
+    assert list(i) == [1, 2, 5, 6] and list(v) == [3, 3, 3, 2]
+    v, i = orc.topk(np.zeros(32, np.float32), 4)
+    assert list(i) == [0, 1, 2, 3]
+    s = np.zeros(32, np.float32)
+    s[5], s[9] = -0.0, 0.0
+    assert list(orc.topk(s, 4)[1]) == [0, 1, 2, 3]
+
+
+def test_argmax_nan_rules(orc):
+    nan = np.float32("nan")
+    assert orc.argmax(np.array([1, nan, 3, 3], np.float32)) == 2
+    assert orc.argmax(np.array([nan, 5, 7], np.float32)) == 0      # NaN in front sticks
+    assert orc.argmax(np.array([-np.inf, -np.inf], np.float32)) == 0
+    assert orc.argmax(np.array([-0.0, 0.0], np.float32)) == 0
+
+
+# ---- (2) the reference's own functions, bit for bit ----------------------------------
+
+@pytest.mark.parametrize("n", [1, 7, 64, 1000, 2880, 4096])
+def test_ref_rmsnorm(orc, ref, n):
+    rng = np.random.default_rng(n)
+    for scale in (1e-3, 1.0, 50.0):
+        x = (rng.standard_normal(n) * scale).astype(np.float32)
+        g = (1 + 0.1 * rng.standard_normal(n)).astype(np.float32)
+        assert_bit_equal(orc.rmsnorm(x, g), ref.rmsnorm(x, g), f"rmsnorm n={n} scale={scale}")
+
+
+@pytest.mark.parametrize("n", [1, 2, 4, 8, 33, 130])
+def test_ref_softmax(orc, ref, n):
+    rng = np.random.default_rng(100 + n)
+    for scale in (0.1, 4.0, 60.0):
+        x = (rng.standard_normal(n) * scale).astype(np.float32)
+        assert_bit_equal(orc.softmax(x), ref.softmax(x), f"softmax n={n}")
+
+
+@pytest.mark.parametrize("E,k", [(16, 8), (32, 4), (128, 4), (200, 2), (32, 2)])
+def test_ref_topk_with_planted_ties(orc, ref, E, k):
+    rng = np.random.default_rng(E * 10 + k)
+    for t in range(40):
+        s = rng.standard_normal(E).astype(np.float32)
+        if t % 3 == 0:
+            s[E - 1] = s[rng.integers(0, E - 1)]
+        if t % 5 == 0:
+            s[1], s[E // 2], s[0], s[E - 2] = 0.0, -0.0, 50.0, 50.0
+        if t % 7 == 0:
+            s = np.trunc(s * 2).astype(np.float32)
+        (v0, i0), (v1, i1) = orc.topk(s, k), ref.topk(s, k)
+        assert np.array_equal(i0, i1), (t, i0, i1)
+        assert_bit_equal(v0, v1)
+
+
+def test_ref_yarn(orc, ref):
+    assert orc.yarn_inv_freq()[0] == ref.yarn_inv_freq()[0]
+    assert_bit_equal(orc.yarn_inv_freq()[1], ref.yarn_inv_freq()[1])
+    # unscaled RoPE branch and another head size
+    assert_bit_equal(orc.yarn_inv_freq(factor=1.0)[1], ref.yarn_inv_freq(factor=1.0)[1])
+    assert_bit_equal(orc.yarn_inv_freq(head_dim=128)[1], ref.yarn_inv_freq(head_dim=128)[1])
+    for p in (0, 1, 2, 37, 127, 128, 1023, 1024, 4095, 4096, 131071):
+        (c0, s0), (c1, s1) = orc.yarn_cos_sin(p), ref.yarn_cos_sin(p)
+        assert_bit_equal(c0, c1, f"cos {p}")
+        assert_bit_equal(s0, s1, f"sin {p}")
+
+
+@pytest.mark.parametrize("heads", [(64, 8), (8, 1), (32, 4)])
+def test_ref_bias_rope_rows(orc, ref, heads):
+    nq, nkv = heads
+    rng = np.random.default_rng(nq)
+    T, row = 9, (nq + 2 * nkv) * 64
+    qkv = rng.standard_normal((T, row)).astype(np.float32)
+    bias = (0.02 * rng.standard_normal(row)).astype(np.float32)
+    pos = rng.integers(0, 4096, T).astype(np.int32)
+    assert_bit_equal(orc.bias_rope_rows(qkv, bias, pos, nq, nkv), ref.bias_rope_rows(qkv, bias, pos, nq, nkv))
+    assert_bit_equal(orc.bias_rope_rows(qkv, None, pos, nq, nkv), ref.bias_rope_rows(qkv, None, pos, nq, nkv))
+
+
+def test_ref_batched_rows(orc, ref):
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((17, 2880)).astype(np.float32)
+    d = rng.standard_normal((17, 2880)).astype(np.float32)
+    g = (1 + 0.1 * rng.standard_normal(2880)).astype(np.float32)
+    for a, b in zip(orc.add_rmsnorm_rows(x, d, g, threads=3), ref.add_rmsnorm_rows(x, d, g, threads=2)):
+        assert_bit_equal(a, b)
+    s = rng.standard_normal((65, 128)).astype(np.float32)
+    (w0, e0), (w1, e1) = orc.router_rows(s, 4, threads=2), ref.router_rows(s, 4, threads=3)
+    assert np.array_equal(e0, e1)
+    assert_bit_equal(w0, w1)
+    lg = rng.standard_normal((5, 50000)).astype(np.float32)
+    lg[2, 40000] = lg[2, 123] = 77.0
+    assert np.array_equal(orc.argmax_rows(lg), ref.argmax_rows(lg))
+    assert orc.argmax_rows(lg)[2] == 123
+
+
+@pytest.mark.parametrize("seed", [1, 2, 3])
+def test_ref_forward_pins_the_inline_loops(orc, ref, seed):
+    """forward() of a tiny model: bias adds, SwiGLU (with clamping hit by the large
+    weights), the expert combine in increasing expert order and both residual adds only
+    exist inside it."""
+    m = gi.tiny_model()
+    if seed == 2:
+        m.update(window=0, top_k=2, n_experts=4)
+    if seed == 3:
+        m.update(n_layers=3, inter=80, hidden=96)
+    cfg = oracle.OrcConfig(*m.values())
+    rng = np.random.default_rng(seed)
+    w = (rng.standard_normal(oracle.flat_weight_count(cfg)) * (0.2 if seed < 3 else 0.6)).astype(np.float32)
+    toks = rng.integers(0, m["vocab"], 8).astype(np.int32)
+    assert_bit_equal(orc.forward_seq(cfg, w, toks), ref.forward_seq(cfg, w, toks), "logits")
