@@ -19,6 +19,11 @@ pytestmark = pytest.mark.gpu
 H, QKV, V = 2880, 5120, 201088
 
 
+def fma32(a, b, c):
+    """fp32 fused multiply-add: the product of two floats is exact in double."""
+    return (np.asarray(a, np.float64) * np.asarray(b, np.float64) + np.asarray(c, np.float64)).astype(np.float32)
+
+
 def rng_of(*key):
     """A generator seeded by the case's name and shape (stable across processes)."""
     return np.random.default_rng(zlib.crc32(repr(key).encode()))
@@ -140,11 +145,18 @@ def test_bias_rope_fp32_mode_is_bit_exact(gpu, orc, T, heads):
                       flags=pkg.EXACT)
     want1 = orc.bias_rope_rows_table(qkv, None, np.full(T, 517, np.int32), ct, st, nq, nkv, hd)
     assert n_bit_diff(qb.get(), want1) == 0
-    # contracted form (the reference's own GPU rounding): same values within fp32 noise
+    # contracted form (the reference's own GPU rounding, fast_common.hpp:25-28), against
+    # the same fused multiply-adds emulated in double
     o3 = d.out((T, row), pkg.F32)
     pkg.qkv_bias_rope(T, d.put(qkv), pkg.F32, row, d.put(bias), d.put(pos), 0, cb, sb, n_pos, nq, nkv, hd,
                       o3, pkg.F32, row, flags=pkg.EXACT | pkg.FMA)
-    assert rel_err(o3.get(), want) <= TOL_F32
+    xb_ = (qkv + bias).reshape(T, nq + 2 * nkv, 2, hd // 2)
+    x1, x2 = xb_[:, :nq + nkv, 0], xb_[:, :nq + nkv, 1]
+    c_, s_ = ct[pos][:, None, :], st[pos][:, None, :]
+    emu = xb_.copy()
+    emu[:, :nq + nkv, 0] = fma32(x1, c_, -(x2 * s_))
+    emu[:, :nq + nkv, 1] = fma32(x2, c_, x1 * s_)
+    assert rel_err(o3.get(), emu.reshape(T, row)) <= 1e-6
 
 
 def test_bias_rope_strided_rows_and_position_clamp(gpu, orc):
@@ -320,10 +332,19 @@ def test_combine_fp32_mode_is_bit_exact(gpu, orc, T, k, Hd):
     pkg.moe_combine(T, xb4, d.put(Z), pkg.F32, None, d.put(w), d.put(e_slot), k, Hd, phys_of=d.put(phys),
                     flags=pkg.EXACT)
     assert n_bit_diff(xb4.get(), want_id) == 0
-    # contracted form: same within fp32 noise
+    # contracted form (the reference's moe_combine_exact, moe.hpp:228-235): a chain of
+    # fused multiply-adds in increasing expert order, emulated in double
     xb5 = d.put_inout(x)
     pkg.moe_combine(T, xb5, d.put(Z), pkg.F32, d.put(row_of), d.put(w), d.put(e), k, Hd, flags=pkg.EXACT | pkg.FMA)
-    assert rel_err(xb5.get(), want) <= TOL_F32
+    emu = x.copy()
+    for t in range(T):
+        if e[t, 0] < 0:
+            continue
+        acc = np.zeros(Hd, np.float32)
+        for j in np.argsort(e[t], kind="stable"):
+            acc = fma32(Z[row_of[t, j]], w[t, j], acc)
+        emu[t] = x[t] + acc
+    assert rel_err(xb5.get(), emu) <= 1e-6
 
 
 @pytest.mark.parametrize("T,k,Hd", [(1, 4, 2880), (9, 4, 2880), (512, 4, 2880), (33, 2, 1000), (33, 8, 4096), (5, 4, 77)])
