@@ -206,6 +206,34 @@ GPTOSS_API int gptoss_argmax(gptoss_stream_t stream, int T, const void *logits,
  * decodes the merged keys. */
 GPTOSS_API int gptoss_argmax_slices(int T, long V, gptoss_dtype_t logits_dtype, int has_keys);
 
+/*
+ * gptoss_argmax for callers that cannot hand over scratch memory.  It has no
+ * counterpart in the reference (whose launcher always receives `keys` from
+ * the engine); it exists for hosts that have no device allocator to call at
+ * this point -- for example a plug-in inside a serving process whose memory
+ * pool already owns the whole GPU, or a decode loop that must stay clear of
+ * cudaMalloc because an allocation stalls all streams of the device.
+ *
+ * Same result as gptoss_argmax, bit for bit.  The per-row merge words live in
+ * a fixed array inside the library (GPTOSS_ARGMAX_NOALLOC_MAX_ROWS words of 8
+ * bytes = 128 KB, resident on every GPU that loads the library until the
+ * process ends), so:
+ *   - T above GPTOSS_ARGMAX_NOALLOC_MAX_ROWS is refused with
+ *     GPTOSS_ERR_UNSUPPORTED and a line on stderr saying so (split the batch,
+ *     or use gptoss_argmax);
+ *   - all calls on one GPU share that array: the call clears the words it
+ *     needs before it starts, but two calls whose work overlaps in time on the
+ *     same GPU (different streams or threads) would corrupt each other --
+ *     keep them on one stream or order them yourself;
+ *   - the first call on each GPU looks up the array's device address; make
+ *     that first call before any stream capture begins.
+ * The call itself allocates nothing, on the device or in the CUDA runtime.
+ */
+#define GPTOSS_ARGMAX_NOALLOC_MAX_ROWS 16384
+GPTOSS_API int gptoss_argmax_noalloc(gptoss_stream_t stream, int T, const void *logits,
+                                     gptoss_dtype_t logits_dtype, long V, long row_stride,
+                                     int *out);
+
 #ifdef __cplusplus
 }
 #endif

@@ -69,6 +69,7 @@ PROTOTYPES = {
     "gptoss_moe_combine": (_i, [_p, _i, _p, _p, _i, _p, _p, _p, _i, _i, _p, _p, _p, _i, _u]),
     "gptoss_argmax": (_i, [_p, _i, _p, _i, _l, _l, _p, _p]),
     "gptoss_argmax_slices": (_i, [_i, _l, _i, _i]),
+    "gptoss_argmax_noalloc": (_i, [_p, _i, _p, _i, _l, _l, _p]),
     "gptoss_device_count": (_i, [C.POINTER(_i)]),
     "gptoss_device_set": (_i, [_i]),
     "gptoss_device_name": (_i, [_i, C.c_char_p, _i]),
@@ -264,6 +265,15 @@ def moe_combine(T, x, Z, z_dtype, own_row, topk_w, topk_e, k, H, phys_of=None, n
 
 def argmax(T, logits, dtype, V, row_stride, keys, out, stream=None):
     check(load().gptoss_argmax(stream, T, _ptr(logits), dtype, V, row_stride, _ptr(keys), _ptr(out)), "argmax")
+
+
+ARGMAX_NOALLOC_MAX_ROWS = 16384
+
+
+def argmax_noalloc(T, logits, dtype, V, row_stride, out, stream=None):
+    """gptoss_argmax without caller scratch: the merge words sit in a fixed array inside the
+    library, so at most ARGMAX_NOALLOC_MAX_ROWS rows per call and no overlapping calls per GPU."""
+    check(load().gptoss_argmax_noalloc(stream, T, _ptr(logits), dtype, V, row_stride, _ptr(out)), "argmax_noalloc")
 
 
 def build_rope_tables(n_pos, head_dim=64, theta=150000.0, factor=32.0, orig_ctx=4096.0,

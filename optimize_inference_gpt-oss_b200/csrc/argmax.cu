@@ -220,3 +220,86 @@ extern "C" int gptoss_argmax_slices(int T, long V, gptoss_dtype_t logits_dtype, 
   const long per = logits_dtype == GPTOSS_F32 ? 4 : 8;
   return plan_slices(T, V / per, has_keys != 0);
 }
+
+// ---- greedy argmax for callers that cannot allocate device memory ---------------------
+#include <stdio.h>
+//
+// gptoss_argmax needs one 64-bit merge word per row from its caller.  Some hosts
+// of this library have no way to provide that: a plug-in running inside a serving
+// process whose memory manager has already claimed the whole GPU and hands out
+// nothing at request time, or a step function that must never reach cudaMalloc
+// because an allocation stalls every stream of the device.  For them the merge
+// words live in this fixed array, which is part of the library image: each GPU
+// that loads the library holds these 128 KB from load until the process exits.
+static __device__ __align__(256) unsigned long long g_noalloc_keys[GPTOSS_ARGMAX_NOALLOC_MAX_ROWS];
+
+namespace gptoss {
+namespace {
+
+// Device address of g_noalloc_keys on the current device.  In host code the
+// array's name is only a handle for the runtime, not an address a kernel can
+// use, so the address is asked for once per device (with that device current)
+// and remembered.  Returns nullptr and sets *status on failure.
+unsigned long long *noalloc_keys_on_current_device(int *status) {
+  static unsigned long long *address_of[64] = {nullptr};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) {
+    note_cuda_error(e);
+    *status = GPTOSS_ERR_CUDA;
+    return nullptr;
+  }
+  if (dev < 0 || dev >= 64) {
+    *status = GPTOSS_ERR_UNSUPPORTED;
+    return nullptr;
+  }
+  if (!address_of[dev]) {
+    void *p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_noalloc_keys);
+    if (e != cudaSuccess || !p) {
+      note_cuda_error(e);
+      (void)cudaGetLastError();
+      *status = GPTOSS_ERR_CUDA;
+      return nullptr;
+    }
+    address_of[dev] = static_cast<unsigned long long *>(p);
+  }
+  return address_of[dev];
+}
+
+} // namespace
+} // namespace gptoss
+
+extern "C" int gptoss_argmax_noalloc(gptoss_stream_t stream, int T, const void *logits,
+                                     gptoss_dtype_t logits_dtype, long V, long row_stride,
+                                     int *out) {
+  using namespace gptoss;
+  if (T < 0 || V <= 0 || V > 0x7fffffffL || row_stride < V || !valid_dtype(logits_dtype))
+    return GPTOSS_ERR_BAD_ARG;
+  if (T == 0)
+    return GPTOSS_OK;
+  if (!logits || !out)
+    return GPTOSS_ERR_BAD_ARG;
+  if (T > GPTOSS_ARGMAX_NOALLOC_MAX_ROWS) {
+    fprintf(stderr,
+            "gptoss_argmax_noalloc: %d rows exceed the built-in scratch of %d rows; split the "
+            "batch or use gptoss_argmax with caller-provided keys\n",
+            T, GPTOSS_ARGMAX_NOALLOC_MAX_ROWS);
+    return GPTOSS_ERR_UNSUPPORTED;
+  }
+  int st = GPTOSS_OK;
+  unsigned long long *keys = noalloc_keys_on_current_device(&st);
+  if (!keys)
+    return st;
+  cudaStream_t s = as_stream(stream);
+  // The array still holds whatever the previous call (of any thread) left
+  // there: the merge words of this call's rows must start from zero.
+  const cudaError_t e = cudaMemsetAsync(keys, 0, (size_t)T * sizeof(unsigned long long), s);
+  if (e != cudaSuccess) {
+    note_cuda_error(e);
+    (void)cudaGetLastError();
+    return GPTOSS_ERR_CUDA;
+  }
+  return logits_dtype == GPTOSS_F32 ? launch<float>(s, T, logits, V, row_stride, keys, out)
+                                    : launch<uint16_t>(s, T, logits, V, row_stride, keys, out);
+}
