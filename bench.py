@@ -16,8 +16,9 @@ for the GEMM and attention outputs.  Rank 0 prints one JSON line:
               positions copied from pinned host memory and the picked tokens copied back
               inside the timed region every step (what the reference engine moves per
               step, gpu_engine.hpp:781-798), wall clock, max over ranks
-  roofline    the dominant kernel: algorithmic bytes per launch / mean launch time from
-              CUDA event pairs around every launch, against the measured HBM copy peak
+  roofline    the dominant kernel: algorithmic bytes per launch / mean launch time (CUDA
+              events on the launching stream around that kernel's launches of a step, one
+              per layer, each on its own layer's tensors), against the measured HBM copy peak
   kernels     the same for every kernel kind
   cpu_baseline  the reference's CPU code (OpenMP over tokens, all host threads) on a
               bounded sample of the same workload; rank 0 at N = 1 only
@@ -56,6 +57,9 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=8.0, help="minimum CPU time of the baseline sample")
     ap.add_argument("--profile-steps", type=int, default=10)
+    ap.add_argument("--ncu-steps", type=int, default=0,
+                    help="profiler mode: build the chain, run this many steps kernel by kernel, exit (no timing)")
+    ap.add_argument("--vocab", type=int, default=0, help="override the vocabulary size (profiler mode: smaller footprint)")
     return ap.parse_args()
 
 
@@ -284,6 +288,8 @@ def main():
 
     T = args.tokens_per_gpu
     c = pkg.chain_config(args.model, pkg.BF16, 4096)
+    if args.vocab > 0:
+        c.vocab = args.vocab
     sets = args.standin_sets or c.n_layers
     t_setup = time.perf_counter()
     chain = pkg.Chain(c, T, sets)
@@ -297,6 +303,15 @@ def main():
     chain.upload(pkg.BUF_TOKENS, 0, tok.array)
     chain.upload(pkg.BUF_POS, 0, pos.array)
     setup_s = time.perf_counter() - t_setup
+
+    if args.ncu_steps > 0:  # launched under ncu: plain launches, nothing timed, nothing printed as a result
+        for _ in range(args.ncu_steps):
+            chain.enqueue(T, False)
+        pkg.synchronize()
+        print(json.dumps({"ncu_steps": args.ncu_steps, "launches_per_step": chain.launches_per_step(T),
+                          "device_bytes": chain.device_bytes}), flush=True)
+        chain.close()
+        return
 
     lib = pkg.load()
     import ctypes as C
@@ -335,8 +350,8 @@ def main():
     e2e_value = world * T * args.steps / e2e_s
     clocks = sampler.stop() if sampler else None
 
-    # ---- per-kernel device times: an event pair around every launch, same stream
-    prof = chain.profile(T, max(1, min(args.profile_steps, args.steps)))
+    # ---- per-kernel device times: per kind, an event pair around its launches of a step
+    prof = chain.profile(T, max(1, min(args.profile_steps, args.steps)), mode=2)
     peak, peak_src = hbm_peak()
     kernels = {}
     chain_bytes = 0

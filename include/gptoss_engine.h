@@ -186,11 +186,18 @@ typedef enum {
   GPTOSS_K_COUNT
 } gptoss_chain_kernel_t;
 
-/* Runs `steps` steps kernel by kernel with a CUDA event pair around every
- * launch (on the chain's stream) and returns, per kernel kind, the summed
- * device time in ms and the number of launches.  Arrays of GPTOSS_K_COUNT.
- * flush_l2 != 0 overwrites a 256 MB scratch buffer before every launch. */
-GPTOSS_API int gptoss_chain_profile(gptoss_chain_t *chain, int T, int steps, int flush_l2,
+/* Device time per kernel kind, from CUDA events on the chain's stream, summed
+ * over `steps` steps, with the number of launches it covers (arrays of
+ * GPTOSS_K_COUNT).
+ *   mode 0: the step runs in order with an event pair around every launch;
+ *   mode 1: the same, and a 256 MB scratch buffer is overwritten before every
+ *           launch (cold L2);
+ *   mode 2: per kind, all of its launches of a step (one per layer, each on its
+ *           own layer's tensors) run back to back between one event pair, so the
+ *           cost of the event records themselves (a few microseconds per pair,
+ *           comparable to the shortest kernels) is spread over the batch; the
+ *           values the chain computes are meaningless in this mode. */
+GPTOSS_API int gptoss_chain_profile(gptoss_chain_t *chain, int T, int steps, int mode,
                                     double *ms_per_kind, long *launches_per_kind);
 
 /* Algorithmic bytes one launch of a kernel kind moves for T rows: compulsory

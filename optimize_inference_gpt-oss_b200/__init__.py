@@ -18,7 +18,7 @@ import os
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libgptoss_b200.so")
+LIB_PATH = os.environ.get("GPTOSS_B200_LIB") or os.path.join(_HERE, "libgptoss_b200.so")
 INCLUDE_DIR = os.path.join(os.path.dirname(_HERE), "include")
 
 F32, BF16 = 0, 1
@@ -393,11 +393,13 @@ class Chain:
         check(load().gptoss_chain_step(self.h, T, tokens_host.ctypes.data, pos_host.ctypes.data,
                                        next_host.ctypes.data), "chain_step")
 
-    def profile(self, T: int, steps: int, flush_l2: bool = False):
+    def profile(self, T: int, steps: int, mode: int = 0):
+        """Per kernel kind: (summed device ms, launches).  mode 0: an event pair per launch;
+        1: the same after an L2 flush; 2: one pair per kind around its back-to-back launches."""
         n = len(KERNEL_KINDS)
         ms = (C.c_double * n)()
         cnt = (_l * n)()
-        check(load().gptoss_chain_profile(self.h, T, steps, 1 if flush_l2 else 0, ms, cnt), "chain_profile")
+        check(load().gptoss_chain_profile(self.h, T, steps, mode, ms, cnt), "chain_profile")
         return {k: (ms[i], cnt[i]) for i, k in enumerate(KERNEL_KINDS)}
 
     def kernel_bytes(self, kind: str, T: int) -> int:

@@ -31,7 +31,7 @@ struct gptoss_chain {
   void *attn_proj = nullptr, *qkv = nullptr, *router = nullptr, *mlp1 = nullptr, *expert = nullptr,
        *logits = nullptr;
   // state
-  int *tokens = nullptr, *pos = nullptr, *next = nullptr, *topk_e = nullptr;
+  int *tokens = nullptr, *pos = nullptr, *next = nullptr, *topk_e = nullptr, *own_row = nullptr;
   float *x = nullptr, *topk_w = nullptr;
   void *normed = nullptr, *qkv_out = nullptr, *swiglu = nullptr;
   unsigned long long *keys = nullptr;
@@ -113,6 +113,8 @@ struct Hook {
 
 #define STEP(kind, call)                                                                          \
   do {                                                                                            \
+    if (only >= 0 && only != (int)(kind))                                                         \
+      break;                                                                                      \
     if (hook)                                                                                     \
       hook->before(kind);                                                                         \
     const int st_ = (call);                                                                       \
@@ -122,8 +124,9 @@ struct Hook {
       return st_;                                                                                 \
   } while (0)
 
-// Issues every kernel of one step for T rows on s.
-int issue_step(gptoss_chain *c, int T, cudaStream_t s, Hook *hook) {
+// Issues every kernel of one step for T rows on s; with only >= 0, just the
+// launches of that kernel kind (all layers, in layer order).
+int issue_step(gptoss_chain *c, int T, cudaStream_t s, Hook *hook, int only = -1) {
   const gptoss_chain_config_t &g = c->cfg;
   const gptoss_dtype_t a = (gptoss_dtype_t)g.act_dtype;
   const int H = g.hidden, L = g.n_layers, K = g.top_k, QKV = c->qkv_dim();
@@ -154,7 +157,7 @@ int issue_step(gptoss_chain *c, int T, cudaStream_t s, Hook *hook) {
     const float *next_gain = l + 1 < L ? (const float *)layer_ptr(c, GPTOSS_BUF_GAIN_ATTN, l + 1)
                                        : c->gain_out;
     STEP(GPTOSS_K_COMBINE,
-         gptoss_moe_combine(gs, T, c->x, layer_ptr(c, GPTOSS_BUF_EXPERT, l), a, nullptr, c->topk_w,
+         gptoss_moe_combine(gs, T, c->x, layer_ptr(c, GPTOSS_BUF_EXPERT, l), a, c->own_row, c->topk_w,
                             c->topk_e, K, H, nullptr, next_gain, c->normed, a, g.flags));
   }
   // [LM-head GEMM of `normed`] -> stand-in logits; greedy pick
@@ -266,11 +269,21 @@ int gptoss_chain_create(const gptoss_chain_config_t *cfg, int max_tokens, int n_
   ALLOC(topk_e, T * K * 4);
   ALLOC(swiglu, K * T * (size_t)cfg->inter * a);
   ALLOC(keys, T * 8);
+  ALLOC(own_row, T * K * 4);
   c->flush_bytes = (size_t)256 << 20;
   ALLOC(flush, c->flush_bytes);
 #undef ALLOC
   if (st == GPTOSS_OK)
     st = cuda_status(cudaMemsetAsync(c->keys, 0, T * 8, c->stream));
+  if (st == GPTOSS_OK) {
+    // The engine's grouping step decides where each (token, choice) pair's expert output
+    // lands; with the stand-in tensors that map is the identity, passed explicitly so the
+    // combine goes through the indirection exactly as it does behind a real grouping.
+    std::vector<int> ident(T * K);
+    for (size_t i = 0; i < ident.size(); i++)
+      ident[i] = (int)i;
+    st = cuda_status(cudaMemcpy(c->own_row, ident.data(), ident.size() * 4, cudaMemcpyHostToDevice));
+  }
   if (st == GPTOSS_OK)
     st = cuda_status(cudaMemsetAsync(c->tokens, 0, T * 4, c->stream));
   if (st == GPTOSS_OK)
@@ -454,16 +467,48 @@ int gptoss_chain_step(gptoss_chain_t *c, int T, const int *tokens_host, const in
   return st;
 }
 
-int gptoss_chain_profile(gptoss_chain_t *c, int T, int steps, int flush_l2, double *ms_per_kind,
+int gptoss_chain_profile(gptoss_chain_t *c, int T, int steps, int mode, double *ms_per_kind,
                          long *launches_per_kind) {
-  if (!c || T <= 0 || T > c->max_tokens || steps <= 0 || !ms_per_kind || !launches_per_kind)
+  if (!c || T <= 0 || T > c->max_tokens || steps <= 0 || !ms_per_kind || !launches_per_kind ||
+      mode < 0 || mode > 2)
     return GPTOSS_ERR_BAD_ARG;
   for (int k = 0; k < GPTOSS_K_COUNT; k++) {
     ms_per_kind[k] = 0.0;
     launches_per_kind[k] = 0;
   }
+  if (mode == 2) {
+    // One event pair around all of a kind's launches of a step, issued back to back:
+    // the per-launch cost of recording events is spread over the batch.
+    const int per_step[GPTOSS_K_COUNT] = {1, 1, c->cfg.n_layers, c->cfg.n_layers, c->cfg.n_layers,
+                                          c->cfg.n_layers, c->cfg.n_layers, 1};
+    while (c->events.size() < 2) {
+      cudaEvent_t e = nullptr;
+      int st = cuda_status(cudaEventCreate(&e));
+      if (st != GPTOSS_OK)
+        return st;
+      c->events.push_back(e);
+    }
+    for (int s = 0; s < steps; s++)
+      for (int kind = 0; kind < GPTOSS_K_COUNT; kind++) {
+        int st = cuda_status(cudaEventRecord(c->events[0], c->stream));
+        if (st == GPTOSS_OK)
+          st = issue_step(c, T, c->stream, nullptr, kind);
+        if (st == GPTOSS_OK)
+          st = cuda_status(cudaEventRecord(c->events[1], c->stream));
+        if (st == GPTOSS_OK)
+          st = cuda_status(cudaStreamSynchronize(c->stream));
+        float ms = 0.0f;
+        if (st == GPTOSS_OK)
+          st = cuda_status(cudaEventElapsedTime(&ms, c->events[0], c->events[1]));
+        if (st != GPTOSS_OK)
+          return st;
+        ms_per_kind[kind] += ms;
+        launches_per_kind[kind] += per_step[kind];
+      }
+    return GPTOSS_OK;
+  }
   for (int s = 0; s < steps; s++) {
-    ProfileHook hook(c, c->stream, flush_l2 != 0);
+    ProfileHook hook(c, c->stream, mode == 1);
     int st = issue_step(c, T, c->stream, &hook);
     if (st != GPTOSS_OK)
       return st;

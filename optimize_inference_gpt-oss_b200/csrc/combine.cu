@@ -3,57 +3,160 @@
 //
 // Per token the kernel reads the residual row, k expert-output rows (through
 // the own_row indirection) and k weights, and writes the residual row and,
-// with the norm, one normalised row.  One thread block per token at a time;
-// each thread owns NC chunks of 8 consecutive elements and issues the loads of
-// the residual chunk and of all k expert chunks (up to 9 x 16-32 B per chunk)
-// before the first use, so a block keeps a whole token (about 34 KB at H = 2880,
-// k = 4, bf16 experts) in flight.
+// with the norm, one normalised row.  One thread block works on one token at a
+// time and walks the tokens with a grid stride; a token's rows (about 34 KB at
+// H = 2880, k = 4, bf16 experts) are staged through a ring of shared-memory
+// buffers filled by cp.async several tokens ahead, so an SM keeps ~200 KB of
+// reads outstanding.  A thread owns NC chunks of 8 consecutive elements, copies
+// those chunks of all k + 1 rows itself and reads only them back.  The small
+// per-token routing data (row numbers, weights, expert ids) is fetched into
+// registers one iteration before it is needed, so no load sits between a
+// token's staged data and its arithmetic.
 #include "common.cuh"
 
 namespace gptoss {
 namespace {
 
-template <typename ZT> struct RawChunk { // 8 elements as loaded
-  uint4 q[sizeof(ZT) / 2];
+__device__ __forceinline__ Vec8 smem_chunk_f32(const unsigned char *p) {
+  const uint4 a = *reinterpret_cast<const uint4 *>(p), b = *reinterpret_cast<const uint4 *>(p + 16);
+  Vec8 v;
+  v.v[0] = __uint_as_float(a.x), v.v[1] = __uint_as_float(a.y), v.v[2] = __uint_as_float(a.z),
+  v.v[3] = __uint_as_float(a.w), v.v[4] = __uint_as_float(b.x), v.v[5] = __uint_as_float(b.y),
+  v.v[6] = __uint_as_float(b.z), v.v[7] = __uint_as_float(b.w);
+  return v;
+}
+
+template <int KM> struct Routing { // weights and expert ids of one token
+  float w[KM];
+  int e[KM];
 };
-
-template <typename ZT> __device__ __forceinline__ RawChunk<ZT> load_raw(const ZT *p) {
-  RawChunk<ZT> r;
-  r.q[0] = ld_stream(p);
-  if constexpr (sizeof(ZT) == 4)
-    r.q[1] = ld_stream(p + 4);
-  return r;
-}
-
-template <typename ZT> __device__ __forceinline__ Vec8 widen(const RawChunk<ZT> &r) {
-  if constexpr (sizeof(ZT) == 2) {
-    return widen8(r.q[0]);
-  } else {
-    Vec8 v;
-    v.v[0] = __uint_as_float(r.q[0].x), v.v[1] = __uint_as_float(r.q[0].y),
-    v.v[2] = __uint_as_float(r.q[0].z), v.v[3] = __uint_as_float(r.q[0].w),
-    v.v[4] = __uint_as_float(r.q[1].x), v.v[5] = __uint_as_float(r.q[1].y),
-    v.v[6] = __uint_as_float(r.q[1].z), v.v[7] = __uint_as_float(r.q[1].w);
-    return v;
-  }
-}
+template <int KM> struct RowIds { // where the token's expert rows are, and whether it is live
+  int row[KM];
+  bool live;
+};
 
 // MODE 0: fast (choice order, FMA).  MODE 1: exact (increasing expert, separate
 // product and sum).  MODE 2: exact order with FMA.
-template <typename ZT, typename OT, int MODE, bool NORM, int KM, int NC>
+template <typename ZT, typename OT, int MODE, bool NORM, int KM, int NC, int STAGES>
 __global__ void combine_rows(float *x, const ZT *__restrict__ Z, const int *__restrict__ own_row,
                              const float *__restrict__ topk_w, const int *__restrict__ topk_e,
                              int k, int H, const int *__restrict__ phys_of,
                              const float *__restrict__ norm_w, OT *__restrict__ out, int T) {
   constexpr bool EXACT = MODE != 0;
+  constexpr int SZ = sizeof(ZT);
   using Acc = typename std::conditional<EXACT, double, float>::type;
+  extern __shared__ __align__(16) unsigned char ring[];
   __shared__ Acc scratch[2][32];
+  const size_t x_bytes = (size_t)H * 4, z_bytes = (size_t)H * SZ;
+  const size_t stage_bytes = x_bytes + (size_t)k * z_bytes;
   const int n_chunks = H >> 3;
-  int flip = 0;
-  for (int row = blockIdx.x; row < T; row += gridDim.x, flip ^= 1) {
-    float *xr = x + (size_t)row * H;
-    const bool live = __ldg(topk_e + (size_t)row * k) >= 0;
-    // order in which the choices are added
+
+  bool has[NC];
+  [[maybe_unused]] Vec8 ws[NC];
+#pragma unroll
+  for (int c = 0; c < NC; c++) {
+    const int chunk = threadIdx.x + c * blockDim.x;
+    has[c] = chunk < n_chunks;
+    if constexpr (NORM)
+      if (has[c])
+        ws[c] = load8<kTable>(norm_w, (size_t)chunk * 8);
+  }
+
+  // Routing data is tiny but every thread needs it.  Instead of every thread
+  // loading every word, lane L of each warp loads one word of a token and the
+  // warp shares them with shuffles at the point of use:
+  //   "ids" word:     L < k: own_row[token*k + L];   L == k: topk_e[token*k] (liveness)
+  //   "routing" word: L < k: topk_w[token*k + L];    k <= L < 2k: topk_e[token*k + L - k]
+  const int lane = threadIdx.x & 31;
+  auto load_ids_word = [&](long row) -> uint32_t {
+    if (lane < k)
+      return own_row ? (uint32_t)__ldg(own_row + (size_t)row * k + lane) : (uint32_t)(row * k + lane);
+    if (lane == k)
+      return (uint32_t)__ldg(topk_e + (size_t)row * k);
+    return 0u;
+  };
+  auto load_routing_word = [&](long row) -> uint32_t {
+    if (lane < k)
+      return __float_as_uint(__ldg(topk_w + (size_t)row * k + lane));
+    if (lane < 2 * k)
+      return (uint32_t)__ldg(topk_e + (size_t)row * k + lane - k);
+    return 0u;
+  };
+  auto spread_ids = [&](uint32_t word) {
+    RowIds<KM> r;
+    r.live = (int)__shfl_sync(0xffffffffu, word, k) >= 0;
+#pragma unroll
+    for (int j = 0; j < KM; j++)
+      r.row[j] = (int)__shfl_sync(0xffffffffu, word, j < k ? j : 0);
+    return r;
+  };
+  auto spread_routing = [&](uint32_t word) {
+    Routing<KM> r;
+#pragma unroll
+    for (int j = 0; j < KM; j++) {
+      r.w[j] = __uint_as_float(__shfl_sync(0xffffffffu, word, j < k ? j : 0));
+      r.e[j] = j < k ? (int)__shfl_sync(0xffffffffu, word, k + j) : 0x7fffffff;
+    }
+    return r;
+  };
+  auto issue = [&](long row, int stage, const RowIds<KM> &ids) {
+    unsigned char *sx = ring + (size_t)stage * stage_bytes;
+    const float *xr = x + (size_t)row * H;
+#pragma unroll
+    for (int c = 0; c < NC; c++)
+      if (has[c]) {
+        const int chunk = threadIdx.x + c * blockDim.x;
+        cp_async16(sx + (size_t)chunk * 32, xr + (size_t)chunk * 8);
+        cp_async16(sx + (size_t)chunk * 32 + 16, xr + (size_t)chunk * 8 + 4);
+        if (ids.live) {
+#pragma unroll
+          for (int j = 0; j < KM; j++)
+            if (j < k) {
+              const ZT *zr = Z + (size_t)ids.row[j] * H + (size_t)chunk * 8;
+              unsigned char *sz = sx + x_bytes + (size_t)j * z_bytes + (size_t)chunk * 8 * SZ;
+              cp_async16(sz, zr);
+              if constexpr (SZ == 4)
+                cp_async16(sz + 16, zr + 4);
+            }
+        }
+      }
+  };
+
+  const long step = gridDim.x;
+  long row = blockIdx.x;
+  if (row >= T)
+    return;
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; s++) {
+    const long r = row + s * step < T ? row + s * step : row;
+    const RowIds<KM> ids = spread_ids(load_ids_word(r));
+    if (row + s * step < T)
+      issue(row + s * step, s, ids);
+    cp_async_commit();
+  }
+  // one word per lane: routing of the current token, row ids of the token STAGES-1 ahead;
+  // both are refilled one iteration before they are needed
+  uint32_t routing_word = load_routing_word(row);
+  uint32_t ids_word = load_ids_word(row + (STAGES - 1) * step < T ? row + (STAGES - 1) * step : row);
+  int stage = 0, flip = 0;
+  for (; row < T; row += step, flip ^= 1) {
+    {
+      const long ahead = row + (STAGES - 1) * step;
+      const int fill = stage == 0 ? STAGES - 1 : stage - 1;
+      const RowIds<KM> ahead_ids = spread_ids(ids_word);
+      if (ahead < T)
+        issue(ahead, fill, ahead_ids);
+      cp_async_commit();
+    }
+    const Routing<KM> cur = spread_routing(routing_word);
+    // fetch for the next iteration while this token's copies finish
+    if (row + step < T)
+      routing_word = load_routing_word(row + step);
+    if (row + STAGES * step < T)
+      ids_word = load_ids_word(row + STAGES * step);
+    cp_async_wait<STAGES - 1>();
+
+    const bool live = cur.e[0] >= 0;
     int ord[KM];
 #pragma unroll
     for (int j = 0; j < KM; j++)
@@ -61,10 +164,8 @@ __global__ void combine_rows(float *x, const ZT *__restrict__ Z, const int *__re
     if (EXACT && live) {
       int key[KM];
 #pragma unroll
-      for (int j = 0; j < KM; j++) {
-        const int e = j < k ? __ldg(topk_e + (size_t)row * k + j) : 0x7fffffff;
-        key[j] = (phys_of && e >= 0 && e != 0x7fffffff) ? __ldg(phys_of + e) : e;
-      }
+      for (int j = 0; j < KM; j++)
+        key[j] = (phys_of && cur.e[j] >= 0 && cur.e[j] != 0x7fffffff) ? __ldg(phys_of + cur.e[j]) : cur.e[j];
 #pragma unroll
       for (int i = 1; i < KM; i++)
 #pragma unroll
@@ -75,56 +176,49 @@ __global__ void combine_rows(float *x, const ZT *__restrict__ Z, const int *__re
             key[j - 1] = tk, ord[j - 1] = to;
           }
     }
-    const ZT *zrow[KM];
-    float wgt[KM];
-#pragma unroll
-    for (int j = 0; j < KM; j++) {
-      zrow[j] = Z;
-      wgt[j] = 0.0f;
-      if (live && j < k) {
-        const size_t p = (size_t)row * k + ord[j];
-        const size_t zr = own_row ? (size_t)__ldg(own_row + p) : p;
-        zrow[j] = Z + zr * H;
-        wgt[j] = __ldg(topk_w + p);
-      }
-    }
+
+    const unsigned char *sx = ring + (size_t)stage * stage_bytes;
+    float *xr = x + (size_t)row * H;
     Vec8 xs[NC];
-    [[maybe_unused]] Vec8 ws[NC];
-    bool has[NC];
     Acc ss = 0;
 #pragma unroll
     for (int c = 0; c < NC; c++) {
-      const int chunk = threadIdx.x + c * blockDim.x;
-      has[c] = chunk < n_chunks;
       if (!has[c])
         continue;
-      const size_t e = (size_t)chunk * 8;
-      xs[c] = load8<kPlain>(xr, e);
-      if constexpr (NORM)
-        ws[c] = load8<kTable>(norm_w, e);
+      const int chunk = threadIdx.x + c * blockDim.x;
+      xs[c] = smem_chunk_f32(sx + (size_t)chunk * 32);
       if (live) {
-        RawChunk<ZT> zr[KM];
-#pragma unroll
-        for (int j = 0; j < KM; j++)
-          if (j < k)
-            zr[j] = load_raw(zrow[j] + e);
         Vec8 acc;
 #pragma unroll
         for (int i = 0; i < 8; i++)
           acc.v[i] = 0.0f;
 #pragma unroll
-        for (int j = 0; j < KM; j++)
-          if (j < k) {
-            const Vec8 z = widen(zr[j]);
+        for (int jj = 0; jj < KM; jj++)
+          if (jj < k) {
+            // position jj of the summation order takes choice ord[jj]
+            int j = jj;
+            float wj = cur.w[jj];
+            if (EXACT) {
+              j = ord[jj];
+#pragma unroll
+              for (int q = 0; q < KM; q++)
+                if (q == j)
+                  wj = cur.w[q];
+            }
+            const unsigned char *sz = sx + x_bytes + (size_t)j * z_bytes + (size_t)chunk * 8 * SZ;
+            Vec8 z;
+            if constexpr (SZ == 2)
+              z = widen8(*reinterpret_cast<const uint4 *>(sz));
+            else
+              z = smem_chunk_f32(sz);
 #pragma unroll
             for (int i = 0; i < 8; i++)
-              acc.v[i] = MODE == 1 ? __fadd_rn(acc.v[i], __fmul_rn(z.v[i], wgt[j]))
-                                   : __fmaf_rn(z.v[i], wgt[j], acc.v[i]);
+              acc.v[i] = MODE == 1 ? __fadd_rn(acc.v[i], __fmul_rn(z.v[i], wj)) : __fmaf_rn(z.v[i], wj, acc.v[i]);
           }
 #pragma unroll
         for (int i = 0; i < 8; i++)
           xs[c].v[i] = __fadd_rn(xs[c].v[i], acc.v[i]);
-        store8(xr, e, xs[c], false);
+        store8(xr, (size_t)chunk * 8, xs[c], false);
       }
       if constexpr (NORM) {
 #pragma unroll
@@ -161,7 +255,9 @@ __global__ void combine_rows(float *x, const ZT *__restrict__ Z, const int *__re
           store8(orow, (size_t)(threadIdx.x + c * blockDim.x) * 8, o);
         }
     }
+    stage = stage + 1 == STAGES ? 0 : stage + 1;
   }
+  cp_async_wait<0>();
 }
 
 // Any H, k <= GPTOSS_MAX_TOPK, any alignment: scalar accesses.
@@ -245,33 +341,52 @@ struct Args {
   void *out;
 };
 
-template <typename ZT, typename OT, int MODE, bool NORM, int KM, int NC>
-int launch_kernel(cudaStream_t s, const Args &a, int threads) {
-  static int occ[33];
-  auto kern = combine_rows<ZT, OT, MODE, NORM, KM, NC>;
-  kern<<<row_grid(a.T, blocks_per_sm(kern, threads, &occ[threads / 32])), threads, 0, s>>>(
-      a.x, static_cast<const ZT *>(a.Z), a.own_row, a.topk_w, a.topk_e, a.k, a.H, a.phys_of,
-      a.norm_w, static_cast<OT *>(a.out), a.T);
+template <typename ZT, typename OT, int MODE, bool NORM, int KM, int NC, int STAGES>
+int launch_kernel(cudaStream_t s, const Args &a, int threads, size_t smem) {
+  auto kern = combine_rows<ZT, OT, MODE, NORM, KM, NC, STAGES>;
+  const int per_sm = blocks_per_sm_smem(kern, threads, smem);
+  if (per_sm < 1)
+    return GPTOSS_ERR_UNSUPPORTED;
+  kern<<<row_grid(a.T, per_sm), threads, smem, s>>>(a.x, static_cast<const ZT *>(a.Z), a.own_row,
+                                                   a.topk_w, a.topk_e, a.k, a.H, a.phys_of, a.norm_w,
+                                                   static_cast<OT *>(a.out), a.T);
   return launch_status();
 }
 
+template <typename ZT, typename OT, int MODE, bool NORM, int KM, int NC>
+int launch_stages(cudaStream_t s, const Args &a, int threads, size_t stage_bytes, int stages) {
+  if constexpr (NC > 1) // wide rows: a stage is tens of KB, two is what fits anyway
+    return launch_kernel<ZT, OT, MODE, NORM, KM, NC, 2>(s, a, threads, stage_bytes * 2);
+  if (stages == 4)
+    return launch_kernel<ZT, OT, MODE, NORM, KM, NC, 4>(s, a, threads, stage_bytes * 4);
+  if (stages == 3)
+    return launch_kernel<ZT, OT, MODE, NORM, KM, NC, 3>(s, a, threads, stage_bytes * 3);
+  return launch_kernel<ZT, OT, MODE, NORM, KM, NC, 2>(s, a, threads, stage_bytes * 2);
+}
+
 template <typename ZT, typename OT, int MODE, bool NORM> int launch(cudaStream_t s, const Args &a) {
-  const bool vec = a.H % 8 == 0 && a.H <= 8 * 512 * 4 && aligned16(a.x) && aligned16(a.Z) &&
+  const size_t stage_bytes = (size_t)a.H * (4 + (size_t)a.k * sizeof(ZT));
+  const int stages = pick_stages(stage_bytes);
+  const bool vec = a.H % 8 == 0 && a.H <= 8 * 512 * 4 && aligned16(a.x) && aligned16(a.Z) && stages > 0 &&
                    (!NORM || (aligned16(a.norm_w) && aligned16(a.out)));
-  if (!vec) {
-    combine_rows_generic<ZT, OT, MODE, NORM><<<row_grid(a.T, 8), 256, 0, s>>>(
-        a.x, static_cast<const ZT *>(a.Z), a.own_row, a.topk_w, a.topk_e, a.k, a.H, a.phys_of,
-        a.norm_w, static_cast<OT *>(a.out), a.T);
-    return launch_status();
+  if (vec) {
+    const int n_chunks = a.H / 8;
+    const int nc = n_chunks <= 512 ? 1 : 4;
+    const int threads = ((n_chunks + nc - 1) / nc + 31) / 32 * 32;
+    int st;
+    if (a.k <= 4)
+      st = nc == 1 ? launch_stages<ZT, OT, MODE, NORM, 4, 1>(s, a, threads, stage_bytes, stages)
+                   : launch_stages<ZT, OT, MODE, NORM, 4, 4>(s, a, threads, stage_bytes, stages);
+    else
+      st = nc == 1 ? launch_stages<ZT, OT, MODE, NORM, 8, 1>(s, a, threads, stage_bytes, stages)
+                   : launch_stages<ZT, OT, MODE, NORM, 8, 4>(s, a, threads, stage_bytes, stages);
+    if (st != GPTOSS_ERR_UNSUPPORTED)
+      return st;
   }
-  const int n_chunks = a.H / 8;
-  const int nc = n_chunks <= 512 ? 1 : 4;
-  int threads = ((n_chunks + nc - 1) / nc + 31) / 32 * 32;
-  if (a.k <= 4)
-    return nc == 1 ? launch_kernel<ZT, OT, MODE, NORM, 4, 1>(s, a, threads)
-                   : launch_kernel<ZT, OT, MODE, NORM, 4, 4>(s, a, threads);
-  return nc == 1 ? launch_kernel<ZT, OT, MODE, NORM, 8, 1>(s, a, threads)
-                 : launch_kernel<ZT, OT, MODE, NORM, 8, 4>(s, a, threads);
+  combine_rows_generic<ZT, OT, MODE, NORM><<<row_grid(a.T, 8), 256, 0, s>>>(
+      a.x, static_cast<const ZT *>(a.Z), a.own_row, a.topk_w, a.topk_e, a.k, a.H, a.phys_of,
+      a.norm_w, static_cast<OT *>(a.out), a.T);
+  return launch_status();
 }
 
 template <typename ZT, int MODE>

@@ -32,16 +32,18 @@ inline int launch_status() {
   return GPTOSS_ERR_CUDA;
 }
 
-// Thread blocks of `kernel` that fit on one SM at `threads` threads per block.
-// Cached per call site (the static lives in the caller's template instance).
-template <typename K> inline int blocks_per_sm(K kernel, int threads, int *cache_slot) {
-  if (*cache_slot > 0)
-    return *cache_slot;
-  int n = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, 0) != cudaSuccess || n < 1)
-    n = 1;
-  *cache_slot = n;
-  return n;
+// Thread blocks of a kernel that fit on one SM at `threads` threads and `smem`
+// bytes of dynamic shared memory per block; above the 48 KB default the
+// kernel's limit is raised first.  Remembered per (kernel, device, threads,
+// smem).  0 means it does not fit.
+int occupancy_cached(const void *kernel, int threads, size_t smem);
+
+template <typename K> inline int blocks_per_sm(K kernel, int threads, int * /*unused*/ = nullptr) {
+  const int n = occupancy_cached(reinterpret_cast<const void *>(kernel), threads, 0);
+  return n > 0 ? n : 1;
+}
+template <typename K> inline int blocks_per_sm_smem(K kernel, int threads, size_t smem) {
+  return occupancy_cached(reinterpret_cast<const void *>(kernel), threads, smem);
 }
 
 // Grid for a row-strided kernel: every SM full, never more blocks than rows.
@@ -79,14 +81,61 @@ __device__ __forceinline__ uint4 ld_table(const void *p) {
 }
 
 // Written once, not read again by this kernel.
+#ifndef GPTOSS_STORE_POLICY
+#define GPTOSS_STORE_POLICY 0 // 0: evict-first (.cs)   1: default write-back   2: no L1, write-back (.cg)
+#endif
 __device__ __forceinline__ void st_stream(void *p, uint4 v) {
+#if GPTOSS_STORE_POLICY == 0
   asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z),
                "r"(v.w)
                : "memory");
+#elif GPTOSS_STORE_POLICY == 1
+  asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+#else
+  asm volatile("st.global.cg.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w)
+               : "memory");
+#endif
 }
 
 __device__ __forceinline__ void st_stream8(void *p, uint2 v) {
   asm volatile("st.global.cs.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
+}
+
+// ---- asynchronous global -> shared copies (row staging) -------------------------
+//
+// The row kernels stage whole rows in shared memory with cp.async: a thread
+// queues 16-byte copies for rows several iterations ahead, so the bytes in
+// flight per SM are set by the shared-memory ring (100-200 KB), not by how many
+// registers a thread can spare.  Every thread only ever reads back the pieces
+// it copied itself, so cp.async.wait_group is the only synchronisation the data
+// needs (a hardware wait, not a software spin).
+
+__device__ __forceinline__ void cp_async16(void *smem_dst, const void *gmem_src) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async4(void *smem_dst, const void *gmem_src) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// Ring depth for a row kernel whose stage takes stage_bytes of shared memory:
+// deep enough to keep >= ~100 KB per SM in flight, shallow enough that two or
+// more blocks still fit on an SM (227 KB); 0 if even two stages do not fit.
+inline int pick_stages(size_t stage_bytes) {
+  if (stage_bytes * 4 <= 72 * 1024)
+    return 4;
+  if (stage_bytes * 3 <= 110 * 1024)
+    return 3;
+  if (stage_bytes * 2 <= 220 * 1024)
+    return 2;
+  return 0;
 }
 
 // ---- bf16 <-> fp32 --------------------------------------------------------------
@@ -105,8 +154,24 @@ __device__ __forceinline__ uint32_t f32_to_bf16_bits(float f) {
   return u >> 16;
 }
 
+// Two fp32 values to a bf16 pair in one instruction (round to nearest even;
+// a NaN becomes the canonical quiet NaN 0x7fff).
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-  return f32_to_bf16_bits(lo) | (f32_to_bf16_bits(hi) << 16);
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+// Fast 2^x and 1/x (about 2 ulp and 1 ulp; flush denormals), one MUFU each.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+__device__ __forceinline__ float fast_rcp(float x) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
 }
 
 // Eight consecutive values of a row held by one thread.

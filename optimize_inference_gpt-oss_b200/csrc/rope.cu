@@ -1,60 +1,152 @@
 // QKV bias add fused with YaRN RoPE (gptoss_qkv_bias_rope).
 //
 // Per row the kernel reads the fused q|k|v row once and writes it once; the
-// bias (one row) and the cos/sin row of the token's position stay in cache.
-// A work item is (head, piece): 8 consecutive elements of the head's first
-// half together with the 8 elements head_dim/2 further on -- the two halves of
-// eight rotation pairs -- so every global access is 128 bits wide and a thread
-// never needs data from another thread.  Value heads use the same items, they
-// just skip the rotation.  One thread block walks the rows with a grid stride.
+// bias (one row for the launch) and the cos/sin row of the token's position are
+// small.  A thread owns one (head, piece) item for the whole launch: 8
+// consecutive elements of the head's first half and the 8 elements head_dim/2
+// further on -- the two halves of eight rotation pairs -- so its slice of the
+// bias lives in registers, every access is 128 bits wide, and no thread needs
+// another thread's row data.  Value heads use the same items and skip the
+// rotation.  Rows are staged through a ring of shared-memory buffers filled by
+// cp.async several rows ahead (an SM keeps ~200 KB of reads outstanding); the
+// cos/sin row of each staged token travels with it, one copy per warp, so the
+// arithmetic of a row waits on nothing but its own stage.
 #include "common.cuh"
 
 namespace gptoss {
 namespace {
 
-template <typename IT, typename OT, bool EXACT, bool FMA>
+template <typename T> __device__ __forceinline__ Vec8 smem_load8(const unsigned char *p) {
+  if constexpr (sizeof(T) == 2) {
+    return widen8(*reinterpret_cast<const uint4 *>(p));
+  } else {
+    const uint4 a = *reinterpret_cast<const uint4 *>(p), b = *reinterpret_cast<const uint4 *>(p + 16);
+    Vec8 v;
+    v.v[0] = __uint_as_float(a.x), v.v[1] = __uint_as_float(a.y), v.v[2] = __uint_as_float(a.z),
+    v.v[3] = __uint_as_float(a.w), v.v[4] = __uint_as_float(b.x), v.v[5] = __uint_as_float(b.y),
+    v.v[6] = __uint_as_float(b.z), v.v[7] = __uint_as_float(b.w);
+    return v;
+  }
+}
+
+template <bool EXACT, bool FMA>
+__device__ __forceinline__ void rotate8(Vec8 &a, Vec8 &b, const Vec8 &c, const Vec8 &s) {
+#pragma unroll
+  for (int i = 0; i < 8; i++) {
+    const float x1 = a.v[i], x2 = b.v[i];
+    if (EXACT && !FMA) { // run.cpp:519-520 built without FMA: four products, then -, +
+      a.v[i] = __fsub_rn(__fmul_rn(x1, c.v[i]), __fmul_rn(x2, s.v[i]));
+      b.v[i] = __fadd_rn(__fmul_rn(x2, c.v[i]), __fmul_rn(x1, s.v[i]));
+    } else { // the reference's GPU form (kernels/fast_common.hpp:25-28)
+      a.v[i] = __fmaf_rn(x1, c.v[i], -__fmul_rn(x2, s.v[i]));
+      b.v[i] = __fmaf_rn(x2, c.v[i], __fmul_rn(x1, s.v[i]));
+    }
+  }
+}
+
+// blockDim.x >= n_heads * (head_dim / 16); thread t owns item t.
+// Stage layout: [row: width * sizeof(IT)] [per warp: cos (half floats), sin (half floats)].
+template <typename IT, typename OT, bool EXACT, bool FMA, int STAGES>
 __global__ void bias_rope_rows(const IT *qkv_in, long in_stride, const float *__restrict__ bias,
                                const int *__restrict__ pos, int pos_scalar,
                                const float *__restrict__ cos_tab,
                                const float *__restrict__ sin_tab, int n_pos, int n_rot_heads,
                                int n_heads, int head_dim, OT *qkv_out, long out_stride, int T) {
+  constexpr int SI = sizeof(IT);
+  extern __shared__ __align__(16) unsigned char ring[];
   const int half = head_dim >> 1, pieces = half >> 3, items = n_heads * pieces;
-  for (int row = blockIdx.x; row < T; row += gridDim.x) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+  const size_t row_bytes = (size_t)n_heads * head_dim * SI;
+  const size_t trig_bytes = (size_t)half * 8; // cos + sin of one position
+  const size_t stage_bytes = row_bytes + (size_t)n_warps * trig_bytes;
+
+  const bool active = (int)threadIdx.x < items;
+  const int head = active ? threadIdx.x / pieces : 0, piece = active ? threadIdx.x - head * pieces : 0;
+  const size_t lo = (size_t)head * head_dim + piece * 8, hi = lo + half;
+  const bool rotates = head < n_rot_heads;
+  Vec8 ba, bb;
+#pragma unroll
+  for (int i = 0; i < 8; i++)
+    ba.v[i] = bb.v[i] = 0.0f;
+  if (bias && active) {
+    ba = load8<kTable>(bias, lo);
+    bb = load8<kTable>(bias, hi);
+  }
+
+  auto position = [&](long row) {
     int p = pos ? __ldg(pos + row) : pos_scalar;
-    p = p < 0 ? 0 : (p >= n_pos ? n_pos - 1 : p);
-    const float *cs = cos_tab + (size_t)p * half, *sn = sin_tab + (size_t)p * half;
-    const IT *in = qkv_in + (size_t)row * in_stride;
-    OT *out = qkv_out + (size_t)row * out_stride;
-    for (int item = threadIdx.x; item < items; item += blockDim.x) {
-      const int head = item / pieces, piece = item - head * pieces;
-      const size_t lo = (size_t)head * head_dim + piece * 8, hi = lo + half;
-      Vec8 a = load8<kStream>(in, lo), b = load8<kStream>(in, hi);
+    return p < 0 ? 0 : (p >= n_pos ? n_pos - 1 : p);
+  };
+  auto issue = [&](long row, int stage, int p) {
+    unsigned char *sr = ring + (size_t)stage * stage_bytes;
+    if (active) {
+      const IT *in = qkv_in + (size_t)row * in_stride;
+      cp_async16(sr + lo * SI, in + lo);
+      cp_async16(sr + hi * SI, in + hi);
+      if constexpr (SI == 4) {
+        cp_async16(sr + lo * SI + 16, in + lo + 4);
+        cp_async16(sr + hi * SI + 16, in + hi + 4);
+      }
+    }
+    // this warp's copy of the token's cos and sin rows: 16-byte pieces, one per lane
+    unsigned char *st = sr + row_bytes + (size_t)warp * trig_bytes;
+    const int per_table = half >> 2;
+    for (int q = lane; q < 2 * per_table; q += 32) {
+      const float *src = q < per_table ? cos_tab + (size_t)p * half + q * 4
+                                       : sin_tab + (size_t)p * half + (q - per_table) * 4;
+      cp_async16(st + (size_t)q * 16, src);
+    }
+  };
+
+  const long step = gridDim.x;
+  long row = blockIdx.x;
+  if (row >= T)
+    return;
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; s++) {
+    if (row + s * step < T)
+      issue(row + s * step, s, position(row + s * step));
+    cp_async_commit();
+  }
+  int ahead_pos = (row + (STAGES - 1) * step < T) ? position(row + (STAGES - 1) * step) : 0;
+  int stage = 0;
+  for (; row < T; row += step) {
+    {
+      const long ahead = row + (STAGES - 1) * step;
+      const int fill = stage == 0 ? STAGES - 1 : stage - 1;
+      if (ahead < T)
+        issue(ahead, fill, ahead_pos);
+      cp_async_commit();
+    }
+    if (row + STAGES * step < T)
+      ahead_pos = position(row + STAGES * step);
+    cp_async_wait<STAGES - 1>();
+    __syncwarp(); // the cos/sin pieces were copied by other lanes of this warp
+
+    if (active) {
+      const unsigned char *sr = ring + (size_t)stage * stage_bytes;
+      Vec8 a = smem_load8<IT>(sr + lo * SI), b = smem_load8<IT>(sr + hi * SI);
       if (bias) {
-        const Vec8 ba = load8<kTable>(bias, lo), bb = load8<kTable>(bias, hi);
 #pragma unroll
         for (int i = 0; i < 8; i++) {
           a.v[i] = __fadd_rn(a.v[i], ba.v[i]);
           b.v[i] = __fadd_rn(b.v[i], bb.v[i]);
         }
       }
-      if (head < n_rot_heads) {
-        const Vec8 c = load8<kTable>(cs, piece * 8), s = load8<kTable>(sn, piece * 8);
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-          const float x1 = a.v[i], x2 = b.v[i];
-          if (EXACT && !FMA) { // run.cpp:519-520 built without FMA: four products, then -, +
-            a.v[i] = __fsub_rn(__fmul_rn(x1, c.v[i]), __fmul_rn(x2, s.v[i]));
-            b.v[i] = __fadd_rn(__fmul_rn(x2, c.v[i]), __fmul_rn(x1, s.v[i]));
-          } else { // the reference's GPU form (kernels/fast_common.hpp:25-28)
-            a.v[i] = __fmaf_rn(x1, c.v[i], -__fmul_rn(x2, s.v[i]));
-            b.v[i] = __fmaf_rn(x2, c.v[i], __fmul_rn(x1, s.v[i]));
-          }
-        }
+      if (rotates) {
+        const unsigned char *st = sr + row_bytes + (size_t)warp * trig_bytes;
+        const Vec8 c = smem_load8<float>(st + (size_t)piece * 32);
+        const Vec8 s = smem_load8<float>(st + (size_t)half * 4 + (size_t)piece * 32);
+        rotate8<EXACT, FMA>(a, b, c, s);
       }
+      OT *out = qkv_out + (size_t)row * out_stride;
       store8(out, lo, a);
       store8(out, hi, b);
     }
+    __syncwarp(); // all lanes are done with this stage's cos/sin before it is refilled
+    stage = stage + 1 == STAGES ? 0 : stage + 1;
   }
+  cp_async_wait<0>();
 }
 
 // Any head_dim (even) and alignment: one rotation pair per thread step.
@@ -111,29 +203,44 @@ struct Args {
   int T;
 };
 
+template <typename IT, typename OT, bool EXACT, bool FMA, int STAGES>
+int launch_pipe(cudaStream_t s, const Args &a, int threads, size_t smem) {
+  auto k = bias_rope_rows<IT, OT, EXACT, FMA, STAGES>;
+  const int per_sm = blocks_per_sm_smem(k, threads, smem);
+  if (per_sm < 1)
+    return GPTOSS_ERR_UNSUPPORTED;
+  k<<<row_grid(a.T, per_sm), threads, smem, s>>>(
+      static_cast<const IT *>(a.in), a.in_stride, a.bias, a.pos, a.pos_scalar, a.cos_tab, a.sin_tab,
+      a.n_pos, a.n_q + a.n_kv, a.n_q + 2 * a.n_kv, a.head_dim, static_cast<OT *>(a.out),
+      a.out_stride, a.T);
+  return launch_status();
+}
+
 template <typename IT, typename OT, bool EXACT, bool FMA> int launch(cudaStream_t s, const Args &a) {
   const int n_heads = a.n_q + 2 * a.n_kv, n_rot = a.n_q + a.n_kv;
-  const IT *in = static_cast<const IT *>(a.in);
-  OT *out = static_cast<OT *>(a.out);
   const bool vec = a.head_dim % 16 == 0 && aligned16(a.in) && aligned16(a.out) &&
                    (a.in_stride * sizeof(IT)) % 16 == 0 && (a.out_stride * sizeof(OT)) % 16 == 0 &&
                    (!a.bias || aligned16(a.bias)) && aligned16(a.cos_tab) && aligned16(a.sin_tab) &&
                    (a.head_dim / 2 * sizeof(float)) % 16 == 0;
-  if (!vec) {
-    bias_rope_rows_generic<IT, OT, EXACT, FMA><<<row_grid(a.T, 8), 256, 0, s>>>(
-        in, a.in_stride, a.bias, a.pos, a.pos_scalar, a.cos_tab, a.sin_tab, a.n_pos, n_rot, n_heads,
-        a.head_dim, out, a.out_stride, a.T);
-    return launch_status();
-  }
   const int items = n_heads * (a.head_dim / 16);
-  int threads = (items + 31) / 32 * 32;
-  if (threads > 512)
-    threads = 512;
-  static int occ[17];
-  auto k = bias_rope_rows<IT, OT, EXACT, FMA>;
-  k<<<row_grid(a.T, blocks_per_sm(k, threads, &occ[threads / 32])), threads, 0, s>>>(
-      in, a.in_stride, a.bias, a.pos, a.pos_scalar, a.cos_tab, a.sin_tab, a.n_pos, n_rot, n_heads,
-      a.head_dim, out, a.out_stride, a.T);
+  if (vec && items <= 1024) {
+    const int threads = (items + 31) / 32 * 32;
+    const size_t stage_bytes = (size_t)n_heads * a.head_dim * sizeof(IT) +
+                               (size_t)(threads / 32) * (size_t)a.head_dim * 4;
+    const int stages = pick_stages(stage_bytes);
+    int st = GPTOSS_ERR_UNSUPPORTED;
+    if (stages == 4)
+      st = launch_pipe<IT, OT, EXACT, FMA, 4>(s, a, threads, stage_bytes * 4);
+    else if (stages == 3)
+      st = launch_pipe<IT, OT, EXACT, FMA, 3>(s, a, threads, stage_bytes * 3);
+    else if (stages == 2)
+      st = launch_pipe<IT, OT, EXACT, FMA, 2>(s, a, threads, stage_bytes * 2);
+    if (st != GPTOSS_ERR_UNSUPPORTED)
+      return st;
+  }
+  bias_rope_rows_generic<IT, OT, EXACT, FMA><<<row_grid(a.T, 8), 256, 0, s>>>(
+      static_cast<const IT *>(a.in), a.in_stride, a.bias, a.pos, a.pos_scalar, a.cos_tab, a.sin_tab,
+      a.n_pos, n_rot, n_heads, a.head_dim, static_cast<OT *>(a.out), a.out_stride, a.T);
   return launch_status();
 }
 

@@ -1,5 +1,7 @@
 // Library-wide host helpers: version, status text, per-thread CUDA error memory,
 // cached device properties.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace gptoss {
@@ -20,6 +22,41 @@ int sm_count() {
     cached[dev] = n;
   }
   return cached[dev];
+}
+
+int occupancy_cached(const void *kernel, int threads, size_t smem) {
+  struct Entry {
+    const void *fn;
+    int dev, threads;
+    size_t smem;
+    int blocks;
+  };
+  static std::mutex mu;
+  static Entry table[512];
+  static int used = 0;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess)
+    return 0;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    for (int i = 0; i < used; i++)
+      if (table[i].fn == kernel && table[i].dev == dev && table[i].threads == threads &&
+          table[i].smem == smem)
+        return table[i].blocks;
+  }
+  int blocks = 0;
+  if (smem > 48 * 1024 &&
+      cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+    (void)cudaGetLastError();
+    blocks = 0;
+  } else if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, kernel, threads, smem) != cudaSuccess) {
+    (void)cudaGetLastError();
+    blocks = 0;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  if (used < 512)
+    table[used++] = Entry{kernel, dev, threads, smem, blocks};
+  return blocks;
 }
 
 } // namespace gptoss

@@ -5,14 +5,19 @@
 // row length, so the kernel runs over flat groups of 8 outputs: two (bf16) or
 // four (fp32) 128-bit loads in, one or two 128-bit stores out.  Each thread
 // fetches kUnroll groups before computing, which keeps 64-256 B of loads in
-// flight per thread.
+// flight per thread.  The fast form costs about 13 instructions per output (two
+// of them on the special-function unit), which at 4 outputs per 24 bytes moved
+// keeps the SM's issue slots well below the memory time.
 #include "common.cuh"
 #include "exact_math.cuh"
 
 namespace gptoss {
 namespace {
 
-constexpr int kUnroll = 2;
+#ifndef GPTOSS_SWIGLU_UNROLL
+#define GPTOSS_SWIGLU_UNROLL 2
+#endif
+constexpr int kUnroll = GPTOSS_SWIGLU_UNROLL;
 
 template <bool EXACT> __device__ __forceinline__ float swiglu_one(float g, float u, float limit) {
   if (EXACT) { // run.cpp:709-722, every step rounded to fp32
@@ -26,41 +31,54 @@ template <bool EXACT> __device__ __forceinline__ float swiglu_one(float g, float
     g = __fmul_rn(g, sig);
     return __fmul_rn(g, __fadd_rn(u, 1.0f));
   }
-  // the reference's fast form (kernels/fast_misc.hpp:136-139)
+  // the reference's fast form (kernels/fast_misc.hpp:136-139):
+  // g / (1 + e^(-1.702 g)) * (u + 1), with e^x as 2^(x log2 e)
   g = fminf(g, limit);
   u = fminf(fmaxf(u, -limit), limit);
-  g = __fdividef(g, 1.0f + __expf(-1.702f * g));
-  return g * (u + 1.0f);
+  const float e = fast_exp2(g * (-1.702f * 1.44269504088896341f));
+  return (g * fast_rcp(1.0f + e)) * (u + 1.0f);
 }
 
+// One group = 8 outputs = 16 inputs: kIn 16-byte loads (2 for bf16, 4 for fp32),
+// kept as loaded until they are used.  One-shot grid: block b owns groups
+// [b * 256 * kUnroll, (b + 1) * 256 * kUnroll), a contiguous tile, and exits;
+// the hardware scheduler keeps every SM stocked with fresh blocks, which
+// measured ~10 % faster on B200 than a grid-stride loop over the same data.
 template <typename YT, typename GT, bool EXACT>
-__global__ void swiglu_flat(const YT *__restrict__ Y, GT *__restrict__ G, size_t n_groups,
-                            float limit) {
-  const size_t stride = (size_t)gridDim.x * blockDim.x;
-  for (size_t base = (size_t)blockIdx.x * blockDim.x + threadIdx.x; base < n_groups;
-       base += stride * kUnroll) {
-    Vec8 lo[kUnroll], hi[kUnroll];
-    bool live[kUnroll];
+__global__ void __launch_bounds__(256)
+    swiglu_flat(const YT *__restrict__ Y, GT *__restrict__ G, size_t n_groups, float limit) {
+  constexpr int kIn = sizeof(YT);         // 16-byte loads per group
+  constexpr int kPer = 16 / sizeof(YT);   // inputs per load
+  const size_t base = (size_t)blockIdx.x * (256 * kUnroll) + threadIdx.x;
+  uint4 raw[kUnroll][kIn];
 #pragma unroll
-    for (int u = 0; u < kUnroll; u++) {
-      const size_t g = base + u * stride;
-      live[u] = g < n_groups;
-      if (live[u]) {
-        lo[u] = load8<kStream>(Y, g * 16);
-        hi[u] = load8<kStream>(Y, g * 16 + 8);
+  for (int u = 0; u < kUnroll; u++) {
+    // past the end: fetch the last group again; its result is not stored
+    const size_t g = base + u * 256 < n_groups ? base + u * 256 : n_groups - 1;
+#pragma unroll
+    for (int j = 0; j < kIn; j++)
+      raw[u][j] = ld_stream(Y + g * 16 + j * kPer);
+  }
+#pragma unroll
+  for (int u = 0; u < kUnroll; u++) {
+    Vec8 o;
+    if constexpr (sizeof(YT) == 2) { // each 32-bit word holds one (gate, up) pair
+#pragma unroll
+      for (int j = 0; j < 2; j++) {
+        const uint32_t w[4] = {raw[u][j].x, raw[u][j].y, raw[u][j].z, raw[u][j].w};
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+          o.v[4 * j + i] = swiglu_one<EXACT>(bf16_lo(w[i]), bf16_hi(w[i]), limit);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        o.v[2 * j] = swiglu_one<EXACT>(__uint_as_float(raw[u][j].x), __uint_as_float(raw[u][j].y), limit);
+        o.v[2 * j + 1] = swiglu_one<EXACT>(__uint_as_float(raw[u][j].z), __uint_as_float(raw[u][j].w), limit);
       }
     }
-#pragma unroll
-    for (int u = 0; u < kUnroll; u++)
-      if (live[u]) {
-        Vec8 o;
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-          o.v[i] = swiglu_one<EXACT>(lo[u].v[2 * i], lo[u].v[2 * i + 1], limit);
-          o.v[4 + i] = swiglu_one<EXACT>(hi[u].v[2 * i], hi[u].v[2 * i + 1], limit);
-        }
-        store8(G, (base + u * stride) * 8, o);
-      }
+    if (base + u * 256 < n_groups)
+      store8(G, (base + u * 256) * 8, o);
   }
 }
 
@@ -80,11 +98,10 @@ int launch(cudaStream_t s, const void *Y, void *G, size_t n_out, float limit) {
   constexpr int threads = 256;
   size_t n_groups = (aligned16(Y) && aligned16(G)) ? n_out / 8 : 0;
   if (n_groups > 0) {
-    static int occ = 0;
-    auto k = swiglu_flat<YT, GT, EXACT>;
-    const size_t want = (n_groups + (size_t)threads * kUnroll - 1) / ((size_t)threads * kUnroll);
-    k<<<row_grid((long)want, blocks_per_sm(k, threads, &occ)), threads, 0, s>>>(yp, gp, n_groups,
-                                                                                limit);
+    const size_t blocks = (n_groups + (size_t)threads * kUnroll - 1) / ((size_t)threads * kUnroll);
+    if (blocks > 0x7fffffffull)
+      return GPTOSS_ERR_UNSUPPORTED;
+    swiglu_flat<YT, GT, EXACT><<<(unsigned)blocks, threads, 0, s>>>(yp, gp, n_groups, limit);
     const int st = launch_status();
     if (st != GPTOSS_OK)
       return st;
