@@ -30,6 +30,14 @@
  *   GPTOSS_FMA    with GPTOSS_EXACT: contract x1*c - x2*s, x2*c + x1*s and
  *                 agg += z*w into fused multiply-adds, as a CPU build with
  *                 -march=native and the reference's *_exact HIP kernels do.
+ *
+ * Launch option (flags), independent of the arithmetic:
+ *   GPTOSS_PDL    launch with programmatic stream serialization: the kernel's
+ *                 thread blocks may be scheduled while the previous kernel in
+ *                 the stream is still finishing, which hides the launch gap
+ *                 between short kernels.  Results do not change: every kernel
+ *                 starts with a grid-dependency wait and reads nothing, not
+ *                 even its tables, before the previous kernel has completed.
  */
 #ifndef GPTOSS_KERNELS_H
 #define GPTOSS_KERNELS_H
@@ -65,6 +73,7 @@ enum {
 enum {
   GPTOSS_EXACT = 1u,
   GPTOSS_FMA = 2u,
+  GPTOSS_PDL = 4u,
 };
 
 #define GPTOSS_MAX_TOPK 8      /* k of the router and of the combine */
@@ -88,7 +97,7 @@ GPTOSS_API int gptoss_last_cuda_error(void);
  */
 GPTOSS_API int gptoss_embed(gptoss_stream_t stream, int T, const void *table,
                             gptoss_dtype_t table_dtype, int V, const int *ids, void *x,
-                            gptoss_dtype_t x_dtype, int H);
+                            gptoss_dtype_t x_dtype, int H, unsigned flags);
 
 /*
  * Residual add fused with RMSNorm (eps 1e-5):
@@ -145,7 +154,8 @@ GPTOSS_API int gptoss_qkv_bias_rope(gptoss_stream_t stream, int T, const void *q
  */
 GPTOSS_API int gptoss_router_topk(gptoss_stream_t stream, int T, const void *logits,
                                   gptoss_dtype_t logits_dtype, int E, int k, float *topk_w,
-                                  int *topk_e, const int *done, const int *slot_of);
+                                  int *topk_e, const int *done, const int *slot_of,
+                                  unsigned flags);
 
 /*
  * Clamped SwiGLU on R rows of interleaved gate/up values:
@@ -198,7 +208,7 @@ GPTOSS_API int gptoss_moe_combine(gptoss_stream_t stream, int T, float *x, const
  */
 GPTOSS_API int gptoss_argmax(gptoss_stream_t stream, int T, const void *logits,
                              gptoss_dtype_t logits_dtype, long V, long row_stride,
-                             unsigned long long *keys, int *out);
+                             unsigned long long *keys, int *out, unsigned flags);
 
 /* How many slices (thread blocks) gptoss_argmax cuts each row into for T rows
  * of V logits on the current device; has_keys = 0 describes a call with

@@ -23,7 +23,7 @@ INCLUDE_DIR = os.path.join(os.path.dirname(_HERE), "include")
 
 F32, BF16 = 0, 1
 OK, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_CUDA = 0, 1, 2, 3
-EXACT, FMA = 1, 2
+EXACT, FMA, PDL = 1, 2, 4
 MAX_TOPK, MAX_EXPERTS = 8, 256
 
 # gptoss_chain_buffer_t
@@ -61,13 +61,13 @@ PROTOTYPES = {
     "gptoss_version": (C.c_char_p, []),
     "gptoss_status_string": (C.c_char_p, [_i]),
     "gptoss_last_cuda_error": (_i, []),
-    "gptoss_embed": (_i, [_p, _i, _p, _i, _i, _p, _p, _i, _i]),
+    "gptoss_embed": (_i, [_p, _i, _p, _i, _i, _p, _p, _i, _i, _u]),
     "gptoss_add_rmsnorm": (_i, [_p, _i, _p, _p, _i, _p, _p, _i, _i, _u]),
     "gptoss_qkv_bias_rope": (_i, [_p, _i, _p, _i, _l, _p, _p, _i, _p, _p, _i, _i, _i, _i, _p, _i, _l, _u]),
-    "gptoss_router_topk": (_i, [_p, _i, _p, _i, _i, _i, _p, _p, _p, _p]),
+    "gptoss_router_topk": (_i, [_p, _i, _p, _i, _i, _i, _p, _p, _p, _p, _u]),
     "gptoss_swiglu": (_i, [_p, _p, _i, _p, _i, _z, _i, _f, _u]),
     "gptoss_moe_combine": (_i, [_p, _i, _p, _p, _i, _p, _p, _p, _i, _i, _p, _p, _p, _i, _u]),
-    "gptoss_argmax": (_i, [_p, _i, _p, _i, _l, _l, _p, _p]),
+    "gptoss_argmax": (_i, [_p, _i, _p, _i, _l, _l, _p, _p, _u]),
     "gptoss_argmax_slices": (_i, [_i, _l, _i, _i]),
     "gptoss_argmax_noalloc": (_i, [_p, _i, _p, _i, _l, _l, _p]),
     "gptoss_device_count": (_i, [C.POINTER(_i)]),
@@ -231,8 +231,8 @@ def _ptr(x):
 
 # ---- the kernels (device pointers in, status checked) ----------------------------
 
-def embed(T, table, table_dtype, V, ids, x, x_dtype, H, stream=None):
-    check(load().gptoss_embed(stream, T, _ptr(table), table_dtype, V, _ptr(ids), _ptr(x), x_dtype, H), "embed")
+def embed(T, table, table_dtype, V, ids, x, x_dtype, H, flags=0, stream=None):
+    check(load().gptoss_embed(stream, T, _ptr(table), table_dtype, V, _ptr(ids), _ptr(x), x_dtype, H, flags), "embed")
 
 
 def add_rmsnorm(T, x, y, y_dtype, weight, out, out_dtype, H, flags=0, stream=None):
@@ -247,9 +247,9 @@ def qkv_bias_rope(T, qkv_in, in_dtype, in_stride, bias, pos, pos_scalar, cos_tab
                                       head_dim, _ptr(qkv_out), out_dtype, out_stride, flags), "qkv_bias_rope")
 
 
-def router_topk(T, logits, dtype, E, k, topk_w, topk_e, done=None, slot_of=None, stream=None):
+def router_topk(T, logits, dtype, E, k, topk_w, topk_e, done=None, slot_of=None, flags=0, stream=None):
     check(load().gptoss_router_topk(stream, T, _ptr(logits), dtype, E, k, _ptr(topk_w), _ptr(topk_e),
-                                    _ptr(done), _ptr(slot_of)), "router_topk")
+                                    _ptr(done), _ptr(slot_of), flags), "router_topk")
 
 
 def swiglu(Y, y_dtype, G, g_dtype, R, I, limit=7.0, flags=0, stream=None):
@@ -263,8 +263,8 @@ def moe_combine(T, x, Z, z_dtype, own_row, topk_w, topk_e, k, H, phys_of=None, n
                                     flags), "moe_combine")
 
 
-def argmax(T, logits, dtype, V, row_stride, keys, out, stream=None):
-    check(load().gptoss_argmax(stream, T, _ptr(logits), dtype, V, row_stride, _ptr(keys), _ptr(out)), "argmax")
+def argmax(T, logits, dtype, V, row_stride, keys, out, flags=0, stream=None):
+    check(load().gptoss_argmax(stream, T, _ptr(logits), dtype, V, row_stride, _ptr(keys), _ptr(out), flags), "argmax")
 
 
 ARGMAX_NOALLOC_MAX_ROWS = 16384

@@ -100,6 +100,7 @@ template <typename LT>
 __global__ void __launch_bounds__(kThreads)
     argmax_slices(const LT *__restrict__ logits, long V, long row_stride, long pieces_per_row,
                   long pieces_per_slice, unsigned long long *keys, int *__restrict__ out) {
+  pdl_prologue();
   constexpr int kPer = 16 / sizeof(LT); // values per 16-byte piece
   __shared__ unsigned long long scratch[kThreads / 32];
   const int row = blockIdx.y;
@@ -151,6 +152,7 @@ __global__ void __launch_bounds__(kThreads)
 template <typename LT>
 __global__ void argmax_finish(unsigned long long *keys, const LT *__restrict__ logits,
                               long row_stride, int T, int *__restrict__ out) {
+  pdl_prologue();
   const int row = blockIdx.x * blockDim.x + threadIdx.x;
   if (row >= T)
     return;
@@ -186,12 +188,12 @@ int launch(cudaStream_t s, int T, const void *logits, long V, long row_stride,
   if (per_slice < 1)
     per_slice = 1;
   unsigned long long *merge = splits > 1 ? keys : nullptr;
-  argmax_slices<LT><<<dim3(splits, T), kThreads, 0, s>>>(lp, V, row_stride, pieces, per_slice, merge,
+  launch_kernel(argmax_slices<LT>, dim3(splits, T), dim3(kThreads), 0, s, lp, V, row_stride, pieces, per_slice, merge,
                                                         out);
   int st = launch_status();
   if (st != GPTOSS_OK || !merge)
     return st;
-  argmax_finish<LT><<<(T + 255) / 256, 256, 0, s>>>(keys, lp, row_stride, T, out);
+  launch_kernel(argmax_finish<LT>, dim3((T + 255) / 256), dim3(256), 0, s, keys, lp, row_stride, T, out);
   return launch_status();
 }
 
@@ -200,8 +202,9 @@ int launch(cudaStream_t s, int T, const void *logits, long V, long row_stride,
 
 extern "C" int gptoss_argmax(gptoss_stream_t stream, int T, const void *logits,
                              gptoss_dtype_t logits_dtype, long V, long row_stride,
-                             unsigned long long *keys, int *out) {
+                             unsigned long long *keys, int *out, unsigned flags) {
   using namespace gptoss;
+  const PdlScope pdl(flags);
   if (T < 0 || V <= 0 || V > 0x7fffffffL || row_stride < V || !valid_dtype(logits_dtype))
     return GPTOSS_ERR_BAD_ARG;
   if (T == 0)

@@ -37,7 +37,8 @@ struct gptoss_chain {
   unsigned long long *keys = nullptr;
   void *flush = nullptr;
   size_t flush_bytes = 0;
-  std::map<int, cudaGraphExec_t> graphs;
+  std::map<int, cudaGraphExec_t> graphs;                       // whole step, per T
+  std::map<std::pair<int, int>, cudaGraphExec_t> kind_graphs; // one kernel kind's launches, per (T, kind)
   std::vector<cudaEvent_t> events;
 
   size_t act() const { return cfg.act_dtype == GPTOSS_F32 ? 4 : 2; }
@@ -132,7 +133,7 @@ int issue_step(gptoss_chain *c, int T, cudaStream_t s, Hook *hook, int only = -1
   const int H = g.hidden, L = g.n_layers, K = g.top_k, QKV = c->qkv_dim();
   gptoss_stream_t gs = s;
   // step_embed: x = embedding[tokens]
-  STEP(GPTOSS_K_EMBED, gptoss_embed(gs, T, c->embedding, a, g.vocab, c->tokens, c->x, GPTOSS_F32, H));
+  STEP(GPTOSS_K_EMBED, gptoss_embed(gs, T, c->embedding, a, g.vocab, c->tokens, c->x, GPTOSS_F32, H, g.flags));
   // layer 0's attention norm; later layers get theirs from the previous combine
   STEP(GPTOSS_K_NORM, gptoss_add_rmsnorm(gs, T, c->x, nullptr, a, c->gain_attn, c->normed, a, H, g.flags));
   for (int l = 0; l < L; l++) {
@@ -149,7 +150,7 @@ int issue_step(gptoss_chain *c, int T, cudaStream_t s, Hook *hook, int only = -1
                             g.flags));
     // [router GEMM] -> stand-in logits; top-k + softmax
     STEP(GPTOSS_K_ROUTER, gptoss_router_topk(gs, T, layer_ptr(c, GPTOSS_BUF_ROUTER, l), a,
-                                             g.n_experts, K, c->topk_w, c->topk_e, nullptr, nullptr));
+                                             g.n_experts, K, c->topk_w, c->topk_e, nullptr, nullptr, g.flags));
     // [mlp1 GEMM] -> stand-in gate/up rows; SwiGLU
     STEP(GPTOSS_K_SWIGLU, gptoss_swiglu(gs, layer_ptr(c, GPTOSS_BUF_MLP1, l), a, c->swiglu, a,
                                         (size_t)K * T, g.inter, g.swiglu_limit, g.flags));
@@ -161,7 +162,7 @@ int issue_step(gptoss_chain *c, int T, cudaStream_t s, Hook *hook, int only = -1
                             c->topk_e, K, H, nullptr, next_gain, c->normed, a, g.flags));
   }
   // [LM-head GEMM of `normed`] -> stand-in logits; greedy pick
-  STEP(GPTOSS_K_ARGMAX, gptoss_argmax(gs, T, c->logits, a, g.vocab, g.vocab, c->keys, c->next));
+  STEP(GPTOSS_K_ARGMAX, gptoss_argmax(gs, T, c->logits, a, g.vocab, g.vocab, c->keys, c->next, g.flags));
   return GPTOSS_OK;
 }
 
@@ -315,6 +316,8 @@ int gptoss_chain_destroy(gptoss_chain_t *c) {
     (void)cudaStreamSynchronize(c->stream);
   for (auto &kv : c->graphs)
     (void)cudaGraphExecDestroy(kv.second);
+  for (auto &kv : c->kind_graphs)
+    (void)cudaGraphExecDestroy(kv.second);
   for (cudaEvent_t e : c->events)
     (void)cudaEventDestroy(e);
   for (void *p : c->allocs)
@@ -412,6 +415,31 @@ int gptoss_chain_fill_synthetic(gptoss_chain_t *c, int T, uint64_t seed, int thr
   return st;
 }
 
+// Captures the launches of one step (only < 0) or of one kernel kind into a graph.
+static int capture_step(gptoss_chain *c, int T, int only, cudaGraphExec_t *exec_out) {
+  // Warm every kernel once outside capture (occupancy queries, lazy module load).
+  int st = issue_step(c, T, c->stream, nullptr, only);
+  if (st != GPTOSS_OK)
+    return st;
+  st = cuda_status(cudaStreamSynchronize(c->stream));
+  if (st != GPTOSS_OK)
+    return st;
+  st = cuda_status(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
+  if (st != GPTOSS_OK)
+    return st;
+  const int issued = issue_step(c, T, c->stream, nullptr, only);
+  cudaGraph_t graph = nullptr;
+  st = cuda_status(cudaStreamEndCapture(c->stream, &graph));
+  if (issued != GPTOSS_OK || st != GPTOSS_OK) {
+    if (graph)
+      (void)cudaGraphDestroy(graph);
+    return issued != GPTOSS_OK ? issued : st;
+  }
+  st = cuda_status(cudaGraphInstantiate(exec_out, graph, 0));
+  (void)cudaGraphDestroy(graph);
+  return st;
+}
+
 int gptoss_chain_enqueue(gptoss_chain_t *c, int T, int use_graph) {
   if (!c || T < 0 || T > c->max_tokens)
     return GPTOSS_ERR_BAD_ARG;
@@ -421,27 +449,8 @@ int gptoss_chain_enqueue(gptoss_chain_t *c, int T, int use_graph) {
     return issue_step(c, T, c->stream, nullptr);
   auto it = c->graphs.find(T);
   if (it == c->graphs.end()) {
-    // Warm every kernel once outside capture (occupancy queries, lazy module load).
-    int st = issue_step(c, T, c->stream, nullptr);
-    if (st != GPTOSS_OK)
-      return st;
-    st = cuda_status(cudaStreamSynchronize(c->stream));
-    if (st != GPTOSS_OK)
-      return st;
-    st = cuda_status(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
-    if (st != GPTOSS_OK)
-      return st;
-    const int issued = issue_step(c, T, c->stream, nullptr);
-    cudaGraph_t graph = nullptr;
-    st = cuda_status(cudaStreamEndCapture(c->stream, &graph));
-    if (issued != GPTOSS_OK || st != GPTOSS_OK) {
-      if (graph)
-        (void)cudaGraphDestroy(graph);
-      return issued != GPTOSS_OK ? issued : st;
-    }
     cudaGraphExec_t exec = nullptr;
-    st = cuda_status(cudaGraphInstantiate(&exec, graph, 0));
-    (void)cudaGraphDestroy(graph);
+    const int st = capture_step(c, T, -1, &exec);
     if (st != GPTOSS_OK)
       return st;
     it = c->graphs.emplace(T, exec).first;
@@ -477,8 +486,9 @@ int gptoss_chain_profile(gptoss_chain_t *c, int T, int steps, int mode, double *
     launches_per_kind[k] = 0;
   }
   if (mode == 2) {
-    // One event pair around all of a kind's launches of a step, issued back to back:
-    // the per-launch cost of recording events is spread over the batch.
+    // One event pair around all of a kind's launches of a step, replayed from a graph
+    // captured for that kind alone: launches sit as close together as they do in the
+    // whole-step graph, and the cost of the two event records is spread over the batch.
     const int per_step[GPTOSS_K_COUNT] = {1, 1, c->cfg.n_layers, c->cfg.n_layers, c->cfg.n_layers,
                                           c->cfg.n_layers, c->cfg.n_layers, 1};
     while (c->events.size() < 2) {
@@ -488,11 +498,19 @@ int gptoss_chain_profile(gptoss_chain_t *c, int T, int steps, int mode, double *
         return st;
       c->events.push_back(e);
     }
+    for (int kind = 0; kind < GPTOSS_K_COUNT; kind++)
+      if (!c->kind_graphs.count({T, kind})) {
+        cudaGraphExec_t exec = nullptr;
+        const int st = capture_step(c, T, kind, &exec);
+        if (st != GPTOSS_OK)
+          return st;
+        c->kind_graphs[{T, kind}] = exec;
+      }
     for (int s = 0; s < steps; s++)
       for (int kind = 0; kind < GPTOSS_K_COUNT; kind++) {
         int st = cuda_status(cudaEventRecord(c->events[0], c->stream));
         if (st == GPTOSS_OK)
-          st = issue_step(c, T, c->stream, nullptr, kind);
+          st = cuda_status(cudaGraphLaunch(c->kind_graphs[{T, kind}], c->stream));
         if (st == GPTOSS_OK)
           st = cuda_status(cudaEventRecord(c->events[1], c->stream));
         if (st == GPTOSS_OK)

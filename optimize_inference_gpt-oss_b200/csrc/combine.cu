@@ -42,6 +42,7 @@ __global__ void combine_rows(float *x, const ZT *__restrict__ Z, const int *__re
                              const float *__restrict__ topk_w, const int *__restrict__ topk_e,
                              int k, int H, const int *__restrict__ phys_of,
                              const float *__restrict__ norm_w, OT *__restrict__ out, int T) {
+  pdl_prologue();
   constexpr bool EXACT = MODE != 0;
   constexpr int SZ = sizeof(ZT);
   using Acc = typename std::conditional<EXACT, double, float>::type;
@@ -269,6 +270,7 @@ __global__ void combine_rows_generic(float *x, const ZT *__restrict__ Z,
                                      const int *__restrict__ phys_of,
                                      const float *__restrict__ norm_w, OT *__restrict__ out,
                                      int T) {
+  pdl_prologue();
   constexpr bool EXACT = MODE != 0;
   using Acc = typename std::conditional<EXACT, double, float>::type;
   __shared__ Acc scratch[2][32];
@@ -342,12 +344,12 @@ struct Args {
 };
 
 template <typename ZT, typename OT, int MODE, bool NORM, int KM, int NC, int STAGES>
-int launch_kernel(cudaStream_t s, const Args &a, int threads, size_t smem) {
+int launch_variant(cudaStream_t s, const Args &a, int threads, size_t smem) {
   auto kern = combine_rows<ZT, OT, MODE, NORM, KM, NC, STAGES>;
   const int per_sm = blocks_per_sm_smem(kern, threads, smem);
   if (per_sm < 1)
     return GPTOSS_ERR_UNSUPPORTED;
-  kern<<<row_grid(a.T, per_sm), threads, smem, s>>>(a.x, static_cast<const ZT *>(a.Z), a.own_row,
+  launch_kernel(kern, dim3(row_grid(a.T, per_sm)), dim3(threads), smem, s, a.x, static_cast<const ZT *>(a.Z), a.own_row,
                                                    a.topk_w, a.topk_e, a.k, a.H, a.phys_of, a.norm_w,
                                                    static_cast<OT *>(a.out), a.T);
   return launch_status();
@@ -356,12 +358,12 @@ int launch_kernel(cudaStream_t s, const Args &a, int threads, size_t smem) {
 template <typename ZT, typename OT, int MODE, bool NORM, int KM, int NC>
 int launch_stages(cudaStream_t s, const Args &a, int threads, size_t stage_bytes, int stages) {
   if constexpr (NC > 1) // wide rows: a stage is tens of KB, two is what fits anyway
-    return launch_kernel<ZT, OT, MODE, NORM, KM, NC, 2>(s, a, threads, stage_bytes * 2);
+    return launch_variant<ZT, OT, MODE, NORM, KM, NC, 2>(s, a, threads, stage_bytes * 2);
   if (stages == 4)
-    return launch_kernel<ZT, OT, MODE, NORM, KM, NC, 4>(s, a, threads, stage_bytes * 4);
+    return launch_variant<ZT, OT, MODE, NORM, KM, NC, 4>(s, a, threads, stage_bytes * 4);
   if (stages == 3)
-    return launch_kernel<ZT, OT, MODE, NORM, KM, NC, 3>(s, a, threads, stage_bytes * 3);
-  return launch_kernel<ZT, OT, MODE, NORM, KM, NC, 2>(s, a, threads, stage_bytes * 2);
+    return launch_variant<ZT, OT, MODE, NORM, KM, NC, 3>(s, a, threads, stage_bytes * 3);
+  return launch_variant<ZT, OT, MODE, NORM, KM, NC, 2>(s, a, threads, stage_bytes * 2);
 }
 
 template <typename ZT, typename OT, int MODE, bool NORM> int launch(cudaStream_t s, const Args &a) {
@@ -383,7 +385,7 @@ template <typename ZT, typename OT, int MODE, bool NORM> int launch(cudaStream_t
     if (st != GPTOSS_ERR_UNSUPPORTED)
       return st;
   }
-  combine_rows_generic<ZT, OT, MODE, NORM><<<row_grid(a.T, 8), 256, 0, s>>>(
+  launch_kernel(combine_rows_generic<ZT, OT, MODE, NORM>, dim3(row_grid(a.T, 8)), dim3(256), 0, s, 
       a.x, static_cast<const ZT *>(a.Z), a.own_row, a.topk_w, a.topk_e, a.k, a.H, a.phys_of,
       a.norm_w, static_cast<OT *>(a.out), a.T);
   return launch_status();
@@ -414,6 +416,7 @@ extern "C" int gptoss_moe_combine(gptoss_stream_t stream, int T, float *x, const
                                   const int *phys_of, const float *norm_w, void *out,
                                   gptoss_dtype_t out_dtype, unsigned flags) {
   using namespace gptoss;
+  const PdlScope pdl(flags);
   if (T < 0 || k <= 0 || H <= 0 || !valid_dtype(z_dtype) || (norm_w && !valid_dtype(out_dtype)))
     return GPTOSS_ERR_BAD_ARG;
   if (k > GPTOSS_MAX_TOPK)

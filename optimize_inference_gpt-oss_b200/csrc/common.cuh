@@ -23,9 +23,43 @@ int sm_count();
 
 inline cudaStream_t as_stream(gptoss_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
 
+// Set by an entry point for the duration of its call (GPTOSS_PDL in flags): kernels
+// are then launched with programmatic stream serialization, so their blocks may be
+// scheduled while the previous kernel in the stream is still draining.
+extern thread_local bool tl_pdl;
+extern thread_local cudaError_t tl_launch_error;
+struct PdlScope {
+  bool prev;
+  explicit PdlScope(unsigned flags) : prev(tl_pdl) { tl_pdl = (flags & GPTOSS_PDL) != 0; }
+  ~PdlScope() { tl_pdl = prev; }
+};
+
+// kernel<<<grid, block, smem, stream>>>(args...), with the launch attribute above when asked for.
+template <typename... KArgs, typename... Args>
+inline void launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                          Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = tl_pdl ? 1 : 0;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+  if (e != cudaSuccess)
+    tl_launch_error = e;
+}
+
 // After a launch: GPTOSS_OK or GPTOSS_ERR_CUDA.
 inline int launch_status() {
-  const cudaError_t e = cudaGetLastError();
+  cudaError_t e = tl_launch_error;
+  tl_launch_error = cudaSuccess;
+  const cudaError_t last = cudaGetLastError();
+  if (e == cudaSuccess)
+    e = last;
   if (e == cudaSuccess)
     return GPTOSS_OK;
   note_cuda_error(e);
@@ -55,6 +89,27 @@ inline int row_grid(long rows, int per_sm) {
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 inline bool valid_dtype(gptoss_dtype_t d) { return d == GPTOSS_F32 || d == GPTOSS_BF16; }
 inline size_t dtype_size(gptoss_dtype_t d) { return d == GPTOSS_F32 ? 4 : 2; }
+
+// First statement of every kernel: returns once the previous kernel in the stream has
+// completed and its writes are visible; a no-op for a kernel launched the ordinary way.
+// Nothing, not even a table, is read before it, so scheduling a kernel's blocks early
+// (GPTOSS_PDL) only hides launch latency and never changes what a kernel sees.
+//
+// No kernel signals its dependents early (griddepcontrol.launch_dependents): the next
+// kernel's blocks become schedulable when this grid's blocks have exited, i.e. exactly one
+// kernel ahead and only in the tail.  Signalling at block start was measured on B200 and
+// made the whole chain 15 % slower: blocks of kernels several launches ahead became
+// resident, sat in their wait, and took the SM slots that the persistent grids of the
+// kernels actually running count on having all at once.
+__device__ __forceinline__ void pdl_prologue() {
+#if defined(GPTOSS_PDL_EARLY_TRIGGER) && GPTOSS_PDL_EARLY_TRIGGER == 1
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#endif
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+#if defined(GPTOSS_PDL_EARLY_TRIGGER) && GPTOSS_PDL_EARLY_TRIGGER == 2
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#endif
+}
 
 // ---- 128-bit memory access ----------------------------------------------------
 

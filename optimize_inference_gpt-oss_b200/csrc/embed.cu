@@ -19,6 +19,7 @@ template <bool WIDEN>
 __global__ void embed_rows(const unsigned char *__restrict__ table, const int *__restrict__ ids,
                            unsigned char *__restrict__ x, long total_chunks, int chunks_per_row,
                            size_t row_bytes, int V) {
+  pdl_prologue();
   const long stride = (long)gridDim.x * blockDim.x;
   for (long base = (long)blockIdx.x * blockDim.x + threadIdx.x; base < total_chunks;
        base += stride * kUnroll) {
@@ -56,6 +57,7 @@ __global__ void embed_rows(const unsigned char *__restrict__ table, const int *_
 template <typename TT, typename OT>
 __global__ void embed_rows_generic(const TT *__restrict__ table, const int *__restrict__ ids,
                                    OT *__restrict__ x, int T, int H, int V) {
+  pdl_prologue();
   for (int row = blockIdx.x; row < T; row += gridDim.x) {
     const int id = ids[row];
     const bool ok = id >= 0 && id < V;
@@ -73,7 +75,7 @@ int launch(cudaStream_t s, int T, const void *table, int V, const int *ids, void
   constexpr bool widen = sizeof(TT) != sizeof(OT);
   const size_t row_bytes = (size_t)H * sizeof(TT);
   if (row_bytes % 16 != 0 || !aligned16(table) || !aligned16(x)) {
-    embed_rows_generic<TT, OT><<<row_grid(T, 8), 256, 0, s>>>(
+    launch_kernel(embed_rows_generic<TT, OT>, dim3(row_grid(T, 8)), dim3(256), 0, s, 
         static_cast<const TT *>(table), ids, static_cast<OT *>(x), T, H, V);
     return launch_status();
   }
@@ -83,7 +85,7 @@ int launch(cudaStream_t s, int T, const void *table, int V, const int *ids, void
   static int occ = 0;
   auto k = embed_rows<widen>;
   const long want = (total + (long)threads * kUnroll - 1) / ((long)threads * kUnroll);
-  k<<<row_grid(want, blocks_per_sm(k, threads, &occ)), threads, 0, s>>>(
+  launch_kernel(k, dim3(row_grid(want, blocks_per_sm(k, threads, &occ))), dim3(threads), 0, s, 
       static_cast<const unsigned char *>(table), ids, static_cast<unsigned char *>(x), total, cpr,
       row_bytes, V);
   return launch_status();
@@ -94,8 +96,9 @@ int launch(cudaStream_t s, int T, const void *table, int V, const int *ids, void
 
 extern "C" int gptoss_embed(gptoss_stream_t stream, int T, const void *table,
                             gptoss_dtype_t table_dtype, int V, const int *ids, void *x,
-                            gptoss_dtype_t x_dtype, int H) {
+                            gptoss_dtype_t x_dtype, int H, unsigned flags) {
   using namespace gptoss;
+  const PdlScope pdl(flags);
   if (T < 0 || H <= 0 || V <= 0 || !valid_dtype(table_dtype) || !valid_dtype(x_dtype))
     return GPTOSS_ERR_BAD_ARG;
   if (T == 0)

@@ -37,6 +37,7 @@ __device__ __forceinline__ float fast_inv_rms(float ss, int H) {
 template <typename YT, typename OT, bool EXACT, int NC, int STAGES>
 __global__ void add_rmsnorm_rows(float *x, const YT *__restrict__ y, const float *__restrict__ w,
                                  OT *out, int T, int H) {
+  pdl_prologue();
   constexpr bool HAS_Y = !std::is_same<YT, NoY>::value;
   constexpr int SY = YSize<YT>::value;
   using Acc = typename std::conditional<EXACT, double, float>::type;
@@ -165,6 +166,7 @@ __global__ void add_rmsnorm_rows(float *x, const YT *__restrict__ y, const float
 template <typename YT, typename OT, bool EXACT>
 __global__ void add_rmsnorm_rows_generic(float *x, const YT *__restrict__ y,
                                          const float *__restrict__ w, OT *out, int T, int H) {
+  pdl_prologue();
   constexpr bool HAS_Y = !std::is_same<YT, NoY>::value;
   using Acc = typename std::conditional<EXACT, double, float>::type;
   __shared__ Acc scratch[2][32];
@@ -204,7 +206,7 @@ int launch_pipe(cudaStream_t s, int T, float *x, const YT *y, const float *w, OT
   const int per_sm = blocks_per_sm_smem(k, threads, smem);
   if (per_sm < 1)
     return GPTOSS_ERR_UNSUPPORTED;
-  k<<<row_grid(T, per_sm), threads, smem, s>>>(x, y, w, out, T, H);
+  launch_kernel(k, dim3(row_grid(T, per_sm)), dim3(threads), smem, s, x, y, w, out, T, H);
   return launch_status();
 }
 
@@ -236,7 +238,7 @@ int launch(cudaStream_t s, int T, float *x, const void *y, const float *w, void 
     if (st != GPTOSS_ERR_UNSUPPORTED)
       return st;
   }
-  add_rmsnorm_rows_generic<YT, OT, EXACT><<<row_grid(T, 8), 256, 0, s>>>(x, yp, w, op, T, H);
+  launch_kernel(add_rmsnorm_rows_generic<YT, OT, EXACT>, dim3(row_grid(T, 8)), dim3(256), 0, s, x, yp, w, op, T, H);
   return launch_status();
 }
 
@@ -263,6 +265,7 @@ extern "C" int gptoss_add_rmsnorm(gptoss_stream_t stream, int T, float *x, const
                                   gptoss_dtype_t y_dtype, const float *weight, void *out,
                                   gptoss_dtype_t out_dtype, int H, unsigned flags) {
   using namespace gptoss;
+  const PdlScope pdl(flags);
   if (T < 0 || H <= 0 || !valid_dtype(out_dtype) || (y && !valid_dtype(y_dtype)))
     return GPTOSS_ERR_BAD_ARG;
   if (T == 0)

@@ -52,6 +52,7 @@ __global__ void bias_rope_rows(const IT *qkv_in, long in_stride, const float *__
                                const float *__restrict__ cos_tab,
                                const float *__restrict__ sin_tab, int n_pos, int n_rot_heads,
                                int n_heads, int head_dim, OT *qkv_out, long out_stride, int T) {
+  pdl_prologue();
   constexpr int SI = sizeof(IT);
   extern __shared__ __align__(16) unsigned char ring[];
   const int half = head_dim >> 1, pieces = half >> 3, items = n_heads * pieces;
@@ -158,6 +159,7 @@ __global__ void bias_rope_rows_generic(const IT *qkv_in, long in_stride,
                                        const float *__restrict__ sin_tab, int n_pos,
                                        int n_rot_heads, int n_heads, int head_dim, OT *qkv_out,
                                        long out_stride, int T) {
+  pdl_prologue();
   const int half = head_dim >> 1, items = n_heads * half;
   for (int row = blockIdx.x; row < T; row += gridDim.x) {
     int p = pos ? pos[row] : pos_scalar;
@@ -209,7 +211,7 @@ int launch_pipe(cudaStream_t s, const Args &a, int threads, size_t smem) {
   const int per_sm = blocks_per_sm_smem(k, threads, smem);
   if (per_sm < 1)
     return GPTOSS_ERR_UNSUPPORTED;
-  k<<<row_grid(a.T, per_sm), threads, smem, s>>>(
+  launch_kernel(k, dim3(row_grid(a.T, per_sm)), dim3(threads), smem, s, 
       static_cast<const IT *>(a.in), a.in_stride, a.bias, a.pos, a.pos_scalar, a.cos_tab, a.sin_tab,
       a.n_pos, a.n_q + a.n_kv, a.n_q + 2 * a.n_kv, a.head_dim, static_cast<OT *>(a.out),
       a.out_stride, a.T);
@@ -238,7 +240,7 @@ template <typename IT, typename OT, bool EXACT, bool FMA> int launch(cudaStream_
     if (st != GPTOSS_ERR_UNSUPPORTED)
       return st;
   }
-  bias_rope_rows_generic<IT, OT, EXACT, FMA><<<row_grid(a.T, 8), 256, 0, s>>>(
+  launch_kernel(bias_rope_rows_generic<IT, OT, EXACT, FMA>, dim3(row_grid(a.T, 8)), dim3(256), 0, s, 
       static_cast<const IT *>(a.in), a.in_stride, a.bias, a.pos, a.pos_scalar, a.cos_tab, a.sin_tab,
       a.n_pos, n_rot, n_heads, a.head_dim, static_cast<OT *>(a.out), a.out_stride, a.T);
   return launch_status();
@@ -261,6 +263,7 @@ extern "C" int gptoss_qkv_bias_rope(gptoss_stream_t stream, int T, const void *q
                                     gptoss_dtype_t out_dtype, long out_row_stride,
                                     unsigned flags) {
   using namespace gptoss;
+  const PdlScope pdl(flags);
   if (T < 0 || n_q_heads < 0 || n_kv_heads < 0 || n_q_heads + n_kv_heads <= 0 || head_dim <= 0 ||
       head_dim % 2 != 0 || n_pos <= 0 || !valid_dtype(in_dtype) || !valid_dtype(out_dtype))
     return GPTOSS_ERR_BAD_ARG;

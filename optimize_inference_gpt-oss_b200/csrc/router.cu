@@ -30,6 +30,7 @@ __global__ void __launch_bounds__(kRowsPerBlock * 32)
     router_rows(const LT *__restrict__ logits, int E, int k, float *__restrict__ topk_w,
                 int *__restrict__ topk_e, int T, const int *__restrict__ done,
                 const int *__restrict__ slot_of) {
+  pdl_prologue();
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * kRowsPerBlock + (threadIdx.x >> 5);
   if (row >= T)
@@ -107,8 +108,10 @@ __global__ void __launch_bounds__(kRowsPerBlock * 32)
 
 extern "C" int gptoss_router_topk(gptoss_stream_t stream, int T, const void *logits,
                                   gptoss_dtype_t logits_dtype, int E, int k, float *topk_w,
-                                  int *topk_e, const int *done, const int *slot_of) {
+                                  int *topk_e, const int *done, const int *slot_of,
+                                  unsigned flags) {
   using namespace gptoss;
+  const PdlScope pdl(flags);
   if (T < 0 || E <= 0 || k <= 0 || k > E || !valid_dtype(logits_dtype))
     return GPTOSS_ERR_BAD_ARG;
   if (E > GPTOSS_MAX_EXPERTS || k > GPTOSS_MAX_TOPK)
@@ -120,10 +123,10 @@ extern "C" int gptoss_router_topk(gptoss_stream_t stream, int T, const void *log
   const int grid = (T + kRowsPerBlock - 1) / kRowsPerBlock;
   cudaStream_t s = as_stream(stream);
   if (logits_dtype == GPTOSS_F32)
-    router_rows<float><<<grid, kRowsPerBlock * 32, 0, s>>>(static_cast<const float *>(logits), E, k,
+    launch_kernel(router_rows<float>, dim3(grid), dim3(kRowsPerBlock * 32), 0, s, static_cast<const float *>(logits), E, k,
                                                           topk_w, topk_e, T, done, slot_of);
   else
-    router_rows<uint16_t><<<grid, kRowsPerBlock * 32, 0, s>>>(
+    launch_kernel(router_rows<uint16_t>, dim3(grid), dim3(kRowsPerBlock * 32), 0, s, 
         static_cast<const uint16_t *>(logits), E, k, topk_w, topk_e, T, done, slot_of);
   return launch_status();
 }

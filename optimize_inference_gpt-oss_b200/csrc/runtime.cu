@@ -7,6 +7,8 @@
 namespace gptoss {
 
 static thread_local int g_last_cuda_error = 0;
+thread_local bool tl_pdl = false;
+thread_local cudaError_t tl_launch_error = cudaSuccess;
 
 void note_cuda_error(cudaError_t e) { g_last_cuda_error = (int)e; }
 

@@ -47,6 +47,7 @@ template <bool EXACT> __device__ __forceinline__ float swiglu_one(float g, float
 template <typename YT, typename GT, bool EXACT>
 __global__ void __launch_bounds__(256)
     swiglu_flat(const YT *__restrict__ Y, GT *__restrict__ G, size_t n_groups, float limit) {
+  pdl_prologue();
   constexpr int kIn = sizeof(YT);         // 16-byte loads per group
   constexpr int kPer = 16 / sizeof(YT);   // inputs per load
   const size_t base = (size_t)blockIdx.x * (256 * kUnroll) + threadIdx.x;
@@ -86,6 +87,7 @@ __global__ void __launch_bounds__(256)
 template <typename YT, typename GT, bool EXACT>
 __global__ void swiglu_scalar(const YT *__restrict__ Y, GT *__restrict__ G, size_t first,
                               size_t n_out, float limit) {
+  pdl_prologue();
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (size_t n = first + (size_t)blockIdx.x * blockDim.x + threadIdx.x; n < n_out; n += stride)
     store1(G + n, swiglu_one<EXACT>(load1(Y + 2 * n), load1(Y + 2 * n + 1), limit));
@@ -101,7 +103,7 @@ int launch(cudaStream_t s, const void *Y, void *G, size_t n_out, float limit) {
     const size_t blocks = (n_groups + (size_t)threads * kUnroll - 1) / ((size_t)threads * kUnroll);
     if (blocks > 0x7fffffffull)
       return GPTOSS_ERR_UNSUPPORTED;
-    swiglu_flat<YT, GT, EXACT><<<(unsigned)blocks, threads, 0, s>>>(yp, gp, n_groups, limit);
+    launch_kernel(swiglu_flat<YT, GT, EXACT>, dim3((unsigned)blocks), dim3(threads), 0, s, yp, gp, n_groups, limit);
     const int st = launch_status();
     if (st != GPTOSS_OK)
       return st;
@@ -110,7 +112,7 @@ int launch(cudaStream_t s, const void *Y, void *G, size_t n_out, float limit) {
   if (done < n_out) {
     const size_t rest = n_out - done;
     const long blocks = (long)((rest + threads - 1) / threads);
-    swiglu_scalar<YT, GT, EXACT><<<row_grid(blocks, 8), threads, 0, s>>>(yp, gp, done, n_out, limit);
+    launch_kernel(swiglu_scalar<YT, GT, EXACT>, dim3(row_grid(blocks, 8)), dim3(threads), 0, s, yp, gp, done, n_out, limit);
     return launch_status();
   }
   return GPTOSS_OK;
@@ -133,6 +135,7 @@ extern "C" int gptoss_swiglu(gptoss_stream_t stream, const void *Y, gptoss_dtype
                              gptoss_dtype_t g_dtype, size_t R, int I, float limit,
                              unsigned flags) {
   using namespace gptoss;
+  const PdlScope pdl(flags);
   if (I <= 0 || !valid_dtype(y_dtype) || !valid_dtype(g_dtype) || !(limit >= 0.0f))
     return GPTOSS_ERR_BAD_ARG;
   if (R == 0)

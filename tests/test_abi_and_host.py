@@ -50,11 +50,11 @@ def test_bad_arguments_are_refused_before_any_launch(pkg):
     instead of aborting (the reference exits the process in HIP_CHECK)."""
     lib, P = pkg.load(), 0x1000  # a fake non-null address; never dereferenced
     B, U = pkg.ERR_BAD_ARG, pkg.ERR_UNSUPPORTED
-    assert lib.gptoss_embed(None, -1, P, 1, 10, P, P, 0, 64) == B
-    assert lib.gptoss_embed(None, 4, None, 1, 10, P, P, 0, 64) == B
-    assert lib.gptoss_embed(None, 4, P, 7, 10, P, P, 0, 64) == B
-    assert lib.gptoss_embed(None, 4, P, 0, 10, P, P, 1, 64) == U      # fp32 table -> bf16 rows
-    assert lib.gptoss_embed(None, 0, None, 1, 10, None, None, 0, 64) == pkg.OK  # empty batch
+    assert lib.gptoss_embed(None, -1, P, 1, 10, P, P, 0, 64, 0) == B
+    assert lib.gptoss_embed(None, 4, None, 1, 10, P, P, 0, 64, 0) == B
+    assert lib.gptoss_embed(None, 4, P, 7, 10, P, P, 0, 64, 0) == B
+    assert lib.gptoss_embed(None, 4, P, 0, 10, P, P, 1, 64, 0) == U      # fp32 table -> bf16 rows
+    assert lib.gptoss_embed(None, 0, None, 1, 10, None, None, 0, 64, 0) == pkg.OK  # empty batch
     assert lib.gptoss_add_rmsnorm(None, 4, None, None, 0, P, P, 0, 64, 0) == B
     assert lib.gptoss_add_rmsnorm(None, 4, P, None, 0, P, P, 0, 0, 0) == B
     assert lib.gptoss_add_rmsnorm(None, 4, P, None, 0, P, P, 1, 64, 0) == B  # in place needs fp32 out
@@ -63,10 +63,10 @@ def test_bad_arguments_are_refused_before_any_launch(pkg):
     assert lib.gptoss_qkv_bias_rope(None, 4, P, 0, 5120, None, None, 0, P, P, 16, 64, 8, 63, P, 0, 5120, 0) == B  # odd head
     assert lib.gptoss_qkv_bias_rope(None, 4, P, 0, 5120, None, None, 0, P, P, 16, 64, 8, 64, P, 1, 5120, 0) == B  # in place, dtype change
     assert lib.gptoss_qkv_bias_rope(None, 4, P, 0, 5120, None, None, 0, None, P, 16, 64, 8, 64, P + 64, 0, 5120, 0) == B
-    assert lib.gptoss_router_topk(None, 4, P, 0, 32, 0, P, P, None, None) == B
-    assert lib.gptoss_router_topk(None, 4, P, 0, 32, 33, P, P, None, None) == B
-    assert lib.gptoss_router_topk(None, 4, P, 0, 512, 4, P, P, None, None) == U
-    assert lib.gptoss_router_topk(None, 4, P, 0, 32, 9, P, P, None, None) == U
+    assert lib.gptoss_router_topk(None, 4, P, 0, 32, 0, P, P, None, None, 0) == B
+    assert lib.gptoss_router_topk(None, 4, P, 0, 32, 33, P, P, None, None, 0) == B
+    assert lib.gptoss_router_topk(None, 4, P, 0, 512, 4, P, P, None, None, 0) == U
+    assert lib.gptoss_router_topk(None, 4, P, 0, 32, 9, P, P, None, None, 0) == U
     assert lib.gptoss_swiglu(None, None, 0, P, 0, 4, 64, 7.0, 0) == B
     assert lib.gptoss_swiglu(None, P, 0, P, 0, 4, 0, 7.0, 0) == B
     assert lib.gptoss_swiglu(None, P, 0, P, 0, 4, 64, -1.0, 0) == B
@@ -74,10 +74,10 @@ def test_bad_arguments_are_refused_before_any_launch(pkg):
     assert lib.gptoss_moe_combine(None, 4, P, P, 0, None, P, None, 4, 64, None, None, None, 0, 0) == B
     assert lib.gptoss_moe_combine(None, 4, P, P, 0, None, P, P, 9, 64, None, None, None, 0, 0) == U
     assert lib.gptoss_moe_combine(None, 4, P, P, 0, None, P, P, 4, 64, None, P, None, 0, 0) == B  # norm without out
-    assert lib.gptoss_argmax(None, 4, P, 0, 0, 0, None, P) == B
-    assert lib.gptoss_argmax(None, 4, P, 0, 100, 50, None, P) == B  # stride < V
-    assert lib.gptoss_argmax(None, 4, P, 0, 100, 100, None, None) == B
-    assert lib.gptoss_argmax(None, 0, None, 0, 100, 100, None, None) == pkg.OK
+    assert lib.gptoss_argmax(None, 4, P, 0, 0, 0, None, P, 0) == B
+    assert lib.gptoss_argmax(None, 4, P, 0, 100, 50, None, P, 0) == B  # stride < V
+    assert lib.gptoss_argmax(None, 4, P, 0, 100, 100, None, None, 0) == B
+    assert lib.gptoss_argmax(None, 0, None, 0, 100, 100, None, None, 0) == pkg.OK
     assert lib.gptoss_chain_create(None, 4, 1, None) == B
     assert lib.gptoss_build_rope_tables(0, 64, 150000.0, 32.0, 4096.0, 32.0, 1.0, P, P) == B
 

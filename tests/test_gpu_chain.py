@@ -123,6 +123,23 @@ def test_chain_bf16_mode_small(gpu, orc):
     _run_and_compare(pkg, orc, _small_config(pkg, pkg.BF16), 64, 3, TOL_BF16, seed=12)
 
 
+def test_chain_with_programmatic_dependent_launch(gpu, orc):
+    """GPTOSS_PDL lets a kernel's blocks be scheduled while the previous kernel drains; every
+    kernel waits for its predecessor before reading anything, so the results are the same
+    bits as without it (graph replay and plain launches alike)."""
+    pkg = gpu
+    outs = []
+    for flags in (0, pkg.PDL):
+        c = _small_config(pkg, pkg.BF16)
+        c.flags |= flags
+        got_x, _ = _run_and_compare(pkg, orc, c, 200, 3, TOL_BF16, seed=15)
+        outs.append(got_x)
+    assert n_bit_diff(outs[0], outs[1]) == 0
+    c = _small_config(pkg, pkg.F32)
+    c.flags |= pkg.PDL
+    _run_and_compare(pkg, orc, c, 64, 3, TOL_F32, seed=11)
+
+
 def test_chain_120b_router_width(gpu, orc):
     pkg = gpu
     c = pkg.chain_config(120, pkg.BF16, max_pos=4096)
