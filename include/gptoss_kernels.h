@@ -33,11 +33,14 @@
  *
  * Launch option (flags), independent of the arithmetic:
  *   GPTOSS_PDL    launch with programmatic stream serialization: the kernel's
- *                 thread blocks may be scheduled while the previous kernel in
- *                 the stream is still finishing, which hides the launch gap
- *                 between short kernels.  Results do not change: every kernel
- *                 starts with a grid-dependency wait and reads nothing, not
- *                 even its tables, before the previous kernel has completed.
+ *                 thread blocks may be scheduled as soon as the previous
+ *                 kernel in the stream allows it (a producer that signals
+ *                 launch completion early, e.g. a GEMM epilogue), which hides
+ *                 this kernel's launch latency.  Results do not change: every
+ *                 kernel starts with a grid-dependency wait and reads nothing,
+ *                 not even its tables, before the previous kernel has
+ *                 completed.  These kernels do not signal early themselves, so
+ *                 between two of them the flag is neutral.
  */
 #ifndef GPTOSS_KERNELS_H
 #define GPTOSS_KERNELS_H

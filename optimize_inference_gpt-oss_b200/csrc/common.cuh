@@ -95,21 +95,15 @@ inline size_t dtype_size(gptoss_dtype_t d) { return d == GPTOSS_F32 ? 4 : 2; }
 // Nothing, not even a table, is read before it, so scheduling a kernel's blocks early
 // (GPTOSS_PDL) only hides launch latency and never changes what a kernel sees.
 //
-// No kernel signals its dependents early (griddepcontrol.launch_dependents): the next
-// kernel's blocks become schedulable when this grid's blocks have exited, i.e. exactly one
-// kernel ahead and only in the tail.  Signalling at block start was measured on B200 and
-// made the whole chain 15 % slower: blocks of kernels several launches ahead became
-// resident, sat in their wait, and took the SM slots that the persistent grids of the
-// kernels actually running count on having all at once.
-__device__ __forceinline__ void pdl_prologue() {
-#if defined(GPTOSS_PDL_EARLY_TRIGGER) && GPTOSS_PDL_EARLY_TRIGGER == 1
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-#endif
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-#if defined(GPTOSS_PDL_EARLY_TRIGGER) && GPTOSS_PDL_EARLY_TRIGGER == 2
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-#endif
-}
+// No kernel here signals its dependents early (griddepcontrol.launch_dependents): the
+// next kernel's blocks become schedulable only when this grid's blocks have exited.
+// Signalling at block start, before or after the wait, was measured on B200 and made the
+// 24-layer chain 15 % slower (and no faster at 64 or 512 tokens): blocks of kernels ahead
+// in the stream became resident, sat in their wait, and took the SM slots that the
+// persistent grids of the kernels actually running count on having all at once.  The flag
+// therefore pays off only behind a producer that signals early itself (a GEMM with a
+// programmatic-launch epilogue); between these kernels it is neutral.
+__device__ __forceinline__ void pdl_prologue() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // ---- 128-bit memory access ----------------------------------------------------
 
@@ -170,6 +164,14 @@ __device__ __forceinline__ void st_stream8(void *p, uint2 v) {
 __device__ __forceinline__ void cp_async16(void *smem_dst, const void *gmem_src) {
   const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
+}
+// The same through L1 (.ca): for small read-only tables that many rows, warps and
+// blocks of an SM ask for again and again (a position's cos/sin row).  Kept in L1, the
+// repeats never reach L2 -- when a whole batch sits at one position every block wants
+// the same two cache lines, and without L1 that single L2 line becomes a hot spot.
+__device__ __forceinline__ void cp_async16_cached(void *smem_dst, const void *gmem_src) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
 }
 __device__ __forceinline__ void cp_async4(void *smem_dst, const void *gmem_src) {
   const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);

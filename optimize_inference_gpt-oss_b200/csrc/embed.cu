@@ -1,55 +1,53 @@
 // Token-embedding gather (gptoss_embed): x[t,:] = table[ids[t],:].
 //
 // Pure data movement: per token one id, one table row in, one row out.  Work is
-// cut into chunks of 8 elements; every thread fetches kUnroll chunks with
-// 128-bit loads before it stores any of them, so a warp keeps 2 KB (bf16 table)
-// to 4 KB (fp32 table) of reads in flight.  Rows are random, but each row is a
+// cut into 16-byte chunks; a block owns a contiguous tile of output chunks and
+// every thread fetches kUnroll of them with 128-bit loads before it stores any
+// (a one-shot grid: the hardware scheduler keeps the SMs stocked with blocks).  Rows are random, but each row is a
 // contiguous multi-kilobyte run, so DRAM pages are still used whole.
 #include "common.cuh"
 
 namespace gptoss {
 namespace {
 
-constexpr int kUnroll = 4;
+constexpr int kUnroll = 2;
 
 // WIDEN = false: rows are copied as raw 16-byte pieces (table and x have the
 // same element type; row_bytes = H * element size).  WIDEN = true: each 16-byte
 // piece holds 8 bf16 values that leave as 8 fp32 values (bits << 16).
 template <bool WIDEN>
-__global__ void embed_rows(const unsigned char *__restrict__ table, const int *__restrict__ ids,
-                           unsigned char *__restrict__ x, long total_chunks, int chunks_per_row,
-                           size_t row_bytes, int V) {
+__global__ void __launch_bounds__(256)
+    embed_rows(const unsigned char *__restrict__ table, const int *__restrict__ ids,
+               unsigned char *__restrict__ x, long total_chunks, int chunks_per_row,
+               size_t row_bytes, int V) {
   pdl_prologue();
-  const long stride = (long)gridDim.x * blockDim.x;
-  for (long base = (long)blockIdx.x * blockDim.x + threadIdx.x; base < total_chunks;
-       base += stride * kUnroll) {
-    uint4 v[kUnroll];
-    bool live[kUnroll];
+  // One-shot grid: block b owns output chunks [b * 256 * kUnroll, (b + 1) * 256 * kUnroll).
+  const long base = (long)blockIdx.x * (256 * kUnroll) + threadIdx.x;
+  uint4 v[kUnroll];
 #pragma unroll
-    for (int u = 0; u < kUnroll; u++) {
-      const long unit = base + u * stride;
-      live[u] = unit < total_chunks;
-      v[u] = make_uint4(0u, 0u, 0u, 0u);
-      if (live[u]) {
-        const int row = (int)(unit / chunks_per_row), c = (int)(unit % chunks_per_row);
-        const int id = __ldg(ids + row);
-        if (id >= 0 && id < V)
-          v[u] = ld_stream(table + (size_t)id * row_bytes + (size_t)c * 16);
-      }
+  for (int u = 0; u < kUnroll; u++) {
+    const long unit = base + u * 256;
+    v[u] = make_uint4(0u, 0u, 0u, 0u);
+    if (unit < total_chunks) {
+      const int row = (int)(unit / chunks_per_row), c = (int)(unit - (long)row * chunks_per_row);
+      const int id = __ldg(ids + row);
+      if (id >= 0 && id < V)
+        v[u] = ld_stream(table + (size_t)id * row_bytes + (size_t)c * 16);
     }
+  }
 #pragma unroll
-    for (int u = 0; u < kUnroll; u++)
-      if (live[u]) {
-        const size_t unit = (size_t)(base + u * stride);
-        if (WIDEN) {
-          st_stream(x + unit * 32, make_uint4(v[u].x << 16, v[u].x & 0xffff0000u, v[u].y << 16,
-                                              v[u].y & 0xffff0000u));
-          st_stream(x + unit * 32 + 16, make_uint4(v[u].z << 16, v[u].z & 0xffff0000u,
-                                                   v[u].w << 16, v[u].w & 0xffff0000u));
-        } else {
-          st_stream(x + unit * 16, v[u]);
-        }
-      }
+  for (int u = 0; u < kUnroll; u++) {
+    const size_t unit = (size_t)(base + u * 256);
+    if ((long)unit >= total_chunks)
+      continue;
+    if (WIDEN) {
+      st_stream(x + unit * 32, make_uint4(v[u].x << 16, v[u].x & 0xffff0000u, v[u].y << 16,
+                                          v[u].y & 0xffff0000u));
+      st_stream(x + unit * 32 + 16, make_uint4(v[u].z << 16, v[u].z & 0xffff0000u,
+                                               v[u].w << 16, v[u].w & 0xffff0000u));
+    } else {
+      st_stream(x + unit * 16, v[u]);
+    }
   }
 }
 
@@ -82,10 +80,10 @@ int launch(cudaStream_t s, int T, const void *table, int V, const int *ids, void
   const int cpr = (int)(row_bytes / 16);
   const long total = (long)T * cpr;
   constexpr int threads = 256;
-  static int occ = 0;
-  auto k = embed_rows<widen>;
-  const long want = (total + (long)threads * kUnroll - 1) / ((long)threads * kUnroll);
-  launch_kernel(k, dim3(row_grid(want, blocks_per_sm(k, threads, &occ))), dim3(threads), 0, s, 
+  const long blocks = (total + (long)threads * kUnroll - 1) / ((long)threads * kUnroll);
+  if (blocks > 0x7fffffffL)
+    return GPTOSS_ERR_UNSUPPORTED;
+  launch_kernel(embed_rows<widen>, dim3((unsigned)blocks), dim3(threads), 0, s, 
       static_cast<const unsigned char *>(table), ids, static_cast<unsigned char *>(x), total, cpr,
       row_bytes, V);
   return launch_status();

@@ -95,7 +95,7 @@ __global__ void bias_rope_rows(const IT *qkv_in, long in_stride, const float *__
     for (int q = lane; q < 2 * per_table; q += 32) {
       const float *src = q < per_table ? cos_tab + (size_t)p * half + q * 4
                                        : sin_tab + (size_t)p * half + (q - per_table) * 4;
-      cp_async16(st + (size_t)q * 16, src);
+      cp_async16_cached(st + (size_t)q * 16, src);
     }
   };
 

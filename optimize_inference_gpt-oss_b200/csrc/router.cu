@@ -13,8 +13,7 @@
 namespace gptoss {
 namespace {
 
-constexpr int kRowsPerBlock = 8;               // warps per block
-constexpr int kSlots = GPTOSS_MAX_EXPERTS / 32; // experts per lane
+constexpr int kRowsPerBlock = 8; // warps per block
 
 // Key that orders like the float: larger value, larger key; -0 and +0 share a
 // key; NaN gets the smallest key so it is never taken ahead of a number.
@@ -25,7 +24,9 @@ __device__ __forceinline__ uint32_t order_key(float v) {
   return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
-template <typename LT>
+// kSlots = experts per lane = ceil(E / 32), a template parameter so that the
+// common E = 32 case scans one value per lane instead of eight predicated ones.
+template <typename LT, int kSlots>
 __global__ void __launch_bounds__(kRowsPerBlock * 32)
     router_rows(const LT *__restrict__ logits, int E, int k, float *__restrict__ topk_w,
                 int *__restrict__ topk_e, int T, const int *__restrict__ done,
@@ -122,11 +123,29 @@ extern "C" int gptoss_router_topk(gptoss_stream_t stream, int T, const void *log
     return GPTOSS_ERR_BAD_ARG;
   const int grid = (T + kRowsPerBlock - 1) / kRowsPerBlock;
   cudaStream_t s = as_stream(stream);
-  if (logits_dtype == GPTOSS_F32)
-    launch_kernel(router_rows<float>, dim3(grid), dim3(kRowsPerBlock * 32), 0, s, static_cast<const float *>(logits), E, k,
-                                                          topk_w, topk_e, T, done, slot_of);
-  else
-    launch_kernel(router_rows<uint16_t>, dim3(grid), dim3(kRowsPerBlock * 32), 0, s, 
-        static_cast<const uint16_t *>(logits), E, k, topk_w, topk_e, T, done, slot_of);
+  const int slots = (E + 31) / 32;
+#define GPTOSS_ROUTER_CASE(LT_, SLOTS_)                                                           \
+  launch_kernel(router_rows<LT_, SLOTS_>, dim3(grid), dim3(kRowsPerBlock * 32), 0, s,             \
+                static_cast<const LT_ *>(logits), E, k, topk_w, topk_e, T, done, slot_of)
+  if (logits_dtype == GPTOSS_F32) {
+    if (slots <= 1)
+      GPTOSS_ROUTER_CASE(float, 1);
+    else if (slots <= 2)
+      GPTOSS_ROUTER_CASE(float, 2);
+    else if (slots <= 4)
+      GPTOSS_ROUTER_CASE(float, 4);
+    else
+      GPTOSS_ROUTER_CASE(float, 8);
+  } else {
+    if (slots <= 1)
+      GPTOSS_ROUTER_CASE(uint16_t, 1);
+    else if (slots <= 2)
+      GPTOSS_ROUTER_CASE(uint16_t, 2);
+    else if (slots <= 4)
+      GPTOSS_ROUTER_CASE(uint16_t, 4);
+    else
+      GPTOSS_ROUTER_CASE(uint16_t, 8);
+  }
+#undef GPTOSS_ROUTER_CASE
   return launch_status();
 }
