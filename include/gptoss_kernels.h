@@ -213,6 +213,36 @@ GPTOSS_API int gptoss_argmax(gptoss_stream_t stream, int T, const void *logits,
                              gptoss_dtype_t logits_dtype, long V, long row_stride,
                              unsigned long long *keys, int *out, unsigned flags);
 
+/*
+ * Grouping of the n_pairs (token, choice) pairs by expert, for the local
+ * experts e_begin .. e_begin + e_count - 1: rows offsets[e] .. offsets[e+1]
+ * (offsets has e_count + 1 entries) hold the pairs that chose local expert e,
+ * in pair order; counts[e] is their number; row_pair[row] is the pair index
+ * (token * k + choice) and own_row[pair] its row, or -1 when the pair's expert
+ * is not local or the token is finished (expert -1).  own_row is the row map
+ * gptoss_moe_combine reads through.
+ * Replaces moe_group_ep without a partner (kernels/moe_ep.hpp:44-257; launch
+ * gpu_engine.hpp:542) and moe_group_kernel (kernels/moe.hpp:138-171).  Integer
+ * results, reproduced exactly.  A step beside the path the fused kernels sit
+ * on (it feeds the expert GEMMs), provided so that a caller gets own_row from
+ * the same library.
+ */
+GPTOSS_API int gptoss_moe_group(gptoss_stream_t stream, const int *topk_e, int n_pairs,
+                                int e_begin, int e_count, int *counts, int *offsets,
+                                int *row_pair, int *own_row, unsigned flags);
+
+/*
+ * Row gather for the expert GEMM input: Xg[row,:] = t[row_pair[row] / k, :] for
+ * R rows, bit for bit (same element type on both sides, fp32 or bf16).
+ * Replaces moe_gather_kernel (kernels/moe.hpp:175-182), gather_bf16_kernel
+ * (kernels/fast_misc.hpp:144-151) and moe_gather_ep_bf16 without a partner
+ * (kernels/moe_ep.hpp:337-368; launch gpu_engine.hpp:567-568).  n_tokens bounds
+ * the source rows: a row_pair entry outside [0, n_tokens * k) yields zeros.
+ */
+GPTOSS_API int gptoss_moe_gather(gptoss_stream_t stream, int R, const void *t,
+                                 gptoss_dtype_t dtype, int n_tokens, const int *row_pair, int k,
+                                 void *Xg, int H, unsigned flags);
+
 /* How many slices (thread blocks) gptoss_argmax cuts each row into for T rows
  * of V logits on the current device; has_keys = 0 describes a call with
  * keys == NULL (always 1).  More than one slice means a second, tiny launch

@@ -68,6 +68,8 @@ PROTOTYPES = {
     "gptoss_swiglu": (_i, [_p, _p, _i, _p, _i, _z, _i, _f, _u]),
     "gptoss_moe_combine": (_i, [_p, _i, _p, _p, _i, _p, _p, _p, _i, _i, _p, _p, _p, _i, _u]),
     "gptoss_argmax": (_i, [_p, _i, _p, _i, _l, _l, _p, _p, _u]),
+    "gptoss_moe_group": (_i, [_p, _p, _i, _i, _i, _p, _p, _p, _p, _u]),
+    "gptoss_moe_gather": (_i, [_p, _i, _p, _i, _i, _p, _i, _p, _i, _u]),
     "gptoss_argmax_slices": (_i, [_i, _l, _i, _i]),
     "gptoss_argmax_noalloc": (_i, [_p, _i, _p, _i, _l, _l, _p]),
     "gptoss_device_count": (_i, [C.POINTER(_i)]),
@@ -265,6 +267,16 @@ def moe_combine(T, x, Z, z_dtype, own_row, topk_w, topk_e, k, H, phys_of=None, n
 
 def argmax(T, logits, dtype, V, row_stride, keys, out, flags=0, stream=None):
     check(load().gptoss_argmax(stream, T, _ptr(logits), dtype, V, row_stride, _ptr(keys), _ptr(out), flags), "argmax")
+
+
+def moe_group(topk_e, n_pairs, e_begin, e_count, counts, offsets, row_pair, own_row, flags=0, stream=None):
+    check(load().gptoss_moe_group(stream, _ptr(topk_e), n_pairs, e_begin, e_count, _ptr(counts), _ptr(offsets),
+                                  _ptr(row_pair), _ptr(own_row), flags), "moe_group")
+
+
+def moe_gather(R, t, dtype, n_tokens, row_pair, k, Xg, H, flags=0, stream=None):
+    check(load().gptoss_moe_gather(stream, R, _ptr(t), dtype, n_tokens, _ptr(row_pair), k, _ptr(Xg), H, flags),
+          "moe_gather")
 
 
 ARGMAX_NOALLOC_MAX_ROWS = 16384

@@ -19,7 +19,7 @@ template <bool WIDEN>
 __global__ void __launch_bounds__(256)
     embed_rows(const unsigned char *__restrict__ table, const int *__restrict__ ids,
                unsigned char *__restrict__ x, long total_chunks, int chunks_per_row,
-               size_t row_bytes, int V) {
+               size_t row_bytes, int V, int id_div) {
   pdl_prologue();
   // One-shot grid: block b owns output chunks [b * 256 * kUnroll, (b + 1) * 256 * kUnroll).
   const long base = (long)blockIdx.x * (256 * kUnroll) + threadIdx.x;
@@ -30,7 +30,8 @@ __global__ void __launch_bounds__(256)
     v[u] = make_uint4(0u, 0u, 0u, 0u);
     if (unit < total_chunks) {
       const int row = (int)(unit / chunks_per_row), c = (int)(unit - (long)row * chunks_per_row);
-      const int id = __ldg(ids + row);
+      const int raw = __ldg(ids + row);
+      const int id = raw >= 0 ? raw / id_div : -1; // id_div = k turns a pair index into its token
       if (id >= 0 && id < V)
         v[u] = ld_stream(table + (size_t)id * row_bytes + (size_t)c * 16);
     }
@@ -54,10 +55,10 @@ __global__ void __launch_bounds__(256)
 // Any H and alignment: one element per thread step.
 template <typename TT, typename OT>
 __global__ void embed_rows_generic(const TT *__restrict__ table, const int *__restrict__ ids,
-                                   OT *__restrict__ x, int T, int H, int V) {
+                                   OT *__restrict__ x, int T, int H, int V, int id_div) {
   pdl_prologue();
   for (int row = blockIdx.x; row < T; row += gridDim.x) {
-    const int id = ids[row];
+    const int id = ids[row] >= 0 ? ids[row] / id_div : -1;
     const bool ok = id >= 0 && id < V;
     for (int j = threadIdx.x; j < H; j += blockDim.x) {
       if constexpr (sizeof(TT) == sizeof(OT)) // same type: move the bits untouched
@@ -69,12 +70,13 @@ __global__ void embed_rows_generic(const TT *__restrict__ table, const int *__re
 }
 
 template <typename TT, typename OT>
-int launch(cudaStream_t s, int T, const void *table, int V, const int *ids, void *x, int H) {
+int launch(cudaStream_t s, int T, const void *table, int V, const int *ids, void *x, int H,
+           int id_div = 1) {
   constexpr bool widen = sizeof(TT) != sizeof(OT);
   const size_t row_bytes = (size_t)H * sizeof(TT);
   if (row_bytes % 16 != 0 || !aligned16(table) || !aligned16(x)) {
     launch_kernel(embed_rows_generic<TT, OT>, dim3(row_grid(T, 8)), dim3(256), 0, s, 
-        static_cast<const TT *>(table), ids, static_cast<OT *>(x), T, H, V);
+        static_cast<const TT *>(table), ids, static_cast<OT *>(x), T, H, V, id_div);
     return launch_status();
   }
   const int cpr = (int)(row_bytes / 16);
@@ -85,7 +87,7 @@ int launch(cudaStream_t s, int T, const void *table, int V, const int *ids, void
     return GPTOSS_ERR_UNSUPPORTED;
   launch_kernel(embed_rows<widen>, dim3((unsigned)blocks), dim3(threads), 0, s, 
       static_cast<const unsigned char *>(table), ids, static_cast<unsigned char *>(x), total, cpr,
-      row_bytes, V);
+      row_bytes, V, id_div);
   return launch_status();
 }
 
@@ -111,4 +113,21 @@ extern "C" int gptoss_embed(gptoss_stream_t stream, int T, const void *table,
   if (table_dtype == GPTOSS_F32 && x_dtype == GPTOSS_F32)
     return launch<float, float>(s, T, table, V, ids, x, H);
   return GPTOSS_ERR_UNSUPPORTED; // narrowing an fp32 table would not be a bit-exact copy
+}
+
+extern "C" int gptoss_moe_gather(gptoss_stream_t stream, int R, const void *t, gptoss_dtype_t dtype,
+                                 int n_tokens, const int *row_pair, int k, void *Xg, int H,
+                                 unsigned flags) {
+  using namespace gptoss;
+  const PdlScope pdl(flags);
+  if (R < 0 || H <= 0 || n_tokens <= 0 || k <= 0 || !valid_dtype(dtype))
+    return GPTOSS_ERR_BAD_ARG;
+  if (R == 0)
+    return GPTOSS_OK;
+  if (!t || !row_pair || !Xg)
+    return GPTOSS_ERR_BAD_ARG;
+  cudaStream_t s = as_stream(stream);
+  // the embedding gather with "ids" = pair indices divided by k
+  return dtype == GPTOSS_BF16 ? launch<uint16_t, uint16_t>(s, R, t, n_tokens, row_pair, Xg, H, k)
+                              : launch<float, float>(s, R, t, n_tokens, row_pair, Xg, H, k);
 }

@@ -1,0 +1,101 @@
+// Grouping of (token, choice) pairs by expert (gptoss_moe_group): the integer
+// bookkeeping between the router and the expert GEMMs that also produces the
+// row map the combine reads through.
+//
+// One thread block per local expert, as in the reference.  Thread t owns the
+// contiguous run of pairs [t * S, (t + 1) * S); a first pass counts, per
+// thread, the pairs of lower local experts (their total is the expert's first
+// row) and the pairs of this expert; a block-wide exclusive scan of the latter
+// gives every thread the row of its first hit, so a second pass can place the
+// hits in pair order.  All data (a few tens of KB of expert ids) is L2-resident;
+// the kernel is latency-bound and kept short.
+#include "common.cuh"
+
+namespace gptoss {
+namespace {
+
+constexpr int kGroupThreads = 256;
+
+__device__ __forceinline__ int warp_inclusive_scan(int v, int lane) {
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int n = __shfl_up_sync(0xffffffffu, v, o);
+    if (lane >= o)
+      v += n;
+  }
+  return v;
+}
+
+__global__ void __launch_bounds__(kGroupThreads)
+    moe_group_rows(const int *__restrict__ topk_e, int n_pairs, int e_begin, int e_count,
+                   int *__restrict__ counts, int *__restrict__ offsets, int *__restrict__ row_pair,
+                   int *__restrict__ own_row) {
+  pdl_prologue();
+  __shared__ int warp_hits[kGroupThreads / 32], warp_below[kGroupThreads / 32];
+  const int e = blockIdx.x, ge = e_begin + e;
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  const int per = (n_pairs + kGroupThreads - 1) / kGroupThreads;
+  const int p0 = min(t * per, n_pairs), p1 = min(p0 + per, n_pairs);
+
+  int below = 0, hits = 0;
+  for (int p = p0; p < p1; p++) {
+    const int x = __ldg(topk_e + p);
+    below += (x >= e_begin && x < ge);
+    hits += (x == ge);
+    // pairs of experts held elsewhere (or of finished tokens, expert -1) get no row;
+    // each block marks its share so that every such pair is written exactly once
+    if ((x < e_begin || x >= e_begin + e_count) && (p % e_count) == e)
+      own_row[p] = -1;
+  }
+  const int incl = warp_inclusive_scan(hits, lane);
+  int below_w = below;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1)
+    below_w += __shfl_xor_sync(0xffffffffu, below_w, o);
+  if (lane == 31)
+    warp_hits[warp] = incl;
+  if (lane == 0)
+    warp_below[warp] = below_w;
+  __syncthreads();
+  // rows of lower experts; hits of this expert in earlier warps; all hits
+  int base = 0, before = 0, total = 0;
+#pragma unroll
+  for (int w = 0; w < kGroupThreads / 32; w++) {
+    base += warp_below[w];
+    total += warp_hits[w];
+    if (w < warp)
+      before += warp_hits[w];
+  }
+  int row = base + before + incl - hits; // row of this thread's first hit
+  if (t == 0) {
+    counts[e] = total;
+    offsets[e] = base;
+    if (e == e_count - 1)
+      offsets[e_count] = base + total;
+  }
+  for (int p = p0; p < p1; p++)
+    if (__ldg(topk_e + p) == ge) {
+      row_pair[row] = p;
+      own_row[p] = row;
+      row++;
+    }
+}
+
+} // namespace
+} // namespace gptoss
+
+extern "C" int gptoss_moe_group(gptoss_stream_t stream, const int *topk_e, int n_pairs, int e_begin,
+                                int e_count, int *counts, int *offsets, int *row_pair, int *own_row,
+                                unsigned flags) {
+  using namespace gptoss;
+  const PdlScope pdl(flags);
+  if (n_pairs < 0 || e_begin < 0 || e_count <= 0)
+    return GPTOSS_ERR_BAD_ARG;
+  if (!counts || !offsets)
+    return GPTOSS_ERR_BAD_ARG;
+  if (n_pairs > 0 && (!topk_e || !row_pair || !own_row))
+    return GPTOSS_ERR_BAD_ARG;
+  launch_kernel(moe_group_rows, dim3(e_count), dim3(kGroupThreads), 0, as_stream(stream), topk_e, n_pairs,
+                e_begin, e_count, counts, offsets, row_pair, own_row);
+  return launch_status();
+}

@@ -206,6 +206,10 @@ class Oracle(_Lib):
         L.orc_yarn_table.restype = None
         L.orc_yarn_table.argtypes = [_f32p, _f32p, C.c_int, C.c_float, C.c_int, C.c_float, C.c_float,
                                      C.c_float, C.c_float, C.c_int]
+        L.orc_moe_group.restype = None
+        L.orc_moe_group.argtypes = [_i32p, C.c_int, C.c_int, C.c_int, _i32p, _i32p, _i32p, _i32p]
+        L.orc_moe_gather.restype = None
+        L.orc_moe_gather.argtypes = [_f32p, _f32p, _i32p, C.c_int, C.c_int, C.c_int]
         L.orc_expf_array.restype = None
         L.orc_expf_array.argtypes = [_f32p, _f32p, C.c_long]
 
@@ -250,6 +254,23 @@ class Oracle(_Lib):
         self.lib.orc_yarn_table(c, s, n_pos, theta, head_dim, factor, orig_ctx, beta_fast, beta_slow,
                                 threads)
         return c, s
+
+    def moe_group(self, topk_e, e_begin, e_count):
+        """Returns (counts[e_count], offsets[e_count+1], row_pair[n_local], own_row[n_pairs])."""
+        te = np.ascontiguousarray(topk_e, np.int32).ravel()
+        counts = np.empty(e_count, np.int32)
+        offsets = np.empty(e_count + 1, np.int32)
+        row_pair = np.full(te.size, -1, np.int32)
+        own_row = np.full(te.size, -7, np.int32)
+        self.lib.orc_moe_group(te, te.size, e_begin, e_count, counts, offsets, row_pair, own_row)
+        return counts, offsets, row_pair[:offsets[-1]], own_row
+
+    def moe_gather(self, t, row_pair, k):
+        t = np.ascontiguousarray(t, np.float32)
+        rp = np.ascontiguousarray(row_pair, np.int32)
+        out = np.empty((rp.size, t.shape[1]), np.float32)
+        self.lib.orc_moe_gather(out, t, rp, rp.size, k, t.shape[1])
+        return out
 
     def expf(self, x):
         x = np.ascontiguousarray(x, np.float32)

@@ -368,6 +368,39 @@ ORC_API void orc_argmax_rows(int *out, const float *logits, int T, long V, int t
     out[t] = orc_argmax(logits + (size_t)t * V, (int)V);
 }
 
+/* Grouping of (token, choice) pairs by expert, the contract of the reference's
+ * moe_group_kernel / moe_group_ep (kernels/moe.hpp:138-171, kernels/moe_ep.hpp:44-49):
+ * rows offsets[e] .. offsets[e+1] belong to local expert e_begin + e, in pair
+ * order; row_pair[row] is the pair (token * k + choice) in that row and
+ * own_row[pair] its inverse, -1 for a pair whose expert is not local (or -1,
+ * a finished token).  The reference has no CPU form of this step (forward()
+ * loops over experts instead), so this function restates the GPU kernel's
+ * documented result and is NOT pinned against a run of the reference. */
+ORC_API void orc_moe_group(const int *topk_e, int n_pairs, int e_begin, int e_count, int *counts,
+                           int *offsets, int *row_pair, int *own_row) {
+  int row = 0;
+  for (int e = 0; e < e_count; e++) {
+    offsets[e] = row;
+    for (int p = 0; p < n_pairs; p++)
+      if (topk_e[p] == e_begin + e) {
+        row_pair[row] = p;
+        own_row[p] = row;
+        row++;
+      }
+    counts[e] = row - offsets[e];
+  }
+  offsets[e_count] = row;
+  for (int p = 0; p < n_pairs; p++)
+    if (topk_e[p] < e_begin || topk_e[p] >= e_begin + e_count)
+      own_row[p] = -1;
+}
+
+/* Xg[row,:] = t[row_pair[row] / k, :] (moe_gather_kernel, kernels/moe.hpp:175-182). */
+ORC_API void orc_moe_gather(float *Xg, const float *t, const int *row_pair, int R, int k, int H) {
+  for (int r = 0; r < R; r++)
+    memcpy(Xg + (size_t)r * H, t + (size_t)(row_pair[r] / k) * H, (size_t)H * sizeof(float));
+}
+
 /* Host expf, exported so tests can compare a device exponential with the C
  * library's on chosen inputs. */
 ORC_API void orc_expf_array(float *out, const float *in, long n) {

@@ -466,3 +466,61 @@ def test_golden_vectors_through_the_gpu(gpu, golden):
         out = d.out((3,), np.int32)
         pkg.argmax(3, d.put(lg, dt), dt, gi.V, gi.V, d.put(np.zeros(3, np.uint64)), out)
         assert np.array_equal(out.get(), golden["argmax"])
+
+
+# ---- beside the path: grouping of (token, choice) pairs by expert, and the row gather ------
+
+@pytest.mark.parametrize("T,k,E,e_begin,e_count", [(512, 4, 32, 0, 32), (512, 4, 128, 0, 64), (512, 4, 128, 64, 64),
+                                                   (1024, 4, 128, 0, 128), (3, 4, 32, 0, 32), (1, 4, 32, 0, 32),
+                                                   (511, 3, 32, 0, 32), (4096, 4, 32, 0, 32), (16384, 4, 128, 0, 128),
+                                                   (77, 8, 200, 10, 150)])
+def test_moe_group(gpu, orc, T, k, E, e_begin, e_count):
+    pkg, d = gpu, Dev(gpu)
+    r = rng_of("group", T, k, E, e_begin)
+    e = np.stack([r.permutation(E)[:k] for _ in range(T)]).astype(np.int32)
+    e[::7] = -1  # finished tokens
+    n = T * k
+    want_counts, want_off, want_rp, want_own = orc.moe_group(e, e_begin, e_count)
+    # an independent statement of the contract: a stable sort of the local pairs by expert
+    flat = e.ravel()
+    local = np.flatnonzero((flat >= e_begin) & (flat < e_begin + e_count))
+    order = local[np.argsort(flat[local], kind="stable")]
+    assert np.array_equal(want_rp, order)
+    counts, off = d.out((e_count,), np.int32), d.out((e_count + 1,), np.int32)
+    rp, own = d.out((n,), np.int32), d.out((n,), np.int32)
+    pkg.moe_group(d.put(e), n, e_begin, e_count, counts, off, rp, own)
+    assert np.array_equal(counts.get(), want_counts)
+    assert np.array_equal(off.get(), want_off)
+    assert np.array_equal(rp.get()[:want_off[-1]], want_rp)
+    assert np.array_equal(own.get(), want_own)
+    # the map and its inverse
+    got_own = own.get()
+    assert np.array_equal(got_own[want_rp], np.arange(want_rp.size))
+    assert (got_own[np.setdiff1d(np.arange(n), local)] == -1).all()
+
+
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
+def test_moe_gather_and_grouped_combine(gpu, orc, dt):
+    """router -> group -> gather -> (expert rows) -> combine through own_row: the grouped row
+    order must give the same residual as the ungrouped one."""
+    pkg, d = gpu, Dev(gpu)
+    dt = pkg.BF16 if dt == "bf16" else pkg.F32
+    T, k, E, Hd = 300, 4, 32, 2880
+    r = rng_of("gather", dt)
+    scores = r.standard_normal((T, E)).astype(np.float32)
+    w, e = orc.router_rows(scores, k)
+    e[::9], w[::9] = -1, 0
+    _, off, row_pair, own_row = orc.moe_group(e, 0, E)
+    R = int(off[-1])
+    t = widen(pkg, r.standard_normal((T, Hd)), dt).reshape(T, Hd)
+    xg = d.out((R, Hd), dt)
+    pkg.moe_gather(R, d.put(t, dt), dt, T, d.put(row_pair), k, xg, Hd)
+    assert n_bit_diff(xg.get(), orc.moe_gather(t, row_pair, k)) == 0
+    # expert outputs per pair, stored in grouped order; combine reads them back through own_row
+    z_pair = r.standard_normal((T * k, Hd)).astype(np.float32)
+    z_grouped = z_pair[row_pair]
+    x = r.standard_normal((T, Hd)).astype(np.float32)
+    want = orc.combine_rows(x, z_pair, np.arange(T * k, dtype=np.int32).reshape(T, k), w, e, E)
+    xb = d.put_inout(x)
+    pkg.moe_combine(T, xb, d.put(z_grouped), pkg.F32, d.put(own_row), d.put(w), d.put(e), k, Hd, flags=pkg.EXACT)
+    assert n_bit_diff(xb.get(), want) == 0
