@@ -134,6 +134,13 @@ class ClockSampler:
                 "samples": len(sm), "power_w_max": float(max(pw))}
 
 
+def host_cores() -> int:
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except Exception:
+        return os.cpu_count() or 1
+
+
 def visible_gpu_index(local_rank: int) -> int:
     vis = os.environ.get("CUDA_VISIBLE_DEVICES")
     if vis:
@@ -162,7 +169,9 @@ class CpuChain:
         self.ref = oracle.Reference() if oracle.have_reference() else None
         self.kind = "reference" if self.ref is not None else "port"
         self.fn = self.ref if self.ref is not None else self.orc
-        self.threads = self.fn.max_threads()
+        # every core this process may run on; passed explicitly to each call, because launchers
+        # such as torchrun export OMP_NUM_THREADS=1
+        self.threads = host_cores()
         c = pkg.chain_config(model, pkg.BF16, 4096)
         self.c, self.T, self.sets = c, tokens, sets
         T, K, H = tokens, c.top_k, c.hidden
@@ -186,7 +195,7 @@ class CpuChain:
         self.ident = np.arange(T * K, dtype=np.int32).reshape(T, K)
 
     def step(self):
-        c, fn, orc, th = self.c, self.fn, self.orc, 0
+        c, fn, orc, th = self.c, self.fn, self.orc, self.threads
         x = orc.embed_rows(self.emb, self.tokens, threads=th)
         fn.add_rmsnorm_rows(x, None, self.gain[0], threads=th)
         for l in range(c.n_layers):
@@ -208,7 +217,7 @@ class CpuChain:
 
 def run_cpu(pkg, args, min_seconds: float, steps: int | None, warmup: int):
     """Times the CPU chain.  steps=None: repeat passes until min_seconds have gone by."""
-    threads = os.cpu_count() or 1
+    threads = host_cores()
     tokens = int(min(args.tokens_per_gpu, max(128, 8 * threads)))
     cpu = CpuChain(pkg, args.model, tokens, args.seed)
     for _ in range(max(1, warmup)):
