@@ -243,6 +243,44 @@ GPTOSS_API int gptoss_moe_gather(gptoss_stream_t stream, int R, const void *t,
                                  gptoss_dtype_t dtype, int n_tokens, const int *row_pair, int k,
                                  void *Xg, int H, unsigned flags);
 
+/*
+ * KV-cache write of one decode step, the half of rope_kv_bf16 that follows the
+ * rotation (kernels/fast_misc.hpp:48-127; launch gpu_engine.hpp:495-496): from
+ * each row of the biased, rotated qkv tensor (gptoss_qkv_bias_rope's output)
+ *   - the n_kv_heads key heads go to kc as bf16 (round to nearest even), at
+ *     (row, slot, head g, dim i) ->
+ *       (row * slots + (slot & ~63)) * kv_dim + g * 4096 + (slot & 63) * 64 + i
+ *     with kv_dim = n_kv_heads * 64 (kv_index_chunk64, fast_attention.hpp:558);
+ *   - the value heads go to vq as int8 codes c = round(v * 127 / max|v|)
+ *     clamped to +-127, at the byte offset of vq_index_chunk64
+ *     (fast_attention.hpp:591), and one fp32 scale max|v| / 127 per (slot, head)
+ *     to vs at vs_index_chunk64 (:597); an all-zero value vector gives codes 0
+ *     and scale 0.
+ * slot_of_row: the cache slot of each row (NULL: slot_scalar for every row, the
+ * engine's one slot per step); a slot outside [0, slots) skips the row.  slots
+ * must be a multiple of 64 and head_dim 64 (the layouts are defined for that).
+ * The row index doubles as the sequence index, as in the engine's decode step.
+ * Beside the path the fused kernels sit on (it feeds the attention kernel).
+ */
+GPTOSS_API int gptoss_kv_cache_write(gptoss_stream_t stream, int T, const void *qkv,
+                                     gptoss_dtype_t qkv_dtype, long row_stride, int n_q_heads,
+                                     int n_kv_heads, int head_dim, uint16_t *kc, int8_t *vq, float *vs,
+                                     int slots, const int *slot_of_row, int slot_scalar,
+                                     unsigned flags);
+
+/*
+ * The second half of a greedy pick fused into a logits producer: out[t] = the
+ * column named by keys[t] (0 if nothing was folded in), then keys[t] = 0.
+ * The producer folds its values into keys with the device functions of
+ * gptoss_argmax_key.cuh and never stores the logits.  Replaces
+ * argmax_keys_kernel (kernels/fast_gemm.hpp:706-714; launch :925) of
+ * gemm_bf16_argmax (gpu_engine.hpp:619).  Unlike gptoss_argmax, which sees the
+ * logits, this cannot reproduce sample_argmax's answer for a row whose
+ * element 0 is NaN (the CPU then returns 0); a NaN simply never wins.
+ */
+GPTOSS_API int gptoss_argmax_keys_finish(gptoss_stream_t stream, int T, unsigned long long *keys,
+                                         int *out, unsigned flags);
+
 /* How many slices (thread blocks) gptoss_argmax cuts each row into for T rows
  * of V logits on the current device; has_keys = 0 describes a call with
  * keys == NULL (always 1).  More than one slice means a second, tiny launch

@@ -70,6 +70,8 @@ PROTOTYPES = {
     "gptoss_argmax": (_i, [_p, _i, _p, _i, _l, _l, _p, _p, _u]),
     "gptoss_moe_group": (_i, [_p, _p, _i, _i, _i, _p, _p, _p, _p, _u]),
     "gptoss_moe_gather": (_i, [_p, _i, _p, _i, _i, _p, _i, _p, _i, _u]),
+    "gptoss_kv_cache_write": (_i, [_p, _i, _p, _i, _l, _i, _i, _i, _p, _p, _p, _i, _p, _i, _u]),
+    "gptoss_argmax_keys_finish": (_i, [_p, _i, _p, _p, _u]),
     "gptoss_argmax_slices": (_i, [_i, _l, _i, _i]),
     "gptoss_argmax_noalloc": (_i, [_p, _i, _p, _i, _l, _l, _p]),
     "gptoss_device_count": (_i, [C.POINTER(_i)]),
@@ -277,6 +279,28 @@ def moe_group(topk_e, n_pairs, e_begin, e_count, counts, offsets, row_pair, own_
 def moe_gather(R, t, dtype, n_tokens, row_pair, k, Xg, H, flags=0, stream=None):
     check(load().gptoss_moe_gather(stream, R, _ptr(t), dtype, n_tokens, _ptr(row_pair), k, _ptr(Xg), H, flags),
           "moe_gather")
+
+
+def kv_cache_write(T, qkv, dtype, row_stride, n_q, n_kv, head_dim, kc, vq, vs, slots, slot_of_row=None,
+                   slot_scalar=0, flags=0, stream=None):
+    check(load().gptoss_kv_cache_write(stream, T, _ptr(qkv), dtype, row_stride, n_q, n_kv, head_dim, _ptr(kc),
+                                       _ptr(vq), _ptr(vs), slots, _ptr(slot_of_row), slot_scalar, flags),
+          "kv_cache_write")
+
+
+def argmax_keys_finish(T, keys, out, flags=0, stream=None):
+    check(load().gptoss_argmax_keys_finish(stream, T, _ptr(keys), _ptr(out), flags), "argmax_keys_finish")
+
+
+def argmax_key_host(values: np.ndarray, cols: np.ndarray) -> np.ndarray:
+    """The 64-bit key of gptoss_argmax_key.cuh computed on the host (for tests and for
+    checking a producer): order-preserving value bits above the complemented column."""
+    v = np.ascontiguousarray(values, np.float32)
+    u = np.where(v == 0, np.uint32(0), v.view(np.uint32)).astype(np.uint32)
+    neg = (u & np.uint32(0x80000000)) != 0
+    u = np.where(neg, ~u, u | np.uint32(0x80000000)).astype(np.uint64)
+    key = (u << np.uint64(32)) | (~np.ascontiguousarray(cols, np.uint32)).astype(np.uint64)
+    return np.where(np.isnan(v), np.uint64(0), key)
 
 
 ARGMAX_NOALLOC_MAX_ROWS = 16384

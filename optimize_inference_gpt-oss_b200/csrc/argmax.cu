@@ -13,6 +13,7 @@
 // indices and zeroes them again.
 #include <cuda_bf16.h>
 
+#include "../../include/gptoss_argmax_key.cuh"
 #include "common.cuh"
 
 namespace gptoss {
@@ -21,12 +22,11 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kUnroll = 4;
 
-// Larger value => larger key; equal values => lower index wins; -0 == +0.
-// idx < 2^31.  Never 0 for a number, so 0 can mean "nothing seen".
+// Larger value => larger key; equal values => lower index wins; -0 == +0; never 0
+// for a number, so 0 can mean "nothing seen".  The formula is public
+// (gptoss_argmax_key.cuh) so that a logits producer can fold into the same words.
 __device__ __forceinline__ unsigned long long pick_key(float v, unsigned idx) {
-  uint32_t u = v == 0.0f ? 0u : __float_as_uint(v);
-  u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
-  return ((unsigned long long)u << 32) | (unsigned)~idx;
+  return gptoss_argmax_key(v, idx);
 }
 
 // Maximum of the values of one 16-byte piece; NaNs are ignored unless every
@@ -93,19 +93,19 @@ __device__ __forceinline__ int decode_pick(unsigned long long key, const LT *row
   return (int)~(unsigned)(key & 0xffffffffull);
 }
 
-// grid = (splits, T).  Vector path: V_vec elements per row, a multiple of the
+// grid = splits * T blocks; block b scans slice b % splits of row b / splits.  Vector path: V_vec elements per row, a multiple of the
 // piece width, start 16-byte aligned; the scalar tail [V_vec, V) is scanned by
 // the block of the last slice.
 template <typename LT>
 __global__ void __launch_bounds__(kThreads)
     argmax_slices(const LT *__restrict__ logits, long V, long row_stride, long pieces_per_row,
-                  long pieces_per_slice, unsigned long long *keys, int *__restrict__ out) {
+                  long pieces_per_slice, int splits, unsigned long long *keys, int *__restrict__ out) {
   pdl_prologue();
   constexpr int kPer = 16 / sizeof(LT); // values per 16-byte piece
   __shared__ unsigned long long scratch[kThreads / 32];
-  const int row = blockIdx.y;
+  const int row = blockIdx.x / splits, slice = blockIdx.x - row * splits;
   const LT *r = logits + (size_t)row * row_stride;
-  const long p0 = (long)blockIdx.x * pieces_per_slice;
+  const long p0 = (long)slice * pieces_per_slice;
   long p1 = p0 + pieces_per_slice;
   if (p1 > pieces_per_row)
     p1 = pieces_per_row;
@@ -131,7 +131,7 @@ __global__ void __launch_bounds__(kThreads)
     }
   }
   // scalar tail of the row, by the last slice's block
-  if (blockIdx.x == gridDim.x - 1)
+  if (slice == splits - 1)
     for (long i = pieces_per_row * kPer + threadIdx.x; i < V; i += kThreads) {
       const float v = load1(r + i);
       if (v > best) {
@@ -160,6 +160,16 @@ __global__ void argmax_finish(unsigned long long *keys, const LT *__restrict__ l
   keys[row] = 0ull;
 }
 
+// The decode half of a fused producer (gptoss_argmax_keys_finish).
+__global__ void argmax_keys_decode(unsigned long long *keys, int T, int *__restrict__ out) {
+  pdl_prologue();
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= T)
+    return;
+  out[row] = gptoss_argmax_column(keys[row]);
+  keys[row] = 0ull;
+}
+
 // Slices per row: enough blocks to fill the machine several times over, each
 // slice at least 2048 pieces (32 KB), at most 64 slices.
 int plan_slices(int T, long pieces, bool has_keys) {
@@ -182,14 +192,14 @@ int launch(cudaStream_t s, int T, const void *logits, long V, long row_stride,
   const bool vec = aligned16(logits) && (row_stride * sizeof(LT)) % 16 == 0;
   const long pieces = vec ? V / kPer : 0;
   const int splits = plan_slices(T, pieces, keys != nullptr);
-  if (T > 65535)
+  if ((long)T * splits > 0x7fffffffL)
     return GPTOSS_ERR_UNSUPPORTED;
   long per_slice = (pieces + splits - 1) / splits;
   if (per_slice < 1)
     per_slice = 1;
   unsigned long long *merge = splits > 1 ? keys : nullptr;
-  launch_kernel(argmax_slices<LT>, dim3(splits, T), dim3(kThreads), 0, s, lp, V, row_stride, pieces, per_slice, merge,
-                                                        out);
+  launch_kernel(argmax_slices<LT>, dim3((unsigned)((long)T * splits)), dim3(kThreads), 0, s, lp, V, row_stride,
+                pieces, per_slice, splits, merge, out);
   int st = launch_status();
   if (st != GPTOSS_OK || !merge)
     return st;
@@ -214,6 +224,20 @@ extern "C" int gptoss_argmax(gptoss_stream_t stream, int T, const void *logits,
   cudaStream_t s = as_stream(stream);
   return logits_dtype == GPTOSS_F32 ? launch<float>(s, T, logits, V, row_stride, keys, out)
                                     : launch<uint16_t>(s, T, logits, V, row_stride, keys, out);
+}
+
+extern "C" int gptoss_argmax_keys_finish(gptoss_stream_t stream, int T, unsigned long long *keys,
+                                         int *out, unsigned flags) {
+  using namespace gptoss;
+  const PdlScope pdl(flags);
+  if (T < 0)
+    return GPTOSS_ERR_BAD_ARG;
+  if (T == 0)
+    return GPTOSS_OK;
+  if (!keys || !out)
+    return GPTOSS_ERR_BAD_ARG;
+  launch_kernel(argmax_keys_decode, dim3((T + 255) / 256), dim3(256), 0, as_stream(stream), keys, T, out);
+  return launch_status();
 }
 
 extern "C" int gptoss_argmax_slices(int T, long V, gptoss_dtype_t logits_dtype, int has_keys) {

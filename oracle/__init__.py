@@ -210,6 +210,9 @@ class Oracle(_Lib):
         L.orc_moe_group.argtypes = [_i32p, C.c_int, C.c_int, C.c_int, _i32p, _i32p, _i32p, _i32p]
         L.orc_moe_gather.restype = None
         L.orc_moe_gather.argtypes = [_f32p, _f32p, _i32p, C.c_int, C.c_int, C.c_int]
+        L.orc_kv_cache_write.restype = None
+        L.orc_kv_cache_write.argtypes = [_f32p, C.c_long, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
+                                         C.c_void_p, C.c_int, _i32p]
         L.orc_expf_array.restype = None
         L.orc_expf_array.argtypes = [_f32p, _f32p, C.c_long]
 
@@ -271,6 +274,13 @@ class Oracle(_Lib):
         out = np.empty((rp.size, t.shape[1]), np.float32)
         self.lib.orc_moe_gather(out, t, rp, rp.size, k, t.shape[1])
         return out
+
+    def kv_cache_write(self, qkv, n_q, n_kv, kc, vq, vs, slots, slot_of_row):
+        """Writes into the given cache arrays (uint16 kc, int8 vq, float32 vs) in place."""
+        qkv = np.ascontiguousarray(qkv, np.float32)
+        assert kc.dtype == np.uint16 and vq.dtype == np.int8 and vs.dtype == np.float32
+        self.lib.orc_kv_cache_write(qkv, qkv.shape[1], qkv.shape[0], n_q, n_kv, kc.ctypes.data, vq.ctypes.data,
+                                    vs.ctypes.data, slots, np.ascontiguousarray(slot_of_row, np.int32))
 
     def expf(self, x):
         x = np.ascontiguousarray(x, np.float32)

@@ -401,6 +401,53 @@ ORC_API void orc_moe_gather(float *Xg, const float *t, const int *row_pair, int 
     memcpy(Xg + (size_t)r * H, t + (size_t)(row_pair[r] / k) * H, (size_t)H * sizeof(float));
 }
 
+/* KV-cache write of one decode step: the cache half of the reference's
+ * rope_kv_bf16_kernel (kernels/fast_misc.hpp:48-108) with the chunk64 index
+ * functions of kernels/fast_attention.hpp:558-600.  qkv rows are already biased
+ * and rotated.  Keys: bf16 round-to-nearest-even.  Values: amax = max|v| over
+ * the head's 64 numbers, inv = amax > 0 ? 127/amax : 0, code =
+ * clamp(rintf(v*inv), +-127), scale = amax/127, all in fp32.  Like the grouping
+ * step this restates a GPU kernel that has no CPU form in the reference, so it
+ * is NOT pinned against a run of the reference. */
+static size_t orc_chunk64(int b, int slot, int g, int i, int slots, int kv_dim) {
+  return ((size_t)b * slots + (size_t)(slot & ~63)) * kv_dim + (size_t)g * 64 * 64 +
+         (size_t)(slot & 63) * 64 + i;
+}
+static uint16_t orc_bf16(float f) {
+  uint32_t u;
+  memcpy(&u, &f, 4);
+  if ((u & 0x7fffffffu) > 0x7f800000u)
+    return (uint16_t)((u >> 16) | 0x40u);
+  u += 0x7fffu + ((u >> 16) & 1u);
+  return (uint16_t)(u >> 16);
+}
+ORC_API void orc_kv_cache_write(const float *qkv, long row_stride, int T, int n_q_heads, int n_kv_heads,
+                                uint16_t *kc, int8_t *vq, float *vs, int slots, const int *slot_of_row) {
+  const int kv_dim = n_kv_heads * 64;
+  for (int b = 0; b < T; b++) {
+    const int slot = slot_of_row[b];
+    if (slot < 0 || slot >= slots)
+      continue;
+    const float *k = qkv + (size_t)b * row_stride + (size_t)n_q_heads * 64, *v = k + kv_dim;
+    for (int g = 0; g < n_kv_heads; g++) {
+      float amax = 0.0f;
+      for (int i = 0; i < 64; i++) {
+        kc[orc_chunk64(b, slot, g, i, slots, kv_dim)] = orc_bf16(k[g * 64 + i]);
+        amax = fmaxf(amax, fabsf(v[g * 64 + i]));
+      }
+      const float inv = amax > 0.0f ? 127.0f / amax : 0.0f;
+      for (int i = 0; i < 64; i++) {
+        float c = rintf(v[g * 64 + i] * inv);
+        c = fminf(fmaxf(c, -127.0f), 127.0f);
+        const size_t at = orc_chunk64(b, slot & ~15, g, 0, slots, kv_dim) + ((slot >> 2) & 3) * 256 +
+                          (i >> 2) * 16 + (i & 3) * 4 + (slot & 3);
+        vq[at] = (int8_t)c;
+      }
+      vs[orc_chunk64(b, slot, g, 0, slots, kv_dim) / 64] = amax / 127.0f;
+    }
+  }
+}
+
 /* Host expf, exported so tests can compare a device exponential with the C
  * library's on chosen inputs. */
 ORC_API void orc_expf_array(float *out, const float *in, long n) {

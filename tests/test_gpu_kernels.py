@@ -6,6 +6,7 @@ bit-identical.  Shapes include the odd ones the reference tests use (H 64/1000/4
 head mixes 8+1 / 32+4, k 2..8, E 16..200) and every output buffer sits between canaries."""
 from __future__ import annotations
 
+import os
 import zlib
 
 import numpy as np
@@ -524,3 +525,114 @@ def test_moe_gather_and_grouped_combine(gpu, orc, dt):
     xb = d.put_inout(x)
     pkg.moe_combine(T, xb, d.put(z_grouped), pkg.F32, d.put(own_row), d.put(w), d.put(e), k, Hd, flags=pkg.EXACT)
     assert n_bit_diff(xb.get(), want) == 0
+
+
+# ---- the argmax key as a public contract for logits producers --------------------------------
+
+def test_argmax_keys_finish_matches_argmax(gpu, orc):
+    """Keys folded on the host with the documented formula, decoded on the device, equal the
+    greedy pick; the words are handed back zeroed."""
+    pkg, d = gpu, Dev(gpu)
+    T, Vv = 64, 5000
+    lg = _logits(rng_of("keys"), T, Vv, pkg.F32, pkg)
+    lg[5, 0] = 1.0  # (a producer that never sees the logits cannot reproduce the NaN-in-front rule)
+    want = orc.argmax_rows(lg)
+    keys_host = pkg.argmax_key_host(lg, np.broadcast_to(np.arange(Vv, dtype=np.uint32), lg.shape)).max(axis=1)
+    keys = d.put(keys_host.astype(np.uint64))
+    out = d.out((T,), np.int32)
+    pkg.argmax_keys_finish(T, keys, out)
+    assert np.array_equal(out.get(), want)
+    assert not keys.numpy(np.uint64, T).any()
+
+
+def test_argmax_key_header_in_a_producer_kernel(gpu, orc, tmp_path):
+    """A small producer compiled against include/gptoss_argmax_key.cuh folds tiles of a logits
+    matrix into the keys (as a GEMM epilogue would) without storing anything else."""
+    import ctypes as C
+    import shutil
+    import subprocess
+    from conftest import ROOT
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        pytest.skip("no nvcc on this machine")
+    pkg, d = gpu, Dev(gpu)
+    src = tmp_path / "producer.cu"
+    src.write_text(r'''
+#include "gptoss_argmax_key.cuh"
+// one block per (row, tile of 256 columns): warp-reduce the keys, then one atomic per warp
+__global__ void produce(const float* logits, int V, unsigned long long* keys) {
+  const int row = blockIdx.y, col = blockIdx.x * 256 + threadIdx.x;
+  unsigned long long k = col < V ? gptoss_argmax_key(logits[(size_t)row * V + col], col) : 0ull;
+  for (int o = 16; o > 0; o >>= 1) k = gptoss_argmax_better(k, __shfl_xor_sync(0xffffffffu, k, o));
+  if ((threadIdx.x & 31) == 0) gptoss_argmax_fold(keys, row, k);
+}
+extern "C" int run(const float* logits, int T, int V, unsigned long long* keys) {
+  produce<<<dim3((V + 255) / 256, T), 256>>>(logits, V, keys);
+  return (int)cudaDeviceSynchronize();
+}
+''')
+    so = tmp_path / "producer.so"
+    subprocess.run([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-Xcompiler", "-fPIC", "-I",
+                    os.path.join(ROOT, "include"), str(src), "-o", str(so)], check=True)
+    lib = C.CDLL(str(so))
+    lib.run.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p]
+    T, Vv = 40, 20011
+    lg = _logits(rng_of("producer"), T, Vv, pkg.F32, pkg)
+    lg[5, 0] = 1.0
+    keys = d.put(np.zeros(T, np.uint64))
+    assert lib.run(d.put(lg).ptr, T, Vv, keys.ptr) == 0
+    out = d.out((T,), np.int32)
+    pkg.argmax_keys_finish(T, keys, out)
+    assert np.array_equal(out.get(), orc.argmax_rows(lg))
+
+
+def test_argmax_many_rows(gpu, orc):
+    """More rows than a grid's y dimension would hold."""
+    pkg, d = gpu, Dev(gpu)
+    T, Vv = 70000, 64
+    lg = (3.0 * rng_of("manyrows").standard_normal((T, Vv))).astype(np.float32)
+    out = d.out((T,), np.int32)
+    pkg.argmax(T, d.put(lg), pkg.F32, Vv, Vv, d.put(np.zeros(T, np.uint64)), out)
+    assert np.array_equal(out.get(), orc.argmax_rows(lg, threads=0))
+
+
+# ---- beside the path: the KV-cache write that follows the rotation -------------------------
+
+@pytest.mark.parametrize("T,nq,nkv,slots", [(37, 64, 8, 1024), (512, 64, 8, 128), (5, 8, 1, 64), (33, 32, 4, 64)])
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+def test_kv_cache_write(gpu, orc, T, nq, nkv, slots, dt):
+    pkg, d = gpu, Dev(gpu)
+    dt = pkg.F32 if dt == "f32" else pkg.BF16
+    r = rng_of("kvwrite", T, nq, nkv, slots)
+    row = (nq + 2 * nkv) * 64
+    qkv = widen(pkg, r.standard_normal((T, row)) * 3, dt).reshape(T, row)
+    qkv[0, (nq + nkv) * 64:(nq + nkv + 1) * 64] = 0.0          # an all-zero value vector: codes 0, scale 0
+    qkv[1 % T, (nq + nkv) * 64 + 3] = np.float32(2.0 ** 100)   # one huge value (exact in bf16): the others quantise to 0
+    slot = r.integers(0, slots, T).astype(np.int32)
+    slot[T // 2] = slots + 5                                   # no place in the cache: row skipped
+    kv_dim = nkv * 64
+    n_k = T * slots * kv_dim
+    kc0 = np.full(n_k, 0x5555, np.uint16)
+    vq0 = np.full(n_k, 0x55, np.int8)
+    vs0 = np.full(n_k // 64, np.float32(7.5), np.float32)
+    want_k, want_q, want_s = kc0.copy(), vq0.copy(), vs0.copy()
+    orc.kv_cache_write(qkv, nq, nkv, want_k, want_q, want_s, slots, slot)
+    kc, vq, vs = d.put_inout(kc0), d.put_inout(vq0), d.put_inout(vs0)
+    pkg.kv_cache_write(T, d.put(qkv, dt), dt, row, nq, nkv, 64, kc, vq, vs, slots, slot_of_row=d.put(slot))
+    assert np.array_equal(kc.get(as_f32=False), want_k)
+    assert np.array_equal(vq.get(), want_q)
+    assert n_bit_diff(vs.get(), want_s) == 0
+    # one slot for the whole batch (the engine's call shape); everything else keeps its fill
+    kc2, vq2, vs2 = d.put_inout(kc0), d.put_inout(vq0), d.put_inout(vs0)
+    pkg.kv_cache_write(T, d.put(qkv, dt), dt, row, nq, nkv, 64, kc2, vq2, vs2, slots, slot_scalar=slots - 1)
+    want_k, want_q, want_s = kc0.copy(), vq0.copy(), vs0.copy()
+    orc.kv_cache_write(qkv, nq, nkv, want_k, want_q, want_s, slots, np.full(T, slots - 1, np.int32))
+    assert np.array_equal(kc2.get(as_f32=False), want_k) and np.array_equal(vq2.get(), want_q)
+    assert n_bit_diff(vs2.get(), want_s) == 0
+    # spot check of the layout, independent of the oracle: the scale of the last row's last
+    # head sits at chunk64(b, slot, g, 0) / 64 and is max|v| / 127
+    got_s = vs2.get()
+    b, g, s_ = T - 1, nkv - 1, slots - 1
+    at = ((b * slots + (s_ & ~63)) * kv_dim + g * 4096 + (s_ & 63) * 64) // 64
+    v = qkv[b, (nq + nkv + g) * 64:(nq + nkv + g + 1) * 64]
+    assert got_s[at] == np.float32(np.abs(v).max()) / np.float32(127.0)
