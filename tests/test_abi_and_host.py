@@ -146,3 +146,14 @@ def test_shard_ranges(pkg):
         sh.shard_range(1000, 4, 0, 1024)
     with pytest.raises(ValueError):
         sh.shard_range(8, 4, 4)
+
+
+def test_reference_named_launchers_compile_as_plain_cxx(tmp_path):
+    """include/gptoss_launchers.hpp (the reference's launcher names over the C ABI) and the demo
+    that uses it build with g++ alone and link against the library."""
+    out = tmp_path / "launcher_demo"
+    pkg_dir = os.path.join(ROOT, "optimize_inference_gpt-oss_b200")
+    subprocess.run(["g++", "-std=c++17", "-Wall", "-Werror", "-I", os.path.join(ROOT, "include"),
+                    os.path.join(ROOT, "tests", "cpp", "launcher_demo.cpp"), "-o", str(out), "-L", pkg_dir,
+                    "-lgptoss_b200", f"-Wl,-rpath,{pkg_dir}"], check=True)
+    assert out.exists()
