@@ -147,6 +147,7 @@ typedef enum {
   GPTOSS_BUF_TOPK_E,  /* [T, top_k] int32 */
   GPTOSS_BUF_SWIGLU,  /* [top_k T, inter] act_dtype */
   GPTOSS_BUF_NEXT,    /* [T] int32: picked tokens */
+  GPTOSS_BUF_ROW_DONE, /* [T] int32: non-zero = finished request: no experts, residual frozen */
   GPTOSS_BUF_COUNT
 } gptoss_chain_buffer_t;
 
@@ -173,6 +174,24 @@ GPTOSS_API int gptoss_chain_enqueue(gptoss_chain_t *chain, int T, int use_graph)
  * tokens back, synchronise the stream.  Host pointers (pinned for speed). */
 GPTOSS_API int gptoss_chain_step(gptoss_chain_t *chain, int T, const int *tokens_host,
                                  const int *pos_host, int *next_host);
+
+/* Serves one wave of requests the way the reference engine does (gpu_run_wave,
+ * gpu_engine.hpp:761-841): request b starts from the first token of its prompt; every step
+ * all rows sit at the same position; after the step a row takes the next prompt token while
+ * it has one and the picked token afterwards; a row finishes when it takes one of the two
+ * end tokens (199999, 200002), is then marked in GPTOSS_BUF_ROW_DONE (re-uploaded only when
+ * it changed) so that the router gives it no experts, and the wave ends after `steps`
+ * positions or when every row is done.
+ *   prompt_tokens / prompt_offsets: the prompts back to back; request b owns
+ *       [prompt_offsets[b], prompt_offsets[b+1]), at least one token each
+ *   generated: [n_requests, steps + 2] int32, request b's generated tokens from column 0,
+ *       closed with -1 (as the reference's output rows are)
+ *   n_generated: the reference's count (for each request, position reached - prompt
+ *       length + 1)
+ * n_requests <= max_tokens, steps <= max_pos.  Host pointers; synchronous. */
+GPTOSS_API int gptoss_chain_run_wave(gptoss_chain_t *chain, const int *prompt_tokens,
+                                     const int *prompt_offsets, int n_requests, int steps,
+                                     int *generated, long long *n_generated, int *steps_run);
 
 typedef enum {
   GPTOSS_K_EMBED = 0,

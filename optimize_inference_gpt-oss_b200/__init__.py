@@ -29,7 +29,7 @@ MAX_TOPK, MAX_EXPERTS = 8, 256
 # gptoss_chain_buffer_t
 (BUF_EMBEDDING, BUF_GAIN_ATTN, BUF_GAIN_FFN, BUF_GAIN_OUT, BUF_QKV_BIAS, BUF_COS, BUF_SIN,
  BUF_ATTN_PROJ, BUF_QKV, BUF_ROUTER, BUF_MLP1, BUF_EXPERT, BUF_LOGITS, BUF_TOKENS, BUF_POS, BUF_X,
- BUF_NORMED, BUF_QKV_OUT, BUF_TOPK_W, BUF_TOPK_E, BUF_SWIGLU, BUF_NEXT, BUF_COUNT) = range(23)
+ BUF_NORMED, BUF_QKV_OUT, BUF_TOPK_W, BUF_TOPK_E, BUF_SWIGLU, BUF_NEXT, BUF_ROW_DONE, BUF_COUNT) = range(24)
 # gptoss_chain_kernel_t
 KERNEL_KINDS = ("embed", "norm", "rope", "add_norm", "router", "swiglu", "combine", "argmax")
 
@@ -106,6 +106,7 @@ PROTOTYPES = {
     "gptoss_chain_fill_synthetic": (_i, [_p, _i, C.c_uint64, _i]),
     "gptoss_chain_enqueue": (_i, [_p, _i, _i]),
     "gptoss_chain_step": (_i, [_p, _i, _p, _p, _p]),
+    "gptoss_chain_run_wave": (_i, [_p, _p, _p, _i, _i, _p, C.POINTER(C.c_longlong), C.POINTER(_i)]),
     "gptoss_chain_profile": (_i, [_p, _i, _i, _i, C.POINTER(C.c_double), C.POINTER(_l)]),
     "gptoss_chain_kernel_bytes": (_z, [_p, _i, _i]),
     "gptoss_chain_launches_per_step": (_i, [_p, _i]),
@@ -428,6 +429,20 @@ class Chain:
         T = tokens_host.size
         check(load().gptoss_chain_step(self.h, T, tokens_host.ctypes.data, pos_host.ctypes.data,
                                        next_host.ctypes.data), "chain_step")
+
+    def run_wave(self, prompts, steps: int):
+        """Serves one wave (gptoss_chain_run_wave).  prompts: a list of token lists.  Returns
+        (generated [n, steps + 2] int32 closed with -1, the reference's generated-token count,
+        steps actually run)."""
+        offs = np.zeros(len(prompts) + 1, np.int32)
+        offs[1:] = np.cumsum([len(p) for p in prompts])
+        toks = np.ascontiguousarray(np.concatenate([np.asarray(p, np.int32) for p in prompts]) if prompts
+                                    else np.zeros(0, np.int32))
+        out = np.empty((len(prompts), steps + 2), np.int32)
+        total, ran = C.c_longlong(0), _i(0)
+        check(load().gptoss_chain_run_wave(self.h, toks.ctypes.data, offs.ctypes.data, len(prompts), steps,
+                                           out.ctypes.data, C.byref(total), C.byref(ran)), "chain_run_wave")
+        return out, int(total.value), int(ran.value)
 
     def profile(self, T: int, steps: int, mode: int = 0):
         """Per kernel kind: (summed device ms, launches).  mode 0: an event pair per launch;

@@ -31,7 +31,7 @@ struct gptoss_chain {
   void *attn_proj = nullptr, *qkv = nullptr, *router = nullptr, *mlp1 = nullptr, *expert = nullptr,
        *logits = nullptr;
   // state
-  int *tokens = nullptr, *pos = nullptr, *next = nullptr, *topk_e = nullptr, *own_row = nullptr;
+  int *tokens = nullptr, *pos = nullptr, *next = nullptr, *topk_e = nullptr, *own_row = nullptr, *row_done = nullptr;
   float *x = nullptr, *topk_w = nullptr;
   void *normed = nullptr, *qkv_out = nullptr, *swiglu = nullptr;
   unsigned long long *keys = nullptr;
@@ -91,6 +91,7 @@ BufInfo buf_info(const gptoss_chain *c, gptoss_chain_buffer_t which) {
   case GPTOSS_BUF_TOPK_E: return {c->topk_e, T * K * 4, 0};
   case GPTOSS_BUF_SWIGLU: return {c->swiglu, K * T * (size_t)g.inter * a, 0};
   case GPTOSS_BUF_NEXT: return {c->next, T * 4, 0};
+  case GPTOSS_BUF_ROW_DONE: return {c->row_done, T * 4, 0};
   default: return {nullptr, 0, 0};
   }
 }
@@ -150,7 +151,7 @@ int issue_step(gptoss_chain *c, int T, cudaStream_t s, Hook *hook, int only = -1
                             g.flags));
     // [router GEMM] -> stand-in logits; top-k + softmax
     STEP(GPTOSS_K_ROUTER, gptoss_router_topk(gs, T, layer_ptr(c, GPTOSS_BUF_ROUTER, l), a,
-                                             g.n_experts, K, c->topk_w, c->topk_e, nullptr, nullptr, g.flags));
+                                             g.n_experts, K, c->topk_w, c->topk_e, c->row_done, nullptr, g.flags));
     // [mlp1 GEMM] -> stand-in gate/up rows; SwiGLU
     STEP(GPTOSS_K_SWIGLU, gptoss_swiglu(gs, layer_ptr(c, GPTOSS_BUF_MLP1, l), a, c->swiglu, a,
                                         (size_t)K * T, g.inter, g.swiglu_limit, g.flags));
@@ -271,6 +272,7 @@ int gptoss_chain_create(const gptoss_chain_config_t *cfg, int max_tokens, int n_
   ALLOC(swiglu, K * T * (size_t)cfg->inter * a);
   ALLOC(keys, T * 8);
   ALLOC(own_row, T * K * 4);
+  ALLOC(row_done, T * 4);
   c->flush_bytes = (size_t)256 << 20;
   ALLOC(flush, c->flush_bytes);
 #undef ALLOC
@@ -285,6 +287,8 @@ int gptoss_chain_create(const gptoss_chain_config_t *cfg, int max_tokens, int n_
       ident[i] = (int)i;
     st = cuda_status(cudaMemcpy(c->own_row, ident.data(), ident.size() * 4, cudaMemcpyHostToDevice));
   }
+  if (st == GPTOSS_OK)
+    st = cuda_status(cudaMemsetAsync(c->row_done, 0, T * 4, c->stream));
   if (st == GPTOSS_OK)
     st = cuda_status(cudaMemsetAsync(c->tokens, 0, T * 4, c->stream));
   if (st == GPTOSS_OK)
@@ -473,6 +477,86 @@ int gptoss_chain_step(gptoss_chain_t *c, int T, const int *tokens_host, const in
     st = cuda_status(cudaMemcpyAsync(next_host, c->next, (size_t)T * 4, cudaMemcpyDeviceToHost, c->stream));
   if (st == GPTOSS_OK)
     st = cuda_status(cudaStreamSynchronize(c->stream));
+  return st;
+}
+
+int gptoss_chain_run_wave(gptoss_chain_t *c, const int *prompt_tokens, const int *prompt_offsets,
+                          int n_requests, int steps, int *generated, long long *n_generated,
+                          int *steps_run) {
+  if (!c || n_requests < 0 || n_requests > c->max_tokens || steps < 0 || steps > c->cfg.max_pos)
+    return GPTOSS_ERR_BAD_ARG;
+  if (n_generated)
+    *n_generated = 0;
+  if (steps_run)
+    *steps_run = 0;
+  if (n_requests == 0)
+    return GPTOSS_OK;
+  if (!prompt_tokens || !prompt_offsets || !generated)
+    return GPTOSS_ERR_BAD_ARG;
+  const int n = n_requests, width = steps + 2;
+  for (int b = 0; b < n; b++)
+    if (prompt_offsets[b + 1] - prompt_offsets[b] < 1)
+      return GPTOSS_ERR_BAD_ARG; // every request needs at least one prompt token
+  const int eos_a = 199999, eos_b = 200002; // the two end tokens of the gpt-oss vocabulary
+  std::vector<int> cur(n), next(n), done(n, 0), position(n, 0);
+  for (int b = 0; b < n; b++)
+    cur[b] = prompt_tokens[prompt_offsets[b]];
+  for (size_t i = 0; i < (size_t)n * width; i++)
+    generated[i] = -1;
+  int st = cuda_status(cudaMemsetAsync(c->row_done, 0, (size_t)n * 4, c->stream));
+  bool done_changed = false;
+  long long total = 0;
+  int active = n, pos = 0;
+  while (st == GPTOSS_OK && pos < steps && active > 0) {
+    // the host side of a step: tokens in (and the done mask when it changed), ids out
+    if (done_changed) {
+      st = cuda_status(cudaMemcpyAsync(c->row_done, done.data(), (size_t)n * 4, cudaMemcpyHostToDevice, c->stream));
+      done_changed = false;
+    }
+    for (int b = 0; b < n; b++)
+      position[b] = pos; // one position for the whole batch, as in the engine
+    if (st == GPTOSS_OK)
+      st = gptoss_chain_step(c, n, cur.data(), position.data(), next.data());
+    if (st != GPTOSS_OK)
+      break;
+    pos++;
+    for (int b = 0; b < n; b++) {
+      if (done[b])
+        continue;
+      const int np = prompt_offsets[b + 1] - prompt_offsets[b];
+      int *out = generated + (size_t)b * width;
+      int token;
+      if (pos < np) {
+        token = prompt_tokens[prompt_offsets[b] + pos];
+      } else {
+        token = next[b];
+        out[pos - np] = token;
+      }
+      if (token == eos_a || token == eos_b) {
+        done[b] = 1;
+        done_changed = true;
+        active--;
+        if (pos - np + 1 >= 0)
+          out[pos - np + 1] = -1;
+        total += pos - np + 1;
+      }
+      cur[b] = token;
+    }
+  }
+  for (int b = 0; b < n && st == GPTOSS_OK; b++) {
+    if (done[b])
+      continue;
+    const int np = prompt_offsets[b + 1] - prompt_offsets[b];
+    if (pos - np + 1 >= 0)
+      generated[(size_t)b * width + (pos - np + 1)] = -1;
+    total += pos - np + 1;
+  }
+  if (st == GPTOSS_OK && done_changed) // leave the mask on the device as the wave ended
+    st = cuda_status(cudaMemcpy(c->row_done, done.data(), (size_t)n * 4, cudaMemcpyHostToDevice));
+  if (n_generated)
+    *n_generated = total;
+  if (steps_run)
+    *steps_run = pos;
   return st;
 }
 

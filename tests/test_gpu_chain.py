@@ -173,3 +173,75 @@ def test_chain_rejects_bad_sizes(gpu):
     c.top_k = 9
     with pytest.raises(pkg.GptossError):
         pkg.Chain(c, 8, 1)
+
+
+def _wave_reference(prompts, picks, steps):
+    """The reference's wave loop (gpu_engine.hpp:777-841) with the model replaced by a fixed
+    pick per row -- which is what the chain produces, since its logits are stand-ins."""
+    n, eos = len(prompts), (199999, 200002)
+    out = np.full((n, steps + 2), -1, np.int32)
+    done = [False] * n
+    total, active, pos = 0, n, 0
+    while pos < steps and active > 0:
+        pos += 1
+        for b in range(n):
+            if done[b]:
+                continue
+            npr = len(prompts[b])
+            if pos < npr:
+                token = prompts[b][pos]
+            else:
+                token = picks[b]
+                out[b, pos - npr] = token
+            if token in eos:
+                done[b] = True
+                active -= 1
+                if pos - npr + 1 >= 0:
+                    out[b, pos - npr + 1] = -1
+                total += pos - npr + 1
+    for b in range(n):
+        if not done[b]:
+            npr = len(prompts[b])
+            if pos - npr + 1 >= 0:
+                out[b, pos - npr + 1] = -1
+            total += pos - npr + 1
+    return out, total, pos, np.array(done, np.int32)
+
+
+def test_wave_loop_with_finished_rows(gpu, orc):
+    """Prompts fed one token per step, picked tokens afterwards, rows finishing on an end token
+    (from the model or inside a prompt), the done mask reaching the router."""
+    pkg = gpu
+    c = pkg.chain_config(20, pkg.BF16, max_pos=64)
+    c.n_layers = 2
+    n, steps = 24, 12
+    ch = pkg.Chain(c, n, 2)
+    try:
+        ch.fill_synthetic(n, seed=21)
+        logits = ch.download(pkg.BUF_LOGITS, 0, np.uint16, (n, c.vocab))
+        big = pkg.to_bf16_bits(np.array([1000.0], np.float32))[0]
+        logits[0, 199999] = logits[5, 199999] = logits[7, 200002] = big  # these rows pick an end token
+        ch.upload(pkg.BUF_LOGITS, 0, logits)
+        picks = orc.argmax_rows(pkg.from_bf16_bits(logits).reshape(n, c.vocab), threads=0)
+        r = np.random.default_rng(3)
+        prompts = [list(r.integers(0, 199000, 1 + b % 6)) for b in range(n)]
+        prompts[3] = [11, 22, 200002, 33, 44]       # an end token inside the prompt
+        prompts[9] = list(r.integers(0, 199000, 20))  # a prompt longer than the wave
+        want_out, want_total, want_pos, want_done = _wave_reference(prompts, picks, steps)
+        out, total, ran = ch.run_wave(prompts, steps)
+        assert ran == want_pos and total == want_total
+        assert np.array_equal(out, want_out)
+        assert np.array_equal(ch.download(pkg.BUF_ROW_DONE, 0, np.int32, (n,)), want_done)
+        # rows that were finished before the last step got no experts in it
+        e = ch.download(pkg.BUF_TOPK_E, 0, np.int32, (n, c.top_k))
+        w = ch.download(pkg.BUF_TOPK_W, 0, np.float32, (n, c.top_k))
+        early = np.array([b in (0, 3, 5, 7) for b in range(n)])
+        assert (e[early] == -1).all() and (w[early] == 0).all() and (e[~early] >= 0).all()
+        # everybody done: the wave stops early
+        logits[:, 199999] = big
+        ch.upload(pkg.BUF_LOGITS, 0, logits)
+        short = [[1, 2]] * n
+        out, total, ran = ch.run_wave(short, steps)
+        assert ran == 2 and total == n * 1 and (out[:, 0] == 199999).all() and (out[:, 1] == -1).all()
+    finally:
+        ch.close()
