@@ -101,8 +101,11 @@ inline size_t dtype_size(gptoss_dtype_t d) { return d == GPTOSS_F32 ? 4 : 2; }
 // 24-layer chain 15 % slower (and no faster at 64 or 512 tokens): blocks of kernels ahead
 // in the stream became resident, sat in their wait, and took the SM slots that the
 // persistent grids of the kernels actually running count on having all at once.  The flag
-// therefore pays off only behind a producer that signals early itself (a GEMM with a
-// programmatic-launch epilogue); between these kernels it is neutral.
+// Signalling late instead (a row kernel's block when it starts its last row, a one-shot
+// grid's blocks after their wait, so that at most two kernels are ever resident) was also
+// measured: 1 % slower than not signalling.  The flag therefore pays off only behind a
+// producer that signals early itself (a GEMM with a programmatic-launch epilogue); between
+// these kernels it is neutral.
 __device__ __forceinline__ void pdl_prologue() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // ---- 128-bit memory access ----------------------------------------------------
