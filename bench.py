@@ -62,6 +62,9 @@ def parse_args():
     ap.add_argument("--pdl", action="store_true",
                     help="launch the chain's kernels with programmatic stream serialization (GPTOSS_PDL); "
                          "measured neutral to slightly negative between these kernels, so off by default")
+    ap.add_argument("--split-embed-norm", action="store_true",
+                    help="open the step with the reference's two launches (gather, then layer 0's norm) "
+                         "instead of the fused one")
     ap.add_argument("--no-host-operands", action="store_true",
                     help="skip the extra e2e leg that re-sends every stand-in tensor from host memory each step")
     ap.add_argument("--vocab", type=int, default=0, help="override the vocabulary size (profiler mode: smaller footprint)")
@@ -354,6 +357,8 @@ def main():
         c.vocab = args.vocab
     if args.pdl:
         c.flags |= pkg.PDL
+    if args.split_embed_norm:
+        c.flags |= pkg.CHAIN_SPLIT_EMBED_NORM
     sets = args.standin_sets or c.n_layers
     t_setup = time.perf_counter()
     chain = pkg.Chain(c, T, sets)
@@ -466,6 +471,12 @@ def main():
         cpu, n, el = run_cpu(pkg, args, args.cpu_seconds, None, 1)
         line["cpu_baseline"] = {"value": cpu.T * n / el, "unit": "tokens/s", "cores": cpu.threads, "kind": cpu.kind,
                                 "sample": f"{n} passes in {el:.1f} s; " + cpu.describe()}
+        # the reference as it ships runs these ops serially per token: the same pass on one thread
+        cpu.threads = 1
+        t0 = time.perf_counter()
+        cpu.step()
+        line["cpu_baseline"]["one_thread"] = {"value": cpu.T / (time.perf_counter() - t0), "unit": "tokens/s",
+                                              "cores": 1, "sample": "one pass"}
     if rank == 0:
         print(json.dumps(line), flush=True)
     chain.close()

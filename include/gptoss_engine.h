@@ -79,8 +79,7 @@ GPTOSS_API int gptoss_synth_uniform_int(int *dst_host, size_t count, uint64_t se
 /* ---- the layer chain ------------------------------------------------------------
  * One decode step of the engine with the GEMMs and the attention taken out:
  *
- *   embed                                   (step_embed,      gpu_engine.hpp:461)
- *   norm of layer 0                         (layer_attention, :491)
+ *   embed + norm of layer 0, one launch     (step_embed, gpu_engine.hpp:461; layer_attention, :491)
  *   per layer:  [QKV GEMM]  bias + RoPE     (:493-496)
  *               [attention, out GEMM]  residual add + norm      (:499-504)
  *               [router GEMM]  top-k + softmax                  (layer_route, :522-527)
@@ -97,13 +96,18 @@ GPTOSS_API int gptoss_synth_uniform_int(int *dst_host, size_t count, uint64_t se
  * chain exactly as in the engine. */
 typedef struct gptoss_chain gptoss_chain_t;
 
+/* Bit of gptoss_chain_config_t.flags that only the chain reads: open the step with the
+ * reference's two launches (gptoss_embed, then gptoss_add_rmsnorm) instead of the fused
+ * gptoss_embed_rmsnorm.  Kernels ignore it. */
+#define GPTOSS_CHAIN_SPLIT_EMBED_NORM 0x100u
+
 typedef struct {
   int vocab, hidden, n_experts, top_k, inter, n_layers, head_dim, n_q_heads, n_kv_heads;
   int max_pos;    /* rows of the cos/sin tables (positions 0..max_pos-1) */
   float orig_ctx; /* initial_context_length */
   float theta, factor, beta_fast, beta_slow, swiglu_limit;
   int act_dtype;  /* gptoss_dtype_t of GEMM-side tensors: F32 = fp32 mode, BF16 = bf16-activation mode */
-  unsigned flags; /* GPTOSS_EXACT / GPTOSS_FMA, passed to every kernel */
+  unsigned flags; /* GPTOSS_EXACT / GPTOSS_FMA / GPTOSS_PDL, passed to every kernel; GPTOSS_CHAIN_* */
 } gptoss_chain_config_t;
 
 /* gpt-oss-20b (24 layers, 32 experts) or gpt-oss-120b (36 layers, 128 experts)
@@ -171,7 +175,9 @@ GPTOSS_API int gptoss_chain_enqueue(gptoss_chain_t *chain, int T, int use_graph)
 
 /* One full engine step as gpu_run_wave does it (gpu_engine.hpp:777-798): copy
  * T tokens and positions from host memory, run the chain, copy the T picked
- * tokens back, synchronise the stream.  Host pointers (pinned for speed). */
+ * tokens back, synchronise the stream.  The copies are nodes of the same CUDA
+ * graph as the kernels (one launch call per step); the caller's arrays, pinned
+ * or not, pass through a pinned staging block owned by the chain. */
 GPTOSS_API int gptoss_chain_step(gptoss_chain_t *chain, int T, const int *tokens_host,
                                  const int *pos_host, int *next_host);
 
@@ -194,8 +200,8 @@ GPTOSS_API int gptoss_chain_run_wave(gptoss_chain_t *chain, const int *prompt_to
                                      int *generated, long long *n_generated, int *steps_run);
 
 typedef enum {
-  GPTOSS_K_EMBED = 0,
-  GPTOSS_K_NORM,     /* RMSNorm alone (layer 0) */
+  GPTOSS_K_EMBED = 0, /* gather fused with layer 0's norm; the gather alone with GPTOSS_CHAIN_SPLIT_EMBED_NORM */
+  GPTOSS_K_NORM,      /* RMSNorm alone (layer 0): launched only with GPTOSS_CHAIN_SPLIT_EMBED_NORM */
   GPTOSS_K_ROPE,     /* qkv bias + RoPE */
   GPTOSS_K_ADD_NORM, /* residual add + RMSNorm */
   GPTOSS_K_ROUTER,

@@ -103,6 +103,19 @@ GPTOSS_API int gptoss_embed(gptoss_stream_t stream, int T, const void *table,
                             gptoss_dtype_t x_dtype, int H, unsigned flags);
 
 /*
+ * The gather and the first layer's norm in one launch:
+ *     x[t,:] = table[ids[t],:] (as fp32);   out[t,:] = weight * x[t,:] / sqrt(mean(x^2) + eps)
+ * Replaces the pair embed_kernel + rmsnorm_bf16_kernel / rmsnorm_exact that opens every step
+ * (gpu_engine.hpp:461-464 with :479 or :491-492; run.cpp:544-545 and :550 for layer 0).  Results
+ * are those of gptoss_embed followed by gptoss_add_rmsnorm(y = NULL) with the same flags, bit for
+ * bit; x is not read back in between.  out must not alias x.
+ */
+GPTOSS_API int gptoss_embed_rmsnorm(gptoss_stream_t stream, int T, const void *table,
+                                    gptoss_dtype_t table_dtype, int V, const int *ids, float *x,
+                                    const float *weight, void *out, gptoss_dtype_t out_dtype, int H,
+                                    unsigned flags);
+
+/*
  * Residual add fused with RMSNorm (eps 1e-5):
  *     if (y) x[t,:] += y[t,:];   out[t,:] = weight * x[t,:] / sqrt(mean(x^2) + eps)
  * With y: replaces add_rmsnorm_bf16 (kernels/fast_misc.hpp:237-267; launch

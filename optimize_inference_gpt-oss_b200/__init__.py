@@ -24,6 +24,7 @@ INCLUDE_DIR = os.path.join(os.path.dirname(_HERE), "include")
 F32, BF16 = 0, 1
 OK, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_CUDA = 0, 1, 2, 3
 EXACT, FMA, PDL = 1, 2, 4
+CHAIN_SPLIT_EMBED_NORM = 0x100  # chain only: gather and first norm as two launches
 MAX_TOPK, MAX_EXPERTS = 8, 256
 
 # gptoss_chain_buffer_t
@@ -62,6 +63,7 @@ PROTOTYPES = {
     "gptoss_status_string": (C.c_char_p, [_i]),
     "gptoss_last_cuda_error": (_i, []),
     "gptoss_embed": (_i, [_p, _i, _p, _i, _i, _p, _p, _i, _i, _u]),
+    "gptoss_embed_rmsnorm": (_i, [_p, _i, _p, _i, _i, _p, _p, _p, _p, _i, _i, _u]),
     "gptoss_add_rmsnorm": (_i, [_p, _i, _p, _p, _i, _p, _p, _i, _i, _u]),
     "gptoss_qkv_bias_rope": (_i, [_p, _i, _p, _i, _l, _p, _p, _i, _p, _p, _i, _i, _i, _i, _p, _i, _l, _u]),
     "gptoss_router_topk": (_i, [_p, _i, _p, _i, _i, _i, _p, _p, _p, _p, _u]),
@@ -238,6 +240,11 @@ def _ptr(x):
 
 def embed(T, table, table_dtype, V, ids, x, x_dtype, H, flags=0, stream=None):
     check(load().gptoss_embed(stream, T, _ptr(table), table_dtype, V, _ptr(ids), _ptr(x), x_dtype, H, flags), "embed")
+
+
+def embed_rmsnorm(T, table, table_dtype, V, ids, x, weight, out, out_dtype, H, flags=0, stream=None):
+    check(load().gptoss_embed_rmsnorm(stream, T, _ptr(table), table_dtype, V, _ptr(ids), _ptr(x), _ptr(weight),
+                                      _ptr(out), out_dtype, H, flags), "embed_rmsnorm")
 
 
 def add_rmsnorm(T, x, y, y_dtype, weight, out, out_dtype, H, flags=0, stream=None):

@@ -38,6 +38,8 @@ struct gptoss_chain {
   void *flush = nullptr;
   size_t flush_bytes = 0;
   std::map<int, cudaGraphExec_t> graphs;                       // whole step, per T
+  std::map<int, cudaGraphExec_t> io_graphs;                    // the step between its host<->device copies, per T
+  int *io_host = nullptr; // pinned staging of gptoss_chain_step: tokens | positions | picked tokens, max_tokens each
   std::map<std::pair<int, int>, cudaGraphExec_t> kind_graphs; // one kernel kind's launches, per (T, kind)
   std::vector<cudaEvent_t> events;
 
@@ -133,10 +135,16 @@ int issue_step(gptoss_chain *c, int T, cudaStream_t s, Hook *hook, int only = -1
   const gptoss_dtype_t a = (gptoss_dtype_t)g.act_dtype;
   const int H = g.hidden, L = g.n_layers, K = g.top_k, QKV = c->qkv_dim();
   gptoss_stream_t gs = s;
-  // step_embed: x = embedding[tokens]
-  STEP(GPTOSS_K_EMBED, gptoss_embed(gs, T, c->embedding, a, g.vocab, c->tokens, c->x, GPTOSS_F32, H, g.flags));
-  // layer 0's attention norm; later layers get theirs from the previous combine
-  STEP(GPTOSS_K_NORM, gptoss_add_rmsnorm(gs, T, c->x, nullptr, a, c->gain_attn, c->normed, a, H, g.flags));
+  if (g.flags & GPTOSS_CHAIN_SPLIT_EMBED_NORM) {
+    // step_embed: x = embedding[tokens]
+    STEP(GPTOSS_K_EMBED, gptoss_embed(gs, T, c->embedding, a, g.vocab, c->tokens, c->x, GPTOSS_F32, H, g.flags));
+    // layer 0's attention norm; later layers get theirs from the previous combine
+    STEP(GPTOSS_K_NORM, gptoss_add_rmsnorm(gs, T, c->x, nullptr, a, c->gain_attn, c->normed, a, H, g.flags));
+  } else {
+    // both in one launch
+    STEP(GPTOSS_K_EMBED, gptoss_embed_rmsnorm(gs, T, c->embedding, a, g.vocab, c->tokens, c->x, c->gain_attn,
+                                              c->normed, a, H, g.flags));
+  }
   for (int l = 0; l < L; l++) {
     // [QKV GEMM of `normed`] -> stand-in qkv; bias + RoPE
     STEP(GPTOSS_K_ROPE,
@@ -277,6 +285,8 @@ int gptoss_chain_create(const gptoss_chain_config_t *cfg, int max_tokens, int n_
   ALLOC(flush, c->flush_bytes);
 #undef ALLOC
   if (st == GPTOSS_OK)
+    st = cuda_status(cudaMallocHost(reinterpret_cast<void **>(&c->io_host), 3 * T * 4));
+  if (st == GPTOSS_OK)
     st = cuda_status(cudaMemsetAsync(c->keys, 0, T * 8, c->stream));
   if (st == GPTOSS_OK) {
     // The engine's grouping step decides where each (token, choice) pair's expert output
@@ -322,6 +332,10 @@ int gptoss_chain_destroy(gptoss_chain_t *c) {
     (void)cudaGraphExecDestroy(kv.second);
   for (auto &kv : c->kind_graphs)
     (void)cudaGraphExecDestroy(kv.second);
+  for (auto &kv : c->io_graphs)
+    (void)cudaGraphExecDestroy(kv.second);
+  if (c->io_host)
+    (void)cudaFreeHost(c->io_host);
   for (cudaEvent_t e : c->events)
     (void)cudaEventDestroy(e);
   for (void *p : c->allocs)
@@ -419,10 +433,14 @@ int gptoss_chain_fill_synthetic(gptoss_chain_t *c, int T, uint64_t seed, int thr
   return st;
 }
 
-// Captures the launches of one step (only < 0) or of one kernel kind into a graph.
-static int capture_step(gptoss_chain *c, int T, int only, cudaGraphExec_t *exec_out) {
+// Captures the launches of one step (only < 0) or of one kernel kind into a graph; with
+// lead_flush an L2 flush goes first (only == GPTOSS_K_COUNT then gives the flush alone).
+static int capture_step(gptoss_chain *c, int T, int only, cudaGraphExec_t *exec_out, bool lead_flush = false,
+                        bool with_io = false) {
   // Warm every kernel once outside capture (occupancy queries, lazy module load).
-  int st = issue_step(c, T, c->stream, nullptr, only);
+  int st = lead_flush ? gptoss_flush_l2(c->flush, c->flush_bytes, c->stream) : GPTOSS_OK;
+  if (st == GPTOSS_OK)
+    st = issue_step(c, T, c->stream, nullptr, only);
   if (st != GPTOSS_OK)
     return st;
   st = cuda_status(cudaStreamSynchronize(c->stream));
@@ -431,7 +449,16 @@ static int capture_step(gptoss_chain *c, int T, int only, cudaGraphExec_t *exec_
   st = cuda_status(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
   if (st != GPTOSS_OK)
     return st;
-  const int issued = issue_step(c, T, c->stream, nullptr, only);
+  int issued = lead_flush ? gptoss_flush_l2(c->flush, c->flush_bytes, c->stream) : GPTOSS_OK;
+  const size_t io_bytes = (size_t)T * 4, io_stride = (size_t)c->max_tokens;
+  if (with_io && issued == GPTOSS_OK)
+    issued = cuda_status(cudaMemcpyAsync(c->tokens, c->io_host, io_bytes, cudaMemcpyHostToDevice, c->stream));
+  if (with_io && issued == GPTOSS_OK)
+    issued = cuda_status(cudaMemcpyAsync(c->pos, c->io_host + io_stride, io_bytes, cudaMemcpyHostToDevice, c->stream));
+  if (issued == GPTOSS_OK)
+    issued = issue_step(c, T, c->stream, nullptr, only);
+  if (with_io && issued == GPTOSS_OK)
+    issued = cuda_status(cudaMemcpyAsync(c->io_host + 2 * io_stride, c->next, io_bytes, cudaMemcpyDeviceToHost, c->stream));
   cudaGraph_t graph = nullptr;
   st = cuda_status(cudaStreamEndCapture(c->stream, &graph));
   if (issued != GPTOSS_OK || st != GPTOSS_OK) {
@@ -468,15 +495,24 @@ int gptoss_chain_step(gptoss_chain_t *c, int T, const int *tokens_host, const in
     return GPTOSS_ERR_BAD_ARG;
   if (T == 0)
     return GPTOSS_OK;
-  int st = cuda_status(cudaMemcpyAsync(c->tokens, tokens_host, (size_t)T * 4, cudaMemcpyHostToDevice, c->stream));
-  if (st == GPTOSS_OK)
-    st = cuda_status(cudaMemcpyAsync(c->pos, pos_host, (size_t)T * 4, cudaMemcpyHostToDevice, c->stream));
-  if (st == GPTOSS_OK)
-    st = gptoss_chain_enqueue(c, T, 1);
-  if (st == GPTOSS_OK)
-    st = cuda_status(cudaMemcpyAsync(next_host, c->next, (size_t)T * 4, cudaMemcpyDeviceToHost, c->stream));
+  // One graph launch per step: the two copies in, every kernel, the copy out.  The caller's
+  // arrays pass through the chain's pinned staging block, whose addresses the graph holds.
+  auto it = c->io_graphs.find(T);
+  if (it == c->io_graphs.end()) {
+    cudaGraphExec_t exec = nullptr;
+    const int st = capture_step(c, T, -1, &exec, false, true);
+    if (st != GPTOSS_OK)
+      return st;
+    it = c->io_graphs.emplace(T, exec).first;
+  }
+  const size_t stride = (size_t)c->max_tokens;
+  memcpy(c->io_host, tokens_host, (size_t)T * 4);
+  memcpy(c->io_host + stride, pos_host, (size_t)T * 4);
+  int st = cuda_status(cudaGraphLaunch(it->second, c->stream));
   if (st == GPTOSS_OK)
     st = cuda_status(cudaStreamSynchronize(c->stream));
+  if (st == GPTOSS_OK)
+    memcpy(next_host, c->io_host + 2 * stride, (size_t)T * 4);
   return st;
 }
 
@@ -573,7 +609,12 @@ int gptoss_chain_profile(gptoss_chain_t *c, int T, int steps, int mode, double *
     // One event pair around all of a kind's launches of a step, replayed from a graph
     // captured for that kind alone: launches sit as close together as they do in the
     // whole-step graph, and the cost of the two event records is spread over the batch.
-    const int per_step[GPTOSS_K_COUNT] = {1, 1, c->cfg.n_layers, c->cfg.n_layers, c->cfg.n_layers,
+    // A kind with a single launch per step has no batch to spread it over (the pair costs
+    // about 4 us): it is timed behind an L2 flush in the same graph -- cold, as it is in the
+    // chain, where the argmax before it has swept the cache -- and the time of the flush
+    // alone, taken between the same kind of event pair in the same pass, is subtracted.
+    const bool split = (c->cfg.flags & GPTOSS_CHAIN_SPLIT_EMBED_NORM) != 0;
+    const int per_step[GPTOSS_K_COUNT] = {1, split ? 1 : 0, c->cfg.n_layers, c->cfg.n_layers, c->cfg.n_layers,
                                           c->cfg.n_layers, c->cfg.n_layers, 1};
     while (c->events.size() < 2) {
       cudaEvent_t e = nullptr;
@@ -582,16 +623,19 @@ int gptoss_chain_profile(gptoss_chain_t *c, int T, int steps, int mode, double *
         return st;
       c->events.push_back(e);
     }
-    for (int kind = 0; kind < GPTOSS_K_COUNT; kind++)
+    for (int kind = 0; kind <= GPTOSS_K_COUNT; kind++) // GPTOSS_K_COUNT: the flush alone
       if (!c->kind_graphs.count({T, kind})) {
         cudaGraphExec_t exec = nullptr;
-        const int st = capture_step(c, T, kind, &exec);
+        const int st = capture_step(c, T, kind, &exec, kind == GPTOSS_K_COUNT || per_step[kind] == 1);
         if (st != GPTOSS_OK)
           return st;
         c->kind_graphs[{T, kind}] = exec;
       }
-    for (int s = 0; s < steps; s++)
-      for (int kind = 0; kind < GPTOSS_K_COUNT; kind++) {
+    for (int s = 0; s < steps; s++) {
+      double flush_ms = 0.0;
+      for (int kind = GPTOSS_K_COUNT; kind >= 0; kind--) { // the flush alone first
+        if (kind < GPTOSS_K_COUNT && per_step[kind] == 0)
+          continue;
         int st = cuda_status(cudaEventRecord(c->events[0], c->stream));
         if (st == GPTOSS_OK)
           st = cuda_status(cudaGraphLaunch(c->kind_graphs[{T, kind}], c->stream));
@@ -604,9 +648,14 @@ int gptoss_chain_profile(gptoss_chain_t *c, int T, int steps, int mode, double *
           st = cuda_status(cudaEventElapsedTime(&ms, c->events[0], c->events[1]));
         if (st != GPTOSS_OK)
           return st;
-        ms_per_kind[kind] += ms;
+        if (kind == GPTOSS_K_COUNT) {
+          flush_ms = ms;
+          continue;
+        }
+        ms_per_kind[kind] += per_step[kind] == 1 ? (ms > flush_ms ? ms - flush_ms : 0.0) : ms;
         launches_per_kind[kind] += per_step[kind];
       }
+    }
     return GPTOSS_OK;
   }
   for (int s = 0; s < steps; s++) {
@@ -636,10 +685,11 @@ size_t gptoss_chain_kernel_bytes(const gptoss_chain_t *c, gptoss_chain_kernel_t 
   const size_t t = (size_t)T, H = (size_t)g.hidden, a = c->act(), K = (size_t)g.top_k;
   const size_t QKV = (size_t)c->qkv_dim();
   switch (kind) {
-  case GPTOSS_K_EMBED: // id + table row in + fp32 row out
-    return t * (4 + H * a + H * 4);
+  case GPTOSS_K_EMBED: // id + table row in + fp32 row out (+ normed out, gain once, when fused)
+    return (g.flags & GPTOSS_CHAIN_SPLIT_EMBED_NORM) ? t * (4 + H * a + H * 4)
+                                                     : t * (4 + H * a + H * 4 + H * a) + H * 4;
   case GPTOSS_K_NORM: // x in, normed out, gain once
-    return t * (H * 4 + H * a) + H * 4;
+    return (g.flags & GPTOSS_CHAIN_SPLIT_EMBED_NORM) ? t * (H * 4 + H * a) + H * 4 : 0;
   case GPTOSS_K_ROPE: // qkv in and out, position; bias once; cos/sin rows stay in cache
     return t * (2 * QKV * a + 4) + QKV * 4;
   case GPTOSS_K_ADD_NORM: // x in/out, delta in, normed out, gain once
@@ -660,9 +710,11 @@ size_t gptoss_chain_kernel_bytes(const gptoss_chain_t *c, gptoss_chain_kernel_t 
 int gptoss_chain_launches_per_step(const gptoss_chain_t *c, int T) {
   if (!c || T <= 0)
     return 0;
-  // embed, first norm, 5 per layer, argmax scan (+ its key decode when rows are split)
+  // embed with the first norm (one launch, or two), 5 per layer, argmax scan (+ its key
+  // decode when rows are split)
   const int slices = gptoss_argmax_slices(T, c->cfg.vocab, (gptoss_dtype_t)c->cfg.act_dtype, 1);
-  return 2 + 5 * c->cfg.n_layers + (slices > 1 ? 2 : 1);
+  const int opening = (c->cfg.flags & GPTOSS_CHAIN_SPLIT_EMBED_NORM) ? 2 : 1;
+  return opening + 5 * c->cfg.n_layers + (slices > 1 ? 2 : 1);
 }
 
 } // extern "C"

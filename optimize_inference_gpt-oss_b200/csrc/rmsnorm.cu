@@ -161,6 +161,137 @@ __global__ void add_rmsnorm_rows(float *x, const YT *__restrict__ y, const float
   cp_async_wait<0>();
 }
 
+// Embedding gather fused with the norm that follows it (gptoss_embed_rmsnorm): the same
+// ring, but a stage is filled from table row ids[row] (bf16 or fp32) instead of from x,
+// and the widened row is stored to x as well as normalised.  Against the two separate
+// launches this leaves out one read of x (4H bytes per row) and one launch.  The ids a
+// block needs are fetched one iteration before their use; an id outside [0, V) stands
+// for a row of zeros, as in the plain gather.
+template <typename TT, typename OT, bool EXACT, int NC, int STAGES>
+__global__ void embed_rmsnorm_rows(const TT *__restrict__ table, const int *__restrict__ ids, int V,
+                                   float *__restrict__ x, const float *__restrict__ w,
+                                   OT *__restrict__ out, int T, int H) {
+  pdl_prologue();
+  constexpr int ST = sizeof(TT);
+  using Acc = typename std::conditional<EXACT, double, float>::type;
+  extern __shared__ __align__(16) unsigned char ring[];
+  __shared__ Acc scratch[2][32];
+  const size_t stage_bytes = (size_t)H * ST;
+  const int n_chunks = H >> 3;
+
+  bool has[NC];
+  Vec8 ws[NC];
+#pragma unroll
+  for (int c = 0; c < NC; c++) {
+    const int chunk = threadIdx.x + c * blockDim.x;
+    has[c] = chunk < n_chunks;
+    if (has[c])
+      ws[c] = load8<kTable>(w, (size_t)chunk * 8);
+  }
+
+  auto row_id = [&](long row) -> int {
+    if (row >= T)
+      return -1;
+    const int id = __ldg(ids + row);
+    return id >= 0 && id < V ? id : -1;
+  };
+  auto issue = [&](int id, int stage) {
+    if (id < 0)
+      return;
+    unsigned char *sx = ring + (size_t)stage * stage_bytes;
+    const TT *tr = table + (size_t)id * H;
+#pragma unroll
+    for (int c = 0; c < NC; c++)
+      if (has[c]) {
+        const int chunk = threadIdx.x + c * blockDim.x;
+        cp_async16(sx + (size_t)chunk * 8 * ST, tr + (size_t)chunk * 8);
+        if constexpr (ST == 4)
+          cp_async16(sx + (size_t)chunk * 32 + 16, tr + (size_t)chunk * 8 + 4);
+      }
+  };
+
+  const long step = gridDim.x;
+  long row = blockIdx.x;
+  {
+    int first[STAGES - 1];
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; s++)
+      first[s] = row_id(row + s * step);
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; s++) {
+      issue(first[s], s);
+      cp_async_commit();
+    }
+  }
+  int id_here = row_id(row);                         // of the row being normalised
+  int id_ahead = row_id(row + (STAGES - 1) * step);  // of the row whose copy is issued next
+  int stage = 0, flip = 0;
+  for (; row < T; row += step, flip ^= 1) {
+    issue(id_ahead, stage == 0 ? STAGES - 1 : stage - 1);
+    cp_async_commit();
+    const bool live = id_here >= 0;
+    id_here = row_id(row + step);
+    id_ahead = row_id(row + STAGES * step);
+    cp_async_wait<STAGES - 1>();
+
+    const unsigned char *sx = ring + (size_t)stage * stage_bytes;
+    Vec8 xs[NC];
+    Acc ss = 0;
+#pragma unroll
+    for (int c = 0; c < NC; c++)
+      if (has[c]) {
+        const int chunk = threadIdx.x + c * blockDim.x;
+        if (!live) {
+#pragma unroll
+          for (int i = 0; i < 8; i++)
+            xs[c].v[i] = 0.0f;
+        } else if constexpr (ST == 2) {
+          xs[c] = widen8(*reinterpret_cast<const uint4 *>(sx + (size_t)chunk * 16));
+        } else {
+          const uint4 a = *reinterpret_cast<const uint4 *>(sx + (size_t)chunk * 32);
+          const uint4 b = *reinterpret_cast<const uint4 *>(sx + (size_t)chunk * 32 + 16);
+          xs[c].v[0] = __uint_as_float(a.x), xs[c].v[1] = __uint_as_float(a.y),
+          xs[c].v[2] = __uint_as_float(a.z), xs[c].v[3] = __uint_as_float(a.w),
+          xs[c].v[4] = __uint_as_float(b.x), xs[c].v[5] = __uint_as_float(b.y),
+          xs[c].v[6] = __uint_as_float(b.z), xs[c].v[7] = __uint_as_float(b.w);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          if constexpr (EXACT)
+            ss = __dadd_rn(ss, (double)__fmul_rn(xs[c].v[i], xs[c].v[i]));
+          else
+            ss = fmaf(xs[c].v[i], xs[c].v[i], ss);
+        }
+      }
+    ss = block_sum<Acc>(ss, scratch[flip]);
+    float *xr = x + (size_t)row * H;
+    OT *orow = out + (size_t)row * H;
+    [[maybe_unused]] double inv_d = 0.0;
+    [[maybe_unused]] float inv_f = 0.0f;
+    if constexpr (EXACT)
+      inv_d = exact_inv_rms(ss, H);
+    else
+      inv_f = fast_inv_rms(ss, H);
+#pragma unroll
+    for (int c = 0; c < NC; c++)
+      if (has[c]) {
+        const size_t e = (size_t)(threadIdx.x + c * blockDim.x) * 8;
+        store8(xr, e, xs[c], false);
+        Vec8 o;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          if constexpr (EXACT)
+            o.v[i] = (float)__dmul_rn((double)ws[c].v[i], __dmul_rn(inv_d, (double)xs[c].v[i]));
+          else
+            o.v[i] = __fmul_rn(ws[c].v[i], __fmul_rn(inv_f, xs[c].v[i]));
+        }
+        store8(orow, e, o);
+      }
+    stage = stage + 1 == STAGES ? 0 : stage + 1;
+  }
+  cp_async_wait<0>();
+}
+
 // Any H, any alignment: scalar accesses, the row is read twice (the second
 // time from cache).  256 threads per row.
 template <typename YT, typename OT, bool EXACT>
@@ -258,6 +389,47 @@ int launch_y(cudaStream_t s, int T, float *x, const void *y, gptoss_dtype_t y_dt
                                : launch_out<uint16_t, EXACT>(s, T, x, y, w, out, out_dtype, H);
 }
 
+template <typename TT, typename OT, bool EXACT, int NC>
+int launch_embed_pipe(cudaStream_t s, int T, const TT *table, const int *ids, int V, float *x, const float *w,
+                      OT *out, int H, int threads, size_t smem) {
+  auto k = embed_rmsnorm_rows<TT, OT, EXACT, NC, 4>;
+  const int per_sm = blocks_per_sm_smem(k, threads, smem);
+  if (per_sm < 1)
+    return GPTOSS_ERR_UNSUPPORTED;
+  launch_kernel(k, dim3(row_grid(T, per_sm)), dim3(threads), smem, s, table, ids, V, x, w, out, T, H);
+  return launch_status();
+}
+
+// GPTOSS_ERR_UNSUPPORTED: the shape or alignment is not one the fused kernel takes.
+template <typename TT, typename OT, bool EXACT>
+int launch_embed(cudaStream_t s, int T, const void *table, const int *ids, int V, float *x, const float *w,
+                 void *out, int H) {
+  const size_t stage_bytes = (size_t)H * sizeof(TT);
+  if (H % 8 != 0 || H > 8 * 512 * 4 || stage_bytes * 4 > 200 * 1024 || !aligned16(table) || !aligned16(x) ||
+      !aligned16(w) || !aligned16(out))
+    return GPTOSS_ERR_UNSUPPORTED;
+  const int n_chunks = H / 8;
+  const int nc = n_chunks <= 512 ? 1 : (n_chunks <= 1024 ? 2 : 4);
+  const int threads = ((n_chunks + nc - 1) / nc + 31) / 32 * 32;
+  const TT *tp = static_cast<const TT *>(table);
+  OT *op = static_cast<OT *>(out);
+  if (nc == 1)
+    return launch_embed_pipe<TT, OT, EXACT, 1>(s, T, tp, ids, V, x, w, op, H, threads, stage_bytes * 4);
+  if (nc == 2)
+    return launch_embed_pipe<TT, OT, EXACT, 2>(s, T, tp, ids, V, x, w, op, H, threads, stage_bytes * 4);
+  return launch_embed_pipe<TT, OT, EXACT, 4>(s, T, tp, ids, V, x, w, op, H, threads, stage_bytes * 4);
+}
+
+template <bool EXACT>
+int launch_embed_types(cudaStream_t s, int T, const void *table, gptoss_dtype_t table_dtype, const int *ids, int V,
+                       float *x, const float *w, void *out, gptoss_dtype_t out_dtype, int H) {
+  if (table_dtype == GPTOSS_BF16)
+    return out_dtype == GPTOSS_BF16 ? launch_embed<uint16_t, uint16_t, EXACT>(s, T, table, ids, V, x, w, out, H)
+                                    : launch_embed<uint16_t, float, EXACT>(s, T, table, ids, V, x, w, out, H);
+  return out_dtype == GPTOSS_BF16 ? launch_embed<float, uint16_t, EXACT>(s, T, table, ids, V, x, w, out, H)
+                                  : launch_embed<float, float, EXACT>(s, T, table, ids, V, x, w, out, H);
+}
+
 } // namespace
 } // namespace gptoss
 
@@ -278,4 +450,29 @@ extern "C" int gptoss_add_rmsnorm(gptoss_stream_t stream, int T, float *x, const
   cudaStream_t s = as_stream(stream);
   return (flags & GPTOSS_EXACT) ? launch_y<true>(s, T, x, y, y_dtype, weight, out, out_dtype, H)
                                 : launch_y<false>(s, T, x, y, y_dtype, weight, out, out_dtype, H);
+}
+
+extern "C" int gptoss_embed_rmsnorm(gptoss_stream_t stream, int T, const void *table, gptoss_dtype_t table_dtype,
+                                    int V, const int *ids, float *x, const float *weight, void *out,
+                                    gptoss_dtype_t out_dtype, int H, unsigned flags) {
+  using namespace gptoss;
+  if (T < 0 || H <= 0 || V <= 0 || !valid_dtype(table_dtype) || !valid_dtype(out_dtype))
+    return GPTOSS_ERR_BAD_ARG;
+  if (T == 0)
+    return GPTOSS_OK;
+  if (!table || !ids || !x || !weight || !out || out == (void *)x)
+    return GPTOSS_ERR_BAD_ARG;
+  int st;
+  {
+    const PdlScope pdl(flags);
+    cudaStream_t s = as_stream(stream);
+    st = (flags & GPTOSS_EXACT)
+             ? launch_embed_types<true>(s, T, table, table_dtype, ids, V, x, weight, out, out_dtype, H)
+             : launch_embed_types<false>(s, T, table, table_dtype, ids, V, x, weight, out, out_dtype, H);
+  }
+  if (st != GPTOSS_ERR_UNSUPPORTED)
+    return st;
+  // odd H or alignment: the two separate kernels, which take anything
+  st = gptoss_embed(stream, T, table, table_dtype, V, ids, x, GPTOSS_F32, H, flags);
+  return st != GPTOSS_OK ? st : gptoss_add_rmsnorm(stream, T, x, nullptr, GPTOSS_F32, weight, out, out_dtype, H, flags);
 }

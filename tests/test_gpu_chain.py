@@ -94,9 +94,13 @@ def _run_and_compare(pkg, orc, c, T, n_sets, tol, seed):
         assert n_bit_diff(ch.download(pkg.BUF_X, 0, np.float32, (T, H)), got_x) == 0
         ch.enqueue(T, use_graph=False)
         assert n_bit_diff(ch.download(pkg.BUF_X, 0, np.float32, (T, H)), got_x) == 0
-        assert ch.launches_per_step(T) in (2 + 5 * c.n_layers + 1, 2 + 5 * c.n_layers + 2)
+        opening = 2 if c.flags & pkg.CHAIN_SPLIT_EMBED_NORM else 1
+        assert ch.launches_per_step(T) in (opening + 5 * c.n_layers + 1, opening + 5 * c.n_layers + 2)
         prof = ch.profile(T, 1)
         assert prof["swiglu"][1] == c.n_layers and prof["embed"][1] == 1 and prof["argmax"][0] > 0
+        assert prof["norm"][1] == opening - 1
+        batched = ch.profile(T, 2, mode=2)  # per kind, its launches of a step between one event pair
+        assert batched["combine"][1] == 2 * c.n_layers and batched["embed"][1] == 2 and batched["rope"][0] > 0
         return got_x, want
     finally:
         ch.close()
@@ -138,6 +142,28 @@ def test_chain_with_programmatic_dependent_launch(gpu, orc):
     c = _small_config(pkg, pkg.F32)
     c.flags |= pkg.PDL
     _run_and_compare(pkg, orc, c, 64, 3, TOL_F32, seed=11)
+
+
+def test_chain_with_the_opening_as_two_launches(gpu, orc):
+    """The step opens with the gather and layer 0's norm in one launch; with
+    CHAIN_SPLIT_EMBED_NORM it opens with the reference's two.  Same bits either way."""
+    pkg = gpu
+    for dt, tol in ((pkg.BF16, TOL_BF16), (pkg.F32, TOL_F32)):
+        outs = []
+        for flags in (0, pkg.CHAIN_SPLIT_EMBED_NORM):
+            c = _small_config(pkg, dt)
+            c.flags |= flags
+            got_x, _ = _run_and_compare(pkg, orc, c, 130, 3, tol, seed=16)
+            outs.append(got_x)
+        assert n_bit_diff(outs[0], outs[1]) == 0
+    c = _small_config(pkg, pkg.BF16)
+    ch = pkg.Chain(c, 64, 1)
+    fused = ch.launches_per_step(64)
+    ch.close()
+    c.flags |= pkg.CHAIN_SPLIT_EMBED_NORM
+    ch = pkg.Chain(c, 64, 1)
+    assert ch.launches_per_step(64) == fused + 1
+    ch.close()
 
 
 def test_chain_120b_router_width(gpu, orc):

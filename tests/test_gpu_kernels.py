@@ -69,6 +69,53 @@ def test_embed_fp32_table_and_bad_ids(gpu, orc):
     assert n_bit_diff(got[ok], table[bad[ok]]) == 0
 
 
+@pytest.mark.parametrize("T", [1, 7, 600, 4096])
+@pytest.mark.parametrize("Hd", [2880, 64, 1000, 4096, 8200, 77])
+@pytest.mark.parametrize("tdt,odt,exact", [("bf16", "bf16", False), ("bf16", "f32", True), ("f32", "f32", True),
+                                             ("f32", "bf16", False), ("bf16", "bf16", True)])
+def test_embed_rmsnorm_equals_the_two_launches(gpu, orc, T, Hd, tdt, odt, exact):
+    """Gather + first norm in one launch: x and the normalised rows bit for bit those of
+    gptoss_embed followed by gptoss_add_rmsnorm, and within tolerance of the CPU functions;
+    ids outside the table give rows of zeros."""
+    pkg, d = gpu, Dev(gpu)
+    if T == 4096 and Hd not in (2880, 77):
+        pytest.skip("large row counts only for the model's width and the scalar path")
+    tdt, odt = (pkg.BF16 if t == "bf16" else pkg.F32 for t in (tdt, odt))
+    flags = pkg.EXACT if exact else 0
+    Vs = 3001
+    r = rng_of("embednorm", T, Hd)
+    table = widen(pkg, 0.02 * r.standard_normal((Vs, Hd)), tdt)
+    w = (1 + 0.1 * r.standard_normal(Hd)).astype(np.float32)
+    ids = r.integers(0, Vs, T).astype(np.int32)
+    if T >= 7:
+        ids[2], ids[5] = -3, Vs  # no such rows
+    tb, ib, wb = d.put(table, tdt), d.put(ids), d.put(w)
+    x1, o1 = d.out((T, Hd), pkg.F32), d.out((T, Hd), odt)
+    pkg.embed_rmsnorm(T, tb, tdt, Vs, ib, x1, wb, o1, odt, Hd, flags=flags)
+    x2, o2 = d.out((T, Hd), pkg.F32), d.out((T, Hd), odt)
+    pkg.embed(T, tb, tdt, Vs, ib, x2, pkg.F32, Hd, flags=flags)
+    pkg.add_rmsnorm(T, x2, None, pkg.F32, wb, o2, odt, Hd, flags=flags)
+    gx, go = x1.get(), o1.get(as_f32=False)
+    assert n_bit_diff(gx, x2.get()) == 0
+    assert np.array_equal(go, o2.get(as_f32=False))
+    ok = (ids >= 0) & (ids < Vs)
+    want_x = np.zeros((T, Hd), np.float32)
+    want_x[ok] = table[ids[ok]]
+    assert n_bit_diff(gx, want_x) == 0
+    want_o = orc.add_rmsnorm_rows(want_x, None, w)[1]
+    assert rel_err(o1.get(), want_o) <= (TOL_F32 if exact and odt == pkg.F32 else TOL_BF16)
+    assert not o1.get()[~ok].any()
+
+
+def test_embed_rmsnorm_rejects_aliased_output(gpu):
+    pkg, d = gpu, Dev(gpu)
+    x = d.out((4, 64), pkg.F32)
+    t, i, w = d.put(np.zeros((8, 64), np.float32)), d.put(np.zeros(4, np.int32)), d.put(np.ones(64, np.float32))
+    assert pkg.load().gptoss_embed_rmsnorm(None, 4, t.ptr, pkg.F32, 8, i.ptr, x.ptr, w.ptr, x.ptr, pkg.F32, 64, 0) \
+        == pkg.ERR_BAD_ARG
+    assert pkg.load().gptoss_embed_rmsnorm(None, 0, None, pkg.F32, 8, None, None, None, None, pkg.F32, 64, 0) == pkg.OK
+
+
 # ---- a2: residual add + RMSNorm -----------------------------------------------------
 
 @pytest.mark.parametrize("T", [1, 7, 512])
