@@ -292,6 +292,113 @@ __global__ void embed_rmsnorm_rows(const TT *__restrict__ table, const int *__re
   cp_async_wait<0>();
 }
 
+// The same operation without the loop, the form used whenever H <= 4096.  A block owns R
+// consecutive rows and a thread one 8-element chunk of each; the block asks for all R table
+// rows at once (cp.async into shared memory, so the data in flight costs no registers) and
+// with R = 8 a 4096-row launch is a single wave of blocks with every read of the launch in
+// flight together.  The R sums of squares share one barrier.  Chunk-to-thread mapping and
+// summation order are those of add_rmsnorm_rows with one chunk per thread, which makes the
+// result the same bits as the two separate launches.
+template <typename TT, typename OT, bool EXACT, int R>
+__global__ void embed_rmsnorm_tile(const TT *__restrict__ table, const int *__restrict__ ids, int V,
+                                   float *__restrict__ x, const float *__restrict__ w,
+                                   OT *__restrict__ out, int T, int H) {
+  pdl_prologue();
+  constexpr int ST = sizeof(TT);
+  using Acc = typename std::conditional<EXACT, double, float>::type;
+  extern __shared__ __align__(16) unsigned char rows[]; // R rows of H table elements
+  __shared__ Acc scratch[R][32];
+  const int chunk = threadIdx.x;
+  const bool has = chunk < (H >> 3);
+  const long row0 = (long)blockIdx.x * R;
+  const size_t row_bytes = (size_t)H * ST;
+
+  int id[R];
+#pragma unroll
+  for (int r = 0; r < R; r++) {
+    id[r] = -1;
+    if (row0 + r < T) {
+      const int v = __ldg(ids + row0 + r);
+      if (v >= 0 && v < V)
+        id[r] = v;
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < R; r++)
+    if (has && id[r] >= 0) {
+      unsigned char *dst = rows + r * row_bytes + (size_t)chunk * 8 * ST;
+      const TT *src = table + (size_t)id[r] * H + (size_t)chunk * 8;
+      cp_async16(dst, src);
+      if constexpr (ST == 4)
+        cp_async16(dst + 16, src + 4);
+    }
+  cp_async_commit();
+  cp_async_wait<0>(); // a thread reads back only what it copied itself: no barrier needed
+  auto values = [&](int r) {
+    Vec8 v;
+    const unsigned char *p = rows + r * row_bytes + (size_t)chunk * 8 * ST;
+    if (id[r] < 0) {
+#pragma unroll
+      for (int i = 0; i < 8; i++)
+        v.v[i] = 0.0f;
+    } else if constexpr (ST == 2) {
+      v = widen8(*reinterpret_cast<const uint4 *>(p));
+    } else {
+      const uint4 a = *reinterpret_cast<const uint4 *>(p), b = *reinterpret_cast<const uint4 *>(p + 16);
+      v.v[0] = __uint_as_float(a.x), v.v[1] = __uint_as_float(a.y), v.v[2] = __uint_as_float(a.z),
+      v.v[3] = __uint_as_float(a.w), v.v[4] = __uint_as_float(b.x), v.v[5] = __uint_as_float(b.y),
+      v.v[6] = __uint_as_float(b.z), v.v[7] = __uint_as_float(b.w);
+    }
+    return v;
+  };
+
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = (blockDim.x + 31) >> 5;
+#pragma unroll
+  for (int r = 0; r < R; r++) {
+    Acc ss = 0;
+    if (has) {
+      const Vec8 v = values(r);
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        if constexpr (EXACT)
+          ss = __dadd_rn(ss, (double)__fmul_rn(v.v[i], v.v[i]));
+        else
+          ss = fmaf(v.v[i], v.v[i], ss);
+      }
+    }
+    ss = warp_sum(ss);
+    if (lane == 0)
+      scratch[r][warp] = ss;
+  }
+  __syncthreads();
+  Vec8 ws;
+  if (has)
+    ws = load8<kTable>(w, (size_t)chunk * 8);
+#pragma unroll
+  for (int r = 0; r < R; r++) {
+    Acc t = lane < n_warps ? scratch[r][lane] : Acc(0);
+    t = warp_sum(t); // every lane takes part, also those without a chunk
+    if (!has || row0 + r >= T)
+      continue;
+    const Vec8 v = values(r);
+    const size_t e = (size_t)chunk * 8;
+    store8(x + (size_t)(row0 + r) * H, e, v, false);
+    Vec8 o;
+    if constexpr (EXACT) {
+      const double inv = exact_inv_rms(t, H);
+#pragma unroll
+      for (int i = 0; i < 8; i++)
+        o.v[i] = (float)__dmul_rn((double)ws.v[i], __dmul_rn(inv, (double)v.v[i]));
+    } else {
+      const float inv = fast_inv_rms(t, H);
+#pragma unroll
+      for (int i = 0; i < 8; i++)
+        o.v[i] = __fmul_rn(ws.v[i], __fmul_rn(inv, v.v[i]));
+    }
+    store8(out + (size_t)(row0 + r) * H, e, o);
+  }
+}
+
 // Any H, any alignment: scalar accesses, the row is read twice (the second
 // time from cache).  256 threads per row.
 template <typename YT, typename OT, bool EXACT>
@@ -413,8 +520,35 @@ int launch_embed(cudaStream_t s, int T, const void *table, const int *ids, int V
   const int threads = ((n_chunks + nc - 1) / nc + 31) / 32 * 32;
   const TT *tp = static_cast<const TT *>(table);
   OT *op = static_cast<OT *>(out);
-  if (nc == 1)
-    return launch_embed_pipe<TT, OT, EXACT, 1>(s, T, tp, ids, V, x, w, op, H, threads, stage_bytes * 4);
+  if (nc == 1) {
+    // rows per block: as few as still let every block be resident at once, at most 8
+    // (and no more than fit in shared memory beside a second block)
+    const int r_fit = stage_bytes * 8 <= 100 * 1024 ? 8 : (stage_bytes * 4 <= 100 * 1024 ? 4 : (stage_bytes * 2 <= 100 * 1024 ? 2 : 1));
+    int r = 1;
+    while (r < r_fit) {
+      const long slots = r == 1   ? (long)sm_count() * blocks_per_sm_smem(embed_rmsnorm_tile<TT, OT, EXACT, 1>, threads, stage_bytes)
+                         : r == 2 ? (long)sm_count() * blocks_per_sm_smem(embed_rmsnorm_tile<TT, OT, EXACT, 2>, threads, stage_bytes * 2)
+                                  : (long)sm_count() * blocks_per_sm_smem(embed_rmsnorm_tile<TT, OT, EXACT, 4>, threads, stage_bytes * 4);
+      if ((T + r - 1) / r <= slots)
+        break;
+      r *= 2;
+    }
+    const unsigned blocks = (unsigned)((T + r - 1) / r);
+    const size_t smem = stage_bytes * r;
+#define GPTOSS_TILE_CASE(R_)                                                                              \
+  if (r == R_) {                                                                                          \
+    if (blocks_per_sm_smem(embed_rmsnorm_tile<TT, OT, EXACT, R_>, threads, smem) < 1)                     \
+      return GPTOSS_ERR_UNSUPPORTED;                                                                      \
+    launch_kernel(embed_rmsnorm_tile<TT, OT, EXACT, R_>, dim3(blocks), dim3(threads), smem, s, tp, ids, V, x, w, op, \
+                  T, H);                                                                                  \
+  }
+    GPTOSS_TILE_CASE(1);
+    GPTOSS_TILE_CASE(2);
+    GPTOSS_TILE_CASE(4);
+    GPTOSS_TILE_CASE(8);
+#undef GPTOSS_TILE_CASE
+    return launch_status();
+  }
   if (nc == 2)
     return launch_embed_pipe<TT, OT, EXACT, 2>(s, T, tp, ids, V, x, w, op, H, threads, stage_bytes * 4);
   return launch_embed_pipe<TT, OT, EXACT, 4>(s, T, tp, ids, V, x, w, op, H, threads, stage_bytes * 4);
