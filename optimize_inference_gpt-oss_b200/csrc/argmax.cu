@@ -170,12 +170,18 @@ __global__ void argmax_keys_decode(unsigned long long *keys, int T, int *__restr
   keys[row] = 0ull;
 }
 
-// Slices per row: enough blocks to fill the machine several times over, each
-// slice at least 2048 pieces (32 KB), at most 64 slices.
+// Slices per row.  With at least two waves of one-block rows the tail is small and a
+// row stays whole (no merge, no second launch).  Below that, rows are cut so that the
+// launch has about four waves of blocks -- measured 9 % faster at 1024 rows than one
+// wave, the same at 128 and 512 -- each slice at least 2048 pieces (32 KB), at most 64
+// slices.
 int plan_slices(int T, long pieces, bool has_keys) {
   if (!has_keys || T <= 0)
     return 1;
-  long want = ((long)sm_count() * 8 + T - 1) / T;
+  const long slots = (long)sm_count() * 8;
+  if (T >= 2 * slots)
+    return 1;
+  long want = (4 * slots + T - 1) / T;
   const long by_size = pieces / 2048 > 0 ? pieces / 2048 : 1;
   if (want > by_size)
     want = by_size;
