@@ -417,6 +417,30 @@ def main():
     barrier()
     e2e_s = sharding.max_over_ranks(e2e_s, dist)
     e2e_value = world * T * args.steps / e2e_s
+    # ---- the same steps as one wave with the bookkeeping on the GPU: prompts in before, output rows
+    # back after, no per-step round trip (one-token prompts, so every step feeds the picked token back)
+    wave_steps = min(args.steps, 4096)
+    w_tok = np.ascontiguousarray(tok.array, np.int32)
+    w_off = np.arange(T + 1, dtype=np.int32)
+    w_out = np.empty((T, wave_steps + 2), np.int32)
+    w_total, w_ran = C.c_longlong(0), C.c_int(0)
+
+    def wave(steps):
+        pkg.check(lib.gptoss_chain_run_wave_on_device(chain.h, w_tok.ctypes.data, w_off.ctypes.data, T, steps,
+                                                      w_out.ctypes.data, C.byref(w_total), C.byref(w_ran)))
+        return int(w_ran.value)
+
+    wave(min(3, wave_steps))
+    barrier()
+    t0 = time.perf_counter()
+    wave_ran = wave(wave_steps)
+    wave_s = sharding.max_over_ranks(time.perf_counter() - t0, dist)
+    barrier()
+    device_loop = {"value": world * T * wave_ran / wave_s, "unit": "tokens/s", "steps": wave_ran,
+                   "ms_per_step": 1e3 * wave_s / max(1, wave_ran), "h2d_bytes": 8 * T + 4,
+                   "d2h_bytes": 4 * T * (wave_steps + 2) + 4 * T,
+                   "what": "gptoss_chain_run_wave_on_device: one wave of `steps` positions, token feedback and "
+                           "finished-row handling by a kernel behind each step, host queues 16 steps at a time"}
     clocks = sampler.stop() if sampler else None
 
     # ---- per-kernel device times: per kind, an event pair around its launches of a step
@@ -460,7 +484,7 @@ def main():
                 "ms_per_step": 1e3 * e2e_s / args.steps,
                 "what": "gptoss_chain_step: token ids + positions from pinned host memory in, picked tokens out, "
                         "stream synchronised every step; activations standing in for GEMM outputs stay on the device",
-                "all_operands_from_host": host_operands},
+                "device_loop": device_loop, "all_operands_from_host": host_operands},
         "gpu_launches": chain.launches_per_step(T) * args.steps,
         "launches_per_step": chain.launches_per_step(T),
         "roofline": roofline, "kernels": kernels, "clocks": clocks,

@@ -199,6 +199,17 @@ GPTOSS_API int gptoss_chain_run_wave(gptoss_chain_t *chain, const int *prompt_to
                                      const int *prompt_offsets, int n_requests, int steps,
                                      int *generated, long long *n_generated, int *steps_run);
 
+/* The same wave with the bookkeeping on the GPU: prompts, the finished-row mask, the
+ * output rows and the counters stay in device memory, a one-block kernel behind each
+ * step's argmax does what the reference's host loop does between steps
+ * (gpu_engine.hpp:800-826), and the host only queues steps, sixteen at a time, looking at
+ * the counters in between to stop once every row is done.  No token crosses the bus
+ * during the wave: prompts go in before it, output rows come back after it.  Same
+ * arguments and, bit for bit, the same outputs as gptoss_chain_run_wave. */
+GPTOSS_API int gptoss_chain_run_wave_on_device(gptoss_chain_t *chain, const int *prompt_tokens,
+                                               const int *prompt_offsets, int n_requests, int steps,
+                                               int *generated, long long *n_generated, int *steps_run);
+
 typedef enum {
   GPTOSS_K_EMBED = 0, /* gather fused with layer 0's norm; the gather alone with GPTOSS_CHAIN_SPLIT_EMBED_NORM */
   GPTOSS_K_NORM,      /* RMSNorm alone (layer 0): launched only with GPTOSS_CHAIN_SPLIT_EMBED_NORM */

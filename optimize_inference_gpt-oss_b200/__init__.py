@@ -109,6 +109,7 @@ PROTOTYPES = {
     "gptoss_chain_enqueue": (_i, [_p, _i, _i]),
     "gptoss_chain_step": (_i, [_p, _i, _p, _p, _p]),
     "gptoss_chain_run_wave": (_i, [_p, _p, _p, _i, _i, _p, C.POINTER(C.c_longlong), C.POINTER(_i)]),
+    "gptoss_chain_run_wave_on_device": (_i, [_p, _p, _p, _i, _i, _p, C.POINTER(C.c_longlong), C.POINTER(_i)]),
     "gptoss_chain_profile": (_i, [_p, _i, _i, _i, C.POINTER(C.c_double), C.POINTER(_l)]),
     "gptoss_chain_kernel_bytes": (_z, [_p, _i, _i]),
     "gptoss_chain_launches_per_step": (_i, [_p, _i]),
@@ -437,17 +438,19 @@ class Chain:
         check(load().gptoss_chain_step(self.h, T, tokens_host.ctypes.data, pos_host.ctypes.data,
                                        next_host.ctypes.data), "chain_step")
 
-    def run_wave(self, prompts, steps: int):
-        """Serves one wave (gptoss_chain_run_wave).  prompts: a list of token lists.  Returns
-        (generated [n, steps + 2] int32 closed with -1, the reference's generated-token count,
-        steps actually run)."""
+    def run_wave(self, prompts, steps: int, on_device: bool = False):
+        """Serves one wave (gptoss_chain_run_wave, or gptoss_chain_run_wave_on_device with the
+        bookkeeping kept on the GPU).  prompts: a list of token lists.  Returns (generated
+        [n, steps + 2] int32 closed with -1, the reference's generated-token count, steps
+        actually run)."""
         offs = np.zeros(len(prompts) + 1, np.int32)
         offs[1:] = np.cumsum([len(p) for p in prompts])
         toks = np.ascontiguousarray(np.concatenate([np.asarray(p, np.int32) for p in prompts]) if prompts
                                     else np.zeros(0, np.int32))
         out = np.empty((len(prompts), steps + 2), np.int32)
         total, ran = C.c_longlong(0), _i(0)
-        check(load().gptoss_chain_run_wave(self.h, toks.ctypes.data, offs.ctypes.data, len(prompts), steps,
+        fn = load().gptoss_chain_run_wave_on_device if on_device else load().gptoss_chain_run_wave
+        check(fn(self.h, toks.ctypes.data, offs.ctypes.data, len(prompts), steps,
                                            out.ctypes.data, C.byref(total), C.byref(ran)), "chain_run_wave")
         return out, int(total.value), int(ran.value)
 

@@ -39,6 +39,12 @@ struct gptoss_chain {
   size_t flush_bytes = 0;
   std::map<int, cudaGraphExec_t> graphs;                       // whole step, per T
   std::map<int, cudaGraphExec_t> io_graphs;                    // the step between its host<->device copies, per T
+  // the wave loop kept on the device (gptoss_chain_run_wave_on_device)
+  std::map<int, cudaGraphExec_t> wave_graphs; // one step followed by the bookkeeping kernel, per T
+  int *wave_prompts = nullptr, *wave_offsets = nullptr, *wave_generated = nullptr;
+  size_t wave_prompts_cap = 0, wave_generated_cap = 0; // in ints
+  struct WaveState *wave_state = nullptr;              // device
+  struct WaveState *wave_state_host = nullptr;         // pinned
   int *io_host = nullptr; // pinned staging of gptoss_chain_step: tokens | positions | picked tokens, max_tokens each
   std::map<std::pair<int, int>, cudaGraphExec_t> kind_graphs; // one kernel kind's launches, per (T, kind)
   std::vector<cudaEvent_t> events;
@@ -47,7 +53,73 @@ struct gptoss_chain {
   int qkv_dim() const { return (cfg.n_q_heads + 2 * cfg.n_kv_heads) * cfg.head_dim; }
 };
 
+// Counters of a wave served without the host in the loop.
+struct WaveState {
+  int active;          // rows not finished
+  int steps_run;       // positions completed while any row was active
+  int width;           // row pitch of `generated` (steps + 2)
+  int pad;
+  long long generated; // the reference's count over the rows that finished on an end token
+  const int *prompts;  // device: the wave's prompts back to back
+  int *out_rows;       // device: [n, width] generated tokens
+  // (the two buffers are named here, not in the kernel's arguments, so that a captured
+  // graph stays valid when a later wave needs larger ones)
+};
+
 namespace {
+
+// The per-step bookkeeping of gpu_run_wave (gpu_engine.hpp:800-826) as a kernel that
+// runs behind the step's argmax: the row takes its next prompt token while it has one
+// and the picked token afterwards, records generated tokens, and finishes on an end
+// token.  One block, so that "was anybody still active when this step began" is a
+// single read followed by a barrier; once nobody is, the kernel leaves everything as
+// it is, and the steps the host had already queued change nothing.
+__global__ void __launch_bounds__(1024)
+    wave_advance(int n, const int *__restrict__ offsets, const int *__restrict__ next,
+                 int *__restrict__ tokens, int *__restrict__ pos, int *__restrict__ done, WaveState *state) {
+  __shared__ int s_active, s_finished;
+  __shared__ long long s_count;
+  if (threadIdx.x == 0) {
+    s_active = state->active;
+    s_finished = 0;
+    s_count = 0;
+  }
+  __syncthreads();
+  if (s_active <= 0)
+    return;
+  const int width = state->width;
+  const int *__restrict__ prompts = state->prompts;
+  int *__restrict__ generated = state->out_rows;
+  for (int b = threadIdx.x; b < n; b += blockDim.x) {
+    const int p = pos[b] + 1; // every row sits at the same position
+    pos[b] = p;
+    if (done[b])
+      continue;
+    const int first = offsets[b], np = offsets[b + 1] - first;
+    int *out = generated + (size_t)b * width;
+    int token;
+    if (p < np) {
+      token = prompts[first + p];
+    } else {
+      token = next[b];
+      out[p - np] = token;
+    }
+    if (token == 199999 || token == 200002) {
+      done[b] = 1;
+      if (p - np + 1 >= 0)
+        out[p - np + 1] = -1;
+      atomicAdd(&s_finished, 1);
+      atomicAdd(reinterpret_cast<unsigned long long *>(&s_count), (unsigned long long)(long long)(p - np + 1));
+    }
+    tokens[b] = token;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    state->active = s_active - s_finished;
+    state->steps_run += 1;
+    state->generated += s_count;
+  }
+}
 
 template <typename P> int dev_alloc(gptoss_chain *c, P **p, size_t bytes) {
   void *q = nullptr;
@@ -334,6 +406,15 @@ int gptoss_chain_destroy(gptoss_chain_t *c) {
     (void)cudaGraphExecDestroy(kv.second);
   for (auto &kv : c->io_graphs)
     (void)cudaGraphExecDestroy(kv.second);
+  for (auto &kv : c->wave_graphs)
+    (void)cudaGraphExecDestroy(kv.second);
+  if (c->wave_state_host)
+    (void)cudaFreeHost(c->wave_state_host);
+  // wave_prompts / wave_generated are not in `allocs`: they are replaced when a wave needs more room
+  if (c->wave_prompts)
+    (void)cudaFree(c->wave_prompts);
+  if (c->wave_generated)
+    (void)cudaFree(c->wave_generated);
   if (c->io_host)
     (void)cudaFreeHost(c->io_host);
   for (cudaEvent_t e : c->events)
@@ -436,7 +517,7 @@ int gptoss_chain_fill_synthetic(gptoss_chain_t *c, int T, uint64_t seed, int thr
 // Captures the launches of one step (only < 0) or of one kernel kind into a graph; with
 // lead_flush an L2 flush goes first (only == GPTOSS_K_COUNT then gives the flush alone).
 static int capture_step(gptoss_chain *c, int T, int only, cudaGraphExec_t *exec_out, bool lead_flush = false,
-                        bool with_io = false) {
+                        bool with_io = false, bool with_wave_advance = false) {
   // Warm every kernel once outside capture (occupancy queries, lazy module load).
   int st = lead_flush ? gptoss_flush_l2(c->flush, c->flush_bytes, c->stream) : GPTOSS_OK;
   if (st == GPTOSS_OK)
@@ -459,6 +540,11 @@ static int capture_step(gptoss_chain *c, int T, int only, cudaGraphExec_t *exec_
     issued = issue_step(c, T, c->stream, nullptr, only);
   if (with_io && issued == GPTOSS_OK)
     issued = cuda_status(cudaMemcpyAsync(c->io_host + 2 * io_stride, c->next, io_bytes, cudaMemcpyDeviceToHost, c->stream));
+  if (with_wave_advance && issued == GPTOSS_OK) {
+    wave_advance<<<1, 1024, 0, c->stream>>>(T, c->wave_offsets, c->next, c->tokens, c->pos, c->row_done,
+                                            c->wave_state);
+    issued = cuda_status(cudaGetLastError());
+  }
   cudaGraph_t graph = nullptr;
   st = cuda_status(cudaStreamEndCapture(c->stream, &graph));
   if (issued != GPTOSS_OK || st != GPTOSS_OK) {
@@ -594,6 +680,174 @@ int gptoss_chain_run_wave(gptoss_chain_t *c, const int *prompt_tokens, const int
   if (steps_run)
     *steps_run = pos;
   return st;
+}
+
+// Room for a wave's prompts and output rows on the device.
+static int wave_reserve(gptoss_chain *c, size_t prompt_ints, size_t generated_ints) {
+  int st = GPTOSS_OK;
+  if (!c->wave_state) {
+    st = dev_alloc(c, &c->wave_offsets, ((size_t)c->max_tokens + 1) * 4);
+    if (st == GPTOSS_OK)
+      st = dev_alloc(c, &c->wave_state, sizeof(WaveState));
+    if (st == GPTOSS_OK)
+      st = cuda_status(cudaMallocHost(reinterpret_cast<void **>(&c->wave_state_host), 3 * sizeof(WaveState))); // [0] set-up and result, [1], [2] batch reports
+    if (st == GPTOSS_OK)
+      st = cuda_status(cudaMemsetAsync(c->wave_state, 0, sizeof(WaveState), c->stream));
+    if (st == GPTOSS_OK) {
+      // first launch of the bookkeeping kernel outside any capture; with no active row it returns at once
+      wave_advance<<<1, 1024, 0, c->stream>>>(0, nullptr, nullptr, nullptr, nullptr, nullptr, c->wave_state);
+      st = cuda_status(cudaGetLastError());
+    }
+    if (st == GPTOSS_OK)
+      st = cuda_status(cudaStreamSynchronize(c->stream));
+  }
+  auto grow = [&](int **buf, size_t *cap, size_t want) {
+    if (st != GPTOSS_OK || want <= *cap)
+      return;
+    (void)cudaStreamSynchronize(c->stream);
+    if (*buf)
+      (void)cudaFree(*buf);
+    *buf = nullptr;
+    *cap = 0;
+    void *q = nullptr;
+    st = cuda_status(cudaMalloc(&q, want * 4));
+    if (st == GPTOSS_OK) {
+      *buf = static_cast<int *>(q);
+      *cap = want;
+    }
+  };
+  grow(&c->wave_prompts, &c->wave_prompts_cap, prompt_ints ? prompt_ints : 1);
+  grow(&c->wave_generated, &c->wave_generated_cap, generated_ints ? generated_ints : 1);
+  return st;
+}
+
+int gptoss_chain_run_wave_on_device(gptoss_chain_t *c, const int *prompt_tokens, const int *prompt_offsets,
+                                    int n_requests, int steps, int *generated, long long *n_generated,
+                                    int *steps_run) {
+  if (!c || n_requests < 0 || n_requests > c->max_tokens || steps < 0 || steps > c->cfg.max_pos)
+    return GPTOSS_ERR_BAD_ARG;
+  if (n_generated)
+    *n_generated = 0;
+  if (steps_run)
+    *steps_run = 0;
+  if (n_requests == 0)
+    return GPTOSS_OK;
+  if (!prompt_tokens || !prompt_offsets || !generated)
+    return GPTOSS_ERR_BAD_ARG;
+  const int n = n_requests, width = steps + 2;
+  for (int b = 0; b < n; b++)
+    if (prompt_offsets[b + 1] - prompt_offsets[b] < 1)
+      return GPTOSS_ERR_BAD_ARG;
+  const size_t n_prompt = (size_t)(prompt_offsets[n] - prompt_offsets[0]);
+  int st = wave_reserve(c, n_prompt, (size_t)n * width);
+  if (st != GPTOSS_OK)
+    return st;
+
+  // the wave's inputs and starting state go to the device once
+  std::vector<int> first(n), offsets(n + 1);
+  for (int b = 0; b <= n; b++)
+    offsets[b] = prompt_offsets[b] - prompt_offsets[0];
+  for (int b = 0; b < n; b++)
+    first[b] = prompt_tokens[prompt_offsets[b]];
+  cudaStream_t s = c->stream;
+  st = cuda_status(cudaMemcpyAsync(c->wave_prompts, prompt_tokens + prompt_offsets[0], n_prompt * 4, cudaMemcpyHostToDevice, s));
+  if (st == GPTOSS_OK)
+    st = cuda_status(cudaMemcpyAsync(c->wave_offsets, offsets.data(), ((size_t)n + 1) * 4, cudaMemcpyHostToDevice, s));
+  if (st == GPTOSS_OK)
+    st = cuda_status(cudaMemcpyAsync(c->tokens, first.data(), (size_t)n * 4, cudaMemcpyHostToDevice, s));
+  if (st == GPTOSS_OK)
+    st = cuda_status(cudaMemsetAsync(c->pos, 0, (size_t)n * 4, s));
+  if (st == GPTOSS_OK)
+    st = cuda_status(cudaMemsetAsync(c->row_done, 0, (size_t)n * 4, s));
+  if (st == GPTOSS_OK)
+    st = cuda_status(cudaMemsetAsync(c->wave_generated, 0xff, (size_t)n * width * 4, s)); // every entry -1
+  WaveState *hs = c->wave_state_host;
+  if (st == GPTOSS_OK)
+    st = cuda_status(cudaStreamSynchronize(s)); // the vectors above are pageable, and hs may still be in use
+  if (st != GPTOSS_OK)
+    return st;
+  hs->active = n;
+  hs->steps_run = 0;
+  hs->width = width;
+  hs->pad = 0;
+  hs->generated = 0;
+  hs->prompts = c->wave_prompts;
+  hs->out_rows = c->wave_generated;
+  st = cuda_status(cudaMemcpyAsync(c->wave_state, hs, sizeof(WaveState), cudaMemcpyHostToDevice, s));
+  if (st == GPTOSS_OK)
+    st = cuda_status(cudaStreamSynchronize(s));
+  if (st != GPTOSS_OK)
+    return st;
+
+  auto it = c->wave_graphs.find(n);
+  if (it == c->wave_graphs.end()) {
+    cudaGraphExec_t exec = nullptr;
+    st = capture_step(c, n, -1, &exec, false, false, true);
+    if (st != GPTOSS_OK)
+      return st;
+    it = c->wave_graphs.emplace(n, exec).first;
+  }
+  // Steps are queued a batch at a time, and the next batch is queued before the host looks
+  // at the counters the previous one left (copied to one of two pinned slots, each with
+  // its event), so the GPU never waits for the host.  Once a batch reports every row done,
+  // no more are queued; steps already queued past that point run with every row masked
+  // and leave the bookkeeping alone.
+  const int batch = 16;
+  while (c->events.size() < 2 && st == GPTOSS_OK) {
+    cudaEvent_t e = nullptr;
+    st = cuda_status(cudaEventCreate(&e));
+    if (st == GPTOSS_OK)
+      c->events.push_back(e);
+  }
+  int queued = 0, batches = 0;
+  auto queue_batch = [&]() {
+    const int now = steps - queued < batch ? steps - queued : batch;
+    for (int i = 0; i < now && st == GPTOSS_OK; i++)
+      st = cuda_status(cudaGraphLaunch(it->second, s));
+    queued += now;
+    if (st == GPTOSS_OK)
+      st = cuda_status(cudaMemcpyAsync(hs + 1 + (batches & 1), c->wave_state, sizeof(WaveState),
+                                       cudaMemcpyDeviceToHost, s));
+    if (st == GPTOSS_OK)
+      st = cuda_status(cudaEventRecord(c->events[batches & 1], s));
+    batches++;
+  };
+  if (steps > 0 && st == GPTOSS_OK)
+    queue_batch();
+  for (int seen = 0; seen < batches && st == GPTOSS_OK; seen++) {
+    if (queued < steps)
+      queue_batch(); // keeps the GPU busy while the host waits for the batch before it
+    st = cuda_status(cudaEventSynchronize(c->events[seen & 1]));
+    if (st == GPTOSS_OK && hs[1 + (seen & 1)].active <= 0)
+      break;
+  }
+  std::vector<int> done(n);
+  if (st == GPTOSS_OK)
+    st = cuda_status(cudaMemcpyAsync(hs, c->wave_state, sizeof(WaveState), cudaMemcpyDeviceToHost, s));
+  if (st == GPTOSS_OK)
+    st = cuda_status(cudaMemcpyAsync(generated, c->wave_generated, (size_t)n * width * 4, cudaMemcpyDeviceToHost, s));
+  if (st == GPTOSS_OK)
+    st = cuda_status(cudaMemcpyAsync(done.data(), c->row_done, (size_t)n * 4, cudaMemcpyDeviceToHost, s));
+  if (st == GPTOSS_OK)
+    st = cuda_status(cudaStreamSynchronize(s));
+  if (st != GPTOSS_OK)
+    return st;
+  // rows still running when the wave ended are closed here, as after the reference's loop (:828-838)
+  const int pos = hs->steps_run;
+  long long total = hs->generated;
+  for (int b = 0; b < n; b++) {
+    if (done[b])
+      continue;
+    const int np = prompt_offsets[b + 1] - prompt_offsets[b];
+    if (pos - np + 1 >= 0)
+      generated[(size_t)b * width + (pos - np + 1)] = -1;
+    total += pos - np + 1;
+  }
+  if (n_generated)
+    *n_generated = total;
+  if (steps_run)
+    *steps_run = pos;
+  return GPTOSS_OK;
 }
 
 int gptoss_chain_profile(gptoss_chain_t *c, int T, int steps, int mode, double *ms_per_kind,

@@ -258,6 +258,13 @@ def test_wave_loop_with_finished_rows(gpu, orc):
         assert ran == want_pos and total == want_total
         assert np.array_equal(out, want_out)
         assert np.array_equal(ch.download(pkg.BUF_ROW_DONE, 0, np.int32, (n,)), want_done)
+        # the same wave with the bookkeeping kept on the GPU; 40 steps are queued in three batches
+        for many in (steps, 40):
+            want = _wave_reference(prompts, picks, many)
+            out, total, ran = ch.run_wave(prompts, many, on_device=True)
+            assert (ran, total) == (want[2], want[1])
+            assert np.array_equal(out, want[0])
+            assert np.array_equal(ch.download(pkg.BUF_ROW_DONE, 0, np.int32, (n,)), want[3])
         # rows that were finished before the last step got no experts in it
         e = ch.download(pkg.BUF_TOPK_E, 0, np.int32, (n, c.top_k))
         w = ch.download(pkg.BUF_TOPK_W, 0, np.float32, (n, c.top_k))
@@ -267,7 +274,13 @@ def test_wave_loop_with_finished_rows(gpu, orc):
         logits[:, 199999] = big
         ch.upload(pkg.BUF_LOGITS, 0, logits)
         short = [[1, 2]] * n
-        out, total, ran = ch.run_wave(short, steps)
-        assert ran == 2 and total == n * 1 and (out[:, 0] == 199999).all() and (out[:, 1] == -1).all()
+        for on_device in (False, True):
+            out, total, ran = ch.run_wave(short, 40, on_device=on_device)
+            assert ran == 2 and total == n * 1 and (out[:, 0] == 199999).all() and (out[:, 1:] == -1).all()
+        # a smaller wave after a larger one, and prompts that need a larger device buffer
+        long_prompts = [list(r.integers(0, 199000, 300)) for _ in range(5)]
+        want = _wave_reference(long_prompts, picks[:5], 6)
+        out, total, ran = ch.run_wave(long_prompts, 6, on_device=True)
+        assert (ran, total) == (want[2], want[1]) and np.array_equal(out, want[0])
     finally:
         ch.close()
