@@ -96,10 +96,33 @@ class _Lib:
         self._argmax_rows = sig("argmax_rows", None, _i32p, _f32p, C.c_int, C.c_long, C.c_int)
         self._forward_seq = sig("forward_seq", C.c_int, C.c_void_p, _f32p, _i32p, C.c_int, _f32p)
         self._max_threads = sig("max_threads", C.c_int)
+        # the KV-cache index functions and the bf16 rounding rule (the reference library has
+        # them when it was built from a checkout that holds the kernels' headers)
+        self.has_cache_layout = p == "orc_" or bool(sig("has_cache_layout", C.c_int)())
+        if self.has_cache_layout:
+            _i64p = np.ctypeslib.ndpointer(dtype=np.int64, flags="C_CONTIGUOUS")
+            _u16p = np.ctypeslib.ndpointer(dtype=np.uint16, flags="C_CONTIGUOUS")
+            self._cache_indices = sig("cache_indices", None, C.c_long, _i32p, _i32p, _i32p, _i32p, C.c_int, C.c_int,
+                                      _i64p, _i64p, _i64p)
+            self._f32_to_bf16 = sig("f32_to_bf16", None, C.c_long, _f32p, _u16p)
 
     # -- single-row primitives ------------------------------------------------
     def max_threads(self) -> int:
         return int(self._max_threads())
+
+    def cache_indices(self, b, slot, g, i, slots, kv_dim):
+        """For tuples (b, slot, g, i): element offsets of the key element, the value code and
+        the value scale in the chunk64 caches."""
+        b, slot, g, i = (np.ascontiguousarray(a, np.int32) for a in (b, slot, g, i))
+        k_at, vq_at, vs_at = (np.empty(b.size, np.int64) for _ in range(3))
+        self._cache_indices(b.size, b, slot, g, i, slots, kv_dim, k_at, vq_at, vs_at)
+        return k_at, vq_at, vs_at
+
+    def f32_to_bf16(self, x):
+        x = np.ascontiguousarray(x, np.float32)
+        out = np.empty(x.shape, np.uint16)
+        self._f32_to_bf16(x.size, x, out)
+        return out
 
     def rmsnorm(self, x, gain):
         x = np.ascontiguousarray(x, np.float32)

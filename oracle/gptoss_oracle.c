@@ -407,8 +407,11 @@ ORC_API void orc_moe_gather(float *Xg, const float *t, const int *row_pair, int 
  * and rotated.  Keys: bf16 round-to-nearest-even.  Values: amax = max|v| over
  * the head's 64 numbers, inv = amax > 0 ? 127/amax : 0, code =
  * clamp(rintf(v*inv), +-127), scale = amax/127, all in fp32.  Like the grouping
- * step this restates a GPU kernel that has no CPU form in the reference, so it
- * is NOT pinned against a run of the reference. */
+ * step this restates a GPU kernel that has no CPU form in the reference, so the
+ * value arithmetic is NOT pinned against a run of the reference; the layout (the
+ * three index functions) and the bf16 rounding rule are: the reference defines
+ * them in host-callable form and tests/test_oracle_pins.py holds these against
+ * them. */
 static size_t orc_chunk64(int b, int slot, int g, int i, int slots, int kv_dim) {
   return ((size_t)b * slots + (size_t)(slot & ~63)) * kv_dim + (size_t)g * 64 * 64 +
          (size_t)(slot & 63) * 64 + i;
@@ -421,6 +424,23 @@ static uint16_t orc_bf16(float f) {
   u += 0x7fffu + ((u >> 16) & 1u);
   return (uint16_t)(u >> 16);
 }
+/* The three index functions and the rounding rule on their own, so that they can be
+ * held against the reference's (which, unlike the kernel around them, are callable on
+ * the host). */
+ORC_API void orc_cache_indices(long n, const int *b, const int *slot, const int *g, const int *i, int slots,
+                               int kv_dim, long long *k_at, long long *vq_at, long long *vs_at) {
+  for (long t = 0; t < n; t++) {
+    k_at[t] = (long long)orc_chunk64(b[t], slot[t], g[t], i[t], slots, kv_dim);
+    vq_at[t] = (long long)(orc_chunk64(b[t], slot[t] & ~15, g[t], 0, slots, kv_dim) + ((slot[t] >> 2) & 3) * 256 +
+                           (i[t] >> 2) * 16 + (i[t] & 3) * 4 + (slot[t] & 3));
+    vs_at[t] = (long long)(orc_chunk64(b[t], slot[t], g[t], 0, slots, kv_dim) / 64);
+  }
+}
+ORC_API void orc_f32_to_bf16(long n, const float *in, uint16_t *out) {
+  for (long t = 0; t < n; t++)
+    out[t] = orc_bf16(in[t]);
+}
+
 ORC_API void orc_kv_cache_write(const float *qkv, long row_stride, int T, int n_q_heads, int n_kv_heads,
                                 uint16_t *kc, int8_t *vq, float *vs, int slots, const int *slot_of_row) {
   const int kv_dim = n_kv_heads * 64;

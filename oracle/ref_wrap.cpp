@@ -109,3 +109,39 @@ REF_API int ref_forward_seq(const void *config_image, float *flat_weights, const
 }
 
 REF_API int ref_config_size(void) { return (int)sizeof(Config); }
+
+// ---- the KV-cache layout and the bf16 rounding rule of the reference's kernels ----------
+// Four small functions that the reference defines in its HIP headers in host-callable
+// form; the Makefile copies their definitions (and nothing else) out of
+// kernels/fast_attention.hpp and kernels/fast_common.hpp into REF_CACHE_PART.  The
+// qualifiers and the one intrinsic they use are given plain C++ meanings here.
+#ifdef REF_CACHE_PART
+#include <stdint.h>
+#include <string.h>
+#define __host__
+#define __device__
+typedef uint16_t bf16_t;
+static inline uint32_t __float_as_uint(float f) {
+  uint32_t u;
+  memcpy(&u, &f, 4);
+  return u;
+}
+#include REF_CACHE_PART
+
+REF_API int ref_has_cache_layout(void) { return 1; }
+// For n (b, slot, g, i) tuples: where a key element, a value code and the value scale go.
+REF_API void ref_cache_indices(long n, const int *b, const int *slot, const int *g, const int *i, int slots,
+                               int kv_dim, long long *k_at, long long *vq_at, long long *vs_at) {
+  for (long t = 0; t < n; t++) {
+    k_at[t] = (long long)kv_index_chunk64(b[t], slot[t], g[t], i[t], slots, kv_dim);
+    vq_at[t] = (long long)vq_index_chunk64(b[t], slot[t], g[t], i[t], slots, kv_dim);
+    vs_at[t] = (long long)vs_index_chunk64(b[t], slot[t], g[t], slots, kv_dim);
+  }
+}
+REF_API void ref_f32_to_bf16(long n, const float *in, uint16_t *out) {
+  for (long t = 0; t < n; t++)
+    out[t] = f32_to_bf16(in[t]);
+}
+#else
+REF_API int ref_has_cache_layout(void) { return 0; }
+#endif

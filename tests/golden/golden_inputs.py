@@ -114,3 +114,27 @@ def tiny_model():
                n_q_heads=4, n_kv_heads=2, seq_len=16, orig_ctx=4096, theta=150000.0, factor=32.0,
                window=4, limit=7.0)
     return cfg
+
+
+def case_cache_layout():
+    """(b, slot, g, i) tuples for the KV-cache index functions: every slot of three chunks for
+    a few (sequence, head, element) corners, plus hashed tuples; slots = 192, 8 heads of 64."""
+    slots, kv_dim = 192, 512
+    grid = [(b, s, g, i) for b in (0, 3) for s in range(slots) for g in (0, 7) for i in (0, 1, 5, 63)]
+    n = 4000
+    extra = np.stack([small_ints(81, (n,), 0, 6), small_ints(82, (n,), 0, slots), small_ints(83, (n,), 0, 8),
+                      small_ints(84, (n,), 0, 64)], axis=1)
+    t = np.concatenate([np.array(grid, np.int32), extra.astype(np.int32)])
+    return t[:, 0].copy(), t[:, 1].copy(), t[:, 2].copy(), t[:, 3].copy(), slots, kv_dim
+
+
+def case_bf16_rounding():
+    """fp32 bit patterns around every rounding case of fp32 -> bf16: ties (even and odd), just
+    above and below a tie, carries into the exponent, the largest finite value, infinities,
+    NaNs with and without payload in the kept bits, denormals, zeros."""
+    hi = np.array([0x0000, 0x0001, 0x007F, 0x0080, 0x3F80, 0x3F81, 0x7F7E, 0x7F7F, 0x7F80, 0x7F81, 0x7FC0, 0x7FFF],
+                  np.uint32)
+    lo = np.array([0x0000, 0x0001, 0x7FFF, 0x8000, 0x8001, 0xFFFF], np.uint32)
+    bits = ((hi[:, None] << 16) | lo[None, :]).ravel()
+    bits = np.concatenate([bits, bits | np.uint32(0x80000000), (hashed(85, 2000) & 0xFFFFFFFF).astype(np.uint32)])
+    return bits.astype(np.uint32).view(np.float32)

@@ -13,6 +13,8 @@ stores the expected outputs:
   * logits of a tiny 2-layer model over 10 decode steps: the REFERENCE's forward(), which
     is what pins the loops that only exist inline in it (bias add, SwiGLU, expert combine,
     residual);
+  * the chunk64 KV-cache index functions and the fp32 -> bf16 rounding rule: the REFERENCE's
+    host-callable definitions in its kernel headers;
   * SwiGLU rows and combine rows: produced by the restated oracle (the reference has no
     callable form of those loops); they are regression vectors for the oracle, whose
     agreement with forward() is checked separately.
@@ -65,6 +67,13 @@ def main():
     out["swiglu_out"] = orc.swiglu_rows(gi.case_swiglu())
     xc, Z, row_of, wt, e = gi.case_combine()
     out["combine_x"] = orc.combine_rows(xc, Z, row_of, wt, e, gi.E20)
+
+    # the KV-cache layout and the bf16 rounding rule: host-callable functions of the
+    # reference's kernel headers (kernels/fast_attention.hpp, kernels/fast_common.hpp)
+    b, slot, g, i, slots, kv_dim = gi.case_cache_layout()
+    k_at, vq_at, vs_at = ref.cache_indices(b, slot, g, i, slots, kv_dim)
+    out["cache_k_at"], out["cache_vq_at"], out["cache_vs_at"] = (a.astype(np.int32) for a in (k_at, vq_at, vs_at))
+    out["bf16_bits"] = ref.f32_to_bf16(gi.case_bf16_rounding())
 
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden.npz")
     np.savez_compressed(path, **out)

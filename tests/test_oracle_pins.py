@@ -74,6 +74,42 @@ def test_golden_swiglu_combine_regression(orc, golden):
     assert_bit_equal(orc.combine_rows(x, Z, row_of, w, e, gi.E20), golden["combine_x"], "combine")
 
 
+def test_golden_cache_layout_and_bf16_rounding(orc, golden):
+    """Where a key element, a value code and a value scale go in the chunk64 caches, and how
+    fp32 becomes bf16: the reference's own functions wrote these vectors."""
+    b, slot, g, i, slots, kv_dim = gi.case_cache_layout()
+    k_at, vq_at, vs_at = orc.cache_indices(b, slot, g, i, slots, kv_dim)
+    assert np.array_equal(k_at, golden["cache_k_at"])
+    assert np.array_equal(vq_at, golden["cache_vq_at"])
+    assert np.array_equal(vs_at, golden["cache_vs_at"])
+    assert np.array_equal(orc.f32_to_bf16(gi.case_bf16_rounding()), golden["bf16_bits"])
+
+
+def test_cache_layout_is_what_the_cache_writer_uses(orc):
+    """orc_kv_cache_write places every element where the index functions say."""
+    T, n_q, n_kv, slots = 5, 2, 3, 128
+    kv_dim = n_kv * 64
+    r = np.random.default_rng(5)
+    qkv = r.standard_normal((T, (n_q + 2 * n_kv) * 64)).astype(np.float32)
+    slot_of = np.array([0, 17, 63, 64, 127], np.int32)
+    kc = np.full(T * slots * kv_dim, 0xAAAA, np.uint16)
+    vq = np.full(T * slots * kv_dim, 0x55, np.int8)
+    vs = np.full(T * slots * n_kv, -1.0, np.float32)
+    orc.kv_cache_write(qkv, n_q, n_kv, kc, vq, vs, slots, slot_of)
+    bb, gg, ii = np.meshgrid(np.arange(T), np.arange(n_kv), np.arange(64), indexing="ij")
+    k_at, vq_at, vs_at = orc.cache_indices(bb.ravel(), slot_of[bb.ravel()], gg.ravel(), ii.ravel(), slots, kv_dim)
+    k = qkv[:, n_q * 64:n_q * 64 + kv_dim].reshape(T, n_kv, 64)
+    v = qkv[:, n_q * 64 + kv_dim:].reshape(T, n_kv, 64)
+    assert np.array_equal(kc[k_at], orc.f32_to_bf16(k).ravel())
+    amax = np.abs(v).max(axis=2, keepdims=True)
+    codes = np.clip(np.rint(v * (np.float32(127.0) / amax)), -127, 127).astype(np.int8)
+    assert np.array_equal(vq[vq_at], codes.ravel())
+    assert np.array_equal(vs[vs_at].reshape(T, n_kv, 64)[:, :, 0], (amax / np.float32(127.0))[:, :, 0])
+    touched = np.zeros(kc.size, bool)
+    touched[k_at] = True
+    assert (kc[~touched] == 0xAAAA).all() and len(np.unique(k_at)) == k_at.size == len(np.unique(vq_at))
+
+
 def test_topk_ties_go_to_the_lowest_index(orc):
     """Guards the one place the CPU program leans on the C library: qsort leaving equal
     scores in index order."""
@@ -168,6 +204,21 @@ def test_ref_batched_rows(orc, ref):
     lg[2, 40000] = lg[2, 123] = 77.0
     assert np.array_equal(orc.argmax_rows(lg), ref.argmax_rows(lg))
     assert orc.argmax_rows(lg)[2] == 123
+
+
+def test_ref_cache_layout_and_bf16_rounding(orc, ref):
+    if not ref.has_cache_layout:
+        pytest.skip("reference library built without the kernels' headers")
+    r = np.random.default_rng(9)
+    for slots, n_kv in ((64, 1), (192, 8), (4096, 8)):
+        n = 20000
+        b, slot, g, i = r.integers(0, 7, n), r.integers(0, slots, n), r.integers(0, n_kv, n), r.integers(0, 64, n)
+        for got, want in zip(orc.cache_indices(b, slot, g, i, slots, n_kv * 64),
+                             ref.cache_indices(b, slot, g, i, slots, n_kv * 64)):
+            assert np.array_equal(got, want)
+    bits = r.integers(0, 2**32, 200000, dtype=np.uint64).astype(np.uint32).view(np.float32)
+    assert np.array_equal(orc.f32_to_bf16(bits), ref.f32_to_bf16(bits))
+    assert np.array_equal(orc.f32_to_bf16(gi.case_bf16_rounding()), ref.f32_to_bf16(gi.case_bf16_rounding()))
 
 
 @pytest.mark.parametrize("seed", [1, 2, 3])
