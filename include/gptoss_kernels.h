@@ -257,6 +257,23 @@ GPTOSS_API int gptoss_moe_gather(gptoss_stream_t stream, int R, const void *t,
                                  void *Xg, int H, unsigned flags);
 
 /*
+ * gptoss_qkv_bias_rope and gptoss_kv_cache_write in one launch, which is what the
+ * reference's rope_kv_bf16 is (kernels/fast_misc.hpp:48-127; launch gpu_engine.hpp:495-496):
+ * the row is biased and rotated and written to qkv_out as by gptoss_qkv_bias_rope, and
+ * its key heads (bf16) and value heads (int8 codes + scale) also go to the caches as by
+ * gptoss_kv_cache_write (arguments kc .. slot_scalar as there), taken from the fp32 values
+ * before they are rounded to out_dtype -- the reference's order, and the same bits as the
+ * two calls when out_dtype is fp32.  head_dim must be 64 and slots a multiple of 64.
+ */
+GPTOSS_API int gptoss_qkv_bias_rope_kv(gptoss_stream_t stream, int T, const void *qkv_in,
+                                       gptoss_dtype_t in_dtype, long in_row_stride, const float *bias,
+                                       const int *pos, int pos_scalar, const float *cos_tab,
+                                       const float *sin_tab, int n_pos, int n_q_heads, int n_kv_heads,
+                                       int head_dim, void *qkv_out, gptoss_dtype_t out_dtype,
+                                       long out_row_stride, uint16_t *kc, int8_t *vq, float *vs, int slots,
+                                       const int *slot_of_row, int slot_scalar, unsigned flags);
+
+/*
  * KV-cache write of one decode step, the half of rope_kv_bf16 that follows the
  * rotation (kernels/fast_misc.hpp:48-127; launch gpu_engine.hpp:495-496): from
  * each row of the biased, rotated qkv tensor (gptoss_qkv_bias_rope's output)

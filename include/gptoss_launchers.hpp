@@ -74,17 +74,16 @@ static inline void rope_exact(gptoss_stream_t s, int B, float *qkv, int row_stri
 }
 
 // :495  rope_kv_bf16(s, B, qkv, row_stride, cosv, sinv, n_q_heads, n_kv_heads, kc, vq, vs, slots, slot,
-// rotate_q): rotation (of the keys, and of the queries with rotate_q), then the cache write.  One
-// difference: the rotated keys are also left in qkv (the reference writes them to the cache only).
+// rotate_q): rotation (of the keys, and of the queries with rotate_q) and the cache write, one launch.
+// One difference: the rotated keys are also left in qkv (the reference writes them to the cache only).
 static inline void rope_kv_bf16(gptoss_stream_t s, int B, float *qkv, int row_stride, const float *cosv,
                                 const float *sinv, int n_q_heads, int n_kv_heads, bf16_t *kc, int8_t *vq,
                                 float *vs, int slots, int slot, bool rotate_q = true) {
-  float *first = rotate_q ? qkv : qkv + (size_t)n_q_heads * 64; // skip the query heads
-  GPTOSS_CHECK(gptoss_qkv_bias_rope(s, B, first, GPTOSS_F32, row_stride, nullptr, nullptr, 0, cosv, sinv, 1,
-                                    rotate_q ? n_q_heads : 0, n_kv_heads, 64, first, GPTOSS_F32, row_stride,
-                                    0));
-  GPTOSS_CHECK(gptoss_kv_cache_write(s, B, qkv, GPTOSS_F32, row_stride, n_q_heads, n_kv_heads, 64, kc, vq, vs,
-                                     slots, nullptr, slot, 0));
+  // without rotate_q the row is described from its first key head on: no query heads at all
+  float *first = rotate_q ? qkv : qkv + (size_t)n_q_heads * 64;
+  GPTOSS_CHECK(gptoss_qkv_bias_rope_kv(s, B, first, GPTOSS_F32, row_stride, nullptr, nullptr, 0, cosv, sinv, 1,
+                                       rotate_q ? n_q_heads : 0, n_kv_heads, 64, first, GPTOSS_F32, row_stride,
+                                       kc, vq, vs, slots, nullptr, slot, 0));
 }
 
 // :525  router_topk_wave_kernel<<<...>>>(logits, E, k, topk_w, topk_e, B, done, slot_of)

@@ -66,6 +66,8 @@ PROTOTYPES = {
     "gptoss_embed_rmsnorm": (_i, [_p, _i, _p, _i, _i, _p, _p, _p, _p, _i, _i, _u]),
     "gptoss_add_rmsnorm": (_i, [_p, _i, _p, _p, _i, _p, _p, _i, _i, _u]),
     "gptoss_qkv_bias_rope": (_i, [_p, _i, _p, _i, _l, _p, _p, _i, _p, _p, _i, _i, _i, _i, _p, _i, _l, _u]),
+    "gptoss_qkv_bias_rope_kv": (_i, [_p, _i, _p, _i, _l, _p, _p, _i, _p, _p, _i, _i, _i, _i, _p, _i, _l,
+                                    _p, _p, _p, _i, _p, _i, _u]),
     "gptoss_router_topk": (_i, [_p, _i, _p, _i, _i, _i, _p, _p, _p, _p, _u]),
     "gptoss_swiglu": (_i, [_p, _p, _i, _p, _i, _z, _i, _f, _u]),
     "gptoss_moe_combine": (_i, [_p, _i, _p, _p, _i, _p, _p, _p, _i, _i, _p, _p, _p, _i, _u]),
@@ -258,6 +260,16 @@ def qkv_bias_rope(T, qkv_in, in_dtype, in_stride, bias, pos, pos_scalar, cos_tab
     check(load().gptoss_qkv_bias_rope(stream, T, _ptr(qkv_in), in_dtype, in_stride, _ptr(bias), _ptr(pos),
                                       pos_scalar, _ptr(cos_tab), _ptr(sin_tab), n_pos, n_q, n_kv,
                                       head_dim, _ptr(qkv_out), out_dtype, out_stride, flags), "qkv_bias_rope")
+
+
+def qkv_bias_rope_kv(T, qkv_in, in_dtype, in_stride, bias, pos, pos_scalar, cos_tab, sin_tab, n_pos,
+                     n_q, n_kv, head_dim, qkv_out, out_dtype, out_stride, kc, vq, vs, slots,
+                     slot_of_row=None, slot_scalar=0, flags=0, stream=None):
+    check(load().gptoss_qkv_bias_rope_kv(stream, T, _ptr(qkv_in), in_dtype, in_stride, _ptr(bias), _ptr(pos),
+                                         pos_scalar, _ptr(cos_tab), _ptr(sin_tab), n_pos, n_q, n_kv,
+                                         head_dim, _ptr(qkv_out), out_dtype, out_stride, _ptr(kc), _ptr(vq),
+                                         _ptr(vs), slots, _ptr(slot_of_row), slot_scalar, flags),
+          "qkv_bias_rope_kv")
 
 
 def router_topk(T, logits, dtype, E, k, topk_w, topk_e, done=None, slot_of=None, flags=0, stream=None):

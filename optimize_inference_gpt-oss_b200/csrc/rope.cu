@@ -44,14 +44,35 @@ __device__ __forceinline__ void rotate8(Vec8 &a, Vec8 &b, const Vec8 &c, const V
   }
 }
 
+// Where the rotated keys and the values of a row also go when the launch writes the KV
+// cache (gptoss_qkv_bias_rope_kv): the caches in the chunk64 layouts, 64-wide heads.
+struct Cache {
+  uint16_t *kc;
+  int8_t *vq;
+  float *vs;
+  int slots;
+  const int *slot_of_row;
+  int slot_scalar;
+  int n_q_heads, n_kv_heads;
+};
+
+// Element (b, slot, g, i) of a chunk64 cache with kv_dim = n_kv_heads * 64.
+__device__ __forceinline__ size_t chunk64_at(int b, int slot, int g, int i, int slots, int kv_dim) {
+  return ((size_t)b * slots + (size_t)(slot & ~63)) * kv_dim + (size_t)g * 64 * 64 + (size_t)(slot & 63) * 64 + i;
+}
+
 // blockDim.x >= n_heads * (head_dim / 16); thread t owns item t.
 // Stage layout: [row: width * sizeof(IT)] [per warp: cos (half floats), sin (half floats)].
-template <typename IT, typename OT, bool EXACT, bool FMA, int STAGES>
+// KV: the launch also writes the row's keys (bf16) and values (int8 codes + scale) into
+// the caches, from the fp32 values it holds in registers (head_dim is 64 then, so a head is
+// the 4 consecutive lanes of its 4 pieces and the value head's max |v| is two shuffles).
+template <typename IT, typename OT, bool EXACT, bool FMA, int STAGES, bool KV>
 __global__ void bias_rope_rows(const IT *qkv_in, long in_stride, const float *__restrict__ bias,
                                const int *__restrict__ pos, int pos_scalar,
                                const float *__restrict__ cos_tab,
                                const float *__restrict__ sin_tab, int n_pos, int n_rot_heads,
-                               int n_heads, int head_dim, OT *qkv_out, long out_stride, int T) {
+                               int n_heads, int head_dim, OT *qkv_out, long out_stride, int T,
+                               Cache cache) {
   pdl_prologue();
   constexpr int SI = sizeof(IT);
   extern __shared__ __align__(16) unsigned char ring[];
@@ -124,9 +145,15 @@ __global__ void bias_rope_rows(const IT *qkv_in, long in_stride, const float *__
     cp_async_wait<STAGES - 1>();
     __syncwarp(); // the cos/sin pieces were copied by other lanes of this warp
 
+    Vec8 a, b;
+    if constexpr (KV) {
+#pragma unroll
+      for (int i = 0; i < 8; i++)
+        a.v[i] = b.v[i] = 0.0f;
+    }
     if (active) {
       const unsigned char *sr = ring + (size_t)stage * stage_bytes;
-      Vec8 a = smem_load8<IT>(sr + lo * SI), b = smem_load8<IT>(sr + hi * SI);
+      a = smem_load8<IT>(sr + lo * SI), b = smem_load8<IT>(sr + hi * SI);
       if (bias) {
 #pragma unroll
         for (int i = 0; i < 8; i++) {
@@ -143,6 +170,50 @@ __global__ void bias_rope_rows(const IT *qkv_in, long in_stride, const float *__
       OT *out = qkv_out + (size_t)row * out_stride;
       store8(out, lo, a);
       store8(out, hi, b);
+    }
+    if constexpr (KV) {
+      // max |v| over the head: every lane takes part in the shuffles, whatever its head is
+      float amax = 0.0f;
+#pragma unroll
+      for (int i = 0; i < 8; i++)
+        amax = fmaxf(amax, fmaxf(fabsf(a.v[i]), fabsf(b.v[i])));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      const int slot = cache.slot_of_row ? __ldg(cache.slot_of_row + row) : cache.slot_scalar;
+      if (active && head >= cache.n_q_heads && slot >= 0 && slot < cache.slots) {
+        const int kv_dim = cache.n_kv_heads * 64;
+        const int g = head - cache.n_q_heads;
+        if (g < cache.n_kv_heads) { // a key head: two runs of 8 bf16 values
+          uint16_t *k = cache.kc + chunk64_at((int)row, slot, g, 0, cache.slots, kv_dim);
+          uint4 lo8, hi8;
+          lo8.x = f32_to_bf16_bits(a.v[0]) | (f32_to_bf16_bits(a.v[1]) << 16);
+          lo8.y = f32_to_bf16_bits(a.v[2]) | (f32_to_bf16_bits(a.v[3]) << 16);
+          lo8.z = f32_to_bf16_bits(a.v[4]) | (f32_to_bf16_bits(a.v[5]) << 16);
+          lo8.w = f32_to_bf16_bits(a.v[6]) | (f32_to_bf16_bits(a.v[7]) << 16);
+          hi8.x = f32_to_bf16_bits(b.v[0]) | (f32_to_bf16_bits(b.v[1]) << 16);
+          hi8.y = f32_to_bf16_bits(b.v[2]) | (f32_to_bf16_bits(b.v[3]) << 16);
+          hi8.z = f32_to_bf16_bits(b.v[4]) | (f32_to_bf16_bits(b.v[5]) << 16);
+          hi8.w = f32_to_bf16_bits(b.v[6]) | (f32_to_bf16_bits(b.v[7]) << 16);
+          *reinterpret_cast<uint4 *>(k + piece * 8) = lo8;
+          *reinterpret_cast<uint4 *>(k + 32 + piece * 8) = hi8;
+        } else { // a value head: codes and one scale (kernels/fast_misc.hpp:79-87)
+          const int gv = g - cache.n_kv_heads;
+          const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+          // byte of code (slot, dim i): 16-slot tile, then ((slot >> 2) & 3) * 256 + (i >> 2) * 16 + (i & 3) * 4 + (slot & 3)
+          int8_t *q = cache.vq + chunk64_at((int)row, slot & ~15, gv, 0, cache.slots, kv_dim) +
+                      ((slot >> 2) & 3) * 256 + (slot & 3);
+#pragma unroll
+          for (int j = 0; j < 8; j++) {
+            const int i0 = piece * 8 + j, i1 = 32 + i0;
+            const float c0 = fminf(fmaxf(rintf(__fmul_rn(a.v[j], inv)), -127.0f), 127.0f);
+            const float c1 = fminf(fmaxf(rintf(__fmul_rn(b.v[j], inv)), -127.0f), 127.0f);
+            q[(i0 >> 2) * 16 + (i0 & 3) * 4] = (int8_t)c0;
+            q[(i1 >> 2) * 16 + (i1 & 3) * 4] = (int8_t)c1;
+          }
+          if (piece == 0)
+            cache.vs[chunk64_at((int)row, slot, gv, 0, cache.slots, kv_dim) / 64] = __fdiv_rn(amax, 127.0f);
+        }
+      }
     }
     __syncwarp(); // all lanes are done with this stage's cos/sin before it is refilled
     stage = stage + 1 == STAGES ? 0 : stage + 1;
@@ -203,18 +274,19 @@ struct Args {
   void *out;
   long out_stride;
   int T;
+  Cache cache; // cache.kc == nullptr: no cache write
 };
 
-template <typename IT, typename OT, bool EXACT, bool FMA, int STAGES>
+template <typename IT, typename OT, bool EXACT, bool FMA, int STAGES, bool KV>
 int launch_pipe(cudaStream_t s, const Args &a, int threads, size_t smem) {
-  auto k = bias_rope_rows<IT, OT, EXACT, FMA, STAGES>;
+  auto k = bias_rope_rows<IT, OT, EXACT, FMA, STAGES, KV>;
   const int per_sm = blocks_per_sm_smem(k, threads, smem);
   if (per_sm < 1)
     return GPTOSS_ERR_UNSUPPORTED;
   launch_kernel(k, dim3(row_grid(a.T, per_sm)), dim3(threads), smem, s, 
       static_cast<const IT *>(a.in), a.in_stride, a.bias, a.pos, a.pos_scalar, a.cos_tab, a.sin_tab,
       a.n_pos, a.n_q + a.n_kv, a.n_q + 2 * a.n_kv, a.head_dim, static_cast<OT *>(a.out),
-      a.out_stride, a.T);
+      a.out_stride, a.T, a.cache);
   return launch_status();
 }
 
@@ -231,15 +303,22 @@ template <typename IT, typename OT, bool EXACT, bool FMA> int launch(cudaStream_
                                (size_t)(threads / 32) * (size_t)a.head_dim * 4;
     const int stages = pick_stages(stage_bytes);
     int st = GPTOSS_ERR_UNSUPPORTED;
+    if (a.cache.kc) { // with the cache write: the model's shape class only (64-wide heads, a 4-deep ring)
+      if (stages == 4 && a.head_dim == 64)
+        st = launch_pipe<IT, OT, EXACT, FMA, 4, true>(s, a, threads, stage_bytes * 4);
+      return st;
+    }
     if (stages == 4)
-      st = launch_pipe<IT, OT, EXACT, FMA, 4>(s, a, threads, stage_bytes * 4);
+      st = launch_pipe<IT, OT, EXACT, FMA, 4, false>(s, a, threads, stage_bytes * 4);
     else if (stages == 3)
-      st = launch_pipe<IT, OT, EXACT, FMA, 3>(s, a, threads, stage_bytes * 3);
+      st = launch_pipe<IT, OT, EXACT, FMA, 3, false>(s, a, threads, stage_bytes * 3);
     else if (stages == 2)
-      st = launch_pipe<IT, OT, EXACT, FMA, 2>(s, a, threads, stage_bytes * 2);
+      st = launch_pipe<IT, OT, EXACT, FMA, 2, false>(s, a, threads, stage_bytes * 2);
     if (st != GPTOSS_ERR_UNSUPPORTED)
       return st;
   }
+  if (a.cache.kc)
+    return GPTOSS_ERR_UNSUPPORTED; // the caller falls back to the two separate launches
   launch_kernel(bias_rope_rows_generic<IT, OT, EXACT, FMA>, dim3(row_grid(a.T, 8)), dim3(256), 0, s, 
       static_cast<const IT *>(a.in), a.in_stride, a.bias, a.pos, a.pos_scalar, a.cos_tab, a.sin_tab,
       a.n_pos, n_rot, n_heads, a.head_dim, static_cast<OT *>(a.out), a.out_stride, a.T);
@@ -255,14 +334,13 @@ template <typename IT, typename OT> int launch_mode(cudaStream_t s, const Args &
 } // namespace
 } // namespace gptoss
 
-extern "C" int gptoss_qkv_bias_rope(gptoss_stream_t stream, int T, const void *qkv_in,
-                                    gptoss_dtype_t in_dtype, long in_row_stride,
-                                    const float *bias, const int *pos, int pos_scalar,
-                                    const float *cos_tab, const float *sin_tab, int n_pos,
-                                    int n_q_heads, int n_kv_heads, int head_dim, void *qkv_out,
-                                    gptoss_dtype_t out_dtype, long out_row_stride,
-                                    unsigned flags) {
-  using namespace gptoss;
+namespace gptoss {
+namespace {
+
+int run_bias_rope(gptoss_stream_t stream, int T, const void *qkv_in, gptoss_dtype_t in_dtype, long in_row_stride,
+                  const float *bias, const int *pos, int pos_scalar, const float *cos_tab, const float *sin_tab,
+                  int n_pos, int n_q_heads, int n_kv_heads, int head_dim, void *qkv_out, gptoss_dtype_t out_dtype,
+                  long out_row_stride, const Cache &cache, unsigned flags) {
   const PdlScope pdl(flags);
   if (T < 0 || n_q_heads < 0 || n_kv_heads < 0 || n_q_heads + n_kv_heads <= 0 || head_dim <= 0 ||
       head_dim % 2 != 0 || n_pos <= 0 || !valid_dtype(in_dtype) || !valid_dtype(out_dtype))
@@ -277,12 +355,56 @@ extern "C" int gptoss_qkv_bias_rope(gptoss_stream_t stream, int T, const void *q
   // In place only with identical layout: a thread overwrites exactly what it read.
   if (qkv_in == qkv_out && (in_dtype != out_dtype || in_row_stride != out_row_stride))
     return GPTOSS_ERR_BAD_ARG;
-  const Args a{qkv_in, in_row_stride, bias,      pos,        pos_scalar,     cos_tab, sin_tab,
-               n_pos,  n_q_heads,     n_kv_heads, head_dim,   qkv_out,        out_row_stride, T};
+  const Args a{qkv_in, in_row_stride, bias,       pos,      pos_scalar, cos_tab,        sin_tab, n_pos,
+               n_q_heads, n_kv_heads, head_dim, qkv_out,  out_row_stride, T,     cache};
   cudaStream_t s = as_stream(stream);
   if (in_dtype == GPTOSS_F32)
     return out_dtype == GPTOSS_F32 ? launch_mode<float, float>(s, a, flags)
                                    : launch_mode<float, uint16_t>(s, a, flags);
   return out_dtype == GPTOSS_F32 ? launch_mode<uint16_t, float>(s, a, flags)
                                  : launch_mode<uint16_t, uint16_t>(s, a, flags);
+}
+
+} // namespace
+} // namespace gptoss
+
+extern "C" int gptoss_qkv_bias_rope(gptoss_stream_t stream, int T, const void *qkv_in,
+                                    gptoss_dtype_t in_dtype, long in_row_stride,
+                                    const float *bias, const int *pos, int pos_scalar,
+                                    const float *cos_tab, const float *sin_tab, int n_pos,
+                                    int n_q_heads, int n_kv_heads, int head_dim, void *qkv_out,
+                                    gptoss_dtype_t out_dtype, long out_row_stride,
+                                    unsigned flags) {
+  const gptoss::Cache none = {};
+  return gptoss::run_bias_rope(stream, T, qkv_in, in_dtype, in_row_stride, bias, pos, pos_scalar, cos_tab, sin_tab,
+                               n_pos, n_q_heads, n_kv_heads, head_dim, qkv_out, out_dtype, out_row_stride, none,
+                               flags);
+}
+
+extern "C" int gptoss_qkv_bias_rope_kv(gptoss_stream_t stream, int T, const void *qkv_in,
+                                       gptoss_dtype_t in_dtype, long in_row_stride, const float *bias,
+                                       const int *pos, int pos_scalar, const float *cos_tab,
+                                       const float *sin_tab, int n_pos, int n_q_heads, int n_kv_heads,
+                                       int head_dim, void *qkv_out, gptoss_dtype_t out_dtype,
+                                       long out_row_stride, uint16_t *kc, int8_t *vq, float *vs, int slots,
+                                       const int *slot_of_row, int slot_scalar, unsigned flags) {
+  if (n_kv_heads <= 0 || slots <= 0)
+    return GPTOSS_ERR_BAD_ARG;
+  if (head_dim != 64 || slots % 64 != 0)
+    return GPTOSS_ERR_UNSUPPORTED; // the chunk64 layouts are defined for 64-wide heads and whole chunks
+  if (T > 0 && (!kc || !vq || !vs))
+    return GPTOSS_ERR_BAD_ARG;
+  const gptoss::Cache cache = {kc, vq, vs, slots, slot_of_row, slot_scalar, n_q_heads, n_kv_heads};
+  int st = gptoss::run_bias_rope(stream, T, qkv_in, in_dtype, in_row_stride, bias, pos, pos_scalar, cos_tab,
+                                 sin_tab, n_pos, n_q_heads, n_kv_heads, head_dim, qkv_out, out_dtype,
+                                 out_row_stride, cache, flags);
+  if (st != GPTOSS_ERR_UNSUPPORTED)
+    return st;
+  // a shape or alignment the fused kernel does not take: the two separate launches
+  st = gptoss_qkv_bias_rope(stream, T, qkv_in, in_dtype, in_row_stride, bias, pos, pos_scalar, cos_tab, sin_tab,
+                            n_pos, n_q_heads, n_kv_heads, head_dim, qkv_out, out_dtype, out_row_stride, flags);
+  if (st != GPTOSS_OK)
+    return st;
+  return gptoss_kv_cache_write(stream, T, qkv_out, out_dtype, out_row_stride, n_q_heads, n_kv_heads, head_dim, kc,
+                               vq, vs, slots, slot_of_row, slot_scalar, flags);
 }

@@ -683,3 +683,92 @@ def test_kv_cache_write(gpu, orc, T, nq, nkv, slots, dt):
     at = ((b * slots + (s_ & ~63)) * kv_dim + g * 4096 + (s_ & 63) * 64) // 64
     v = qkv[b, (nq + nkv + g) * 64:(nq + nkv + g + 1) * 64]
     assert got_s[at] == np.float32(np.abs(v).max()) / np.float32(127.0)
+
+
+@pytest.mark.parametrize("T,nq,nkv,slots", [(37, 64, 8, 1024), (600, 64, 8, 128), (5, 8, 1, 64), (1, 0, 4, 64)])
+@pytest.mark.parametrize("mode", ["exact", "exact_fma", "fast"])
+def test_bias_rope_with_cache_write_equals_the_two_launches(gpu, orc, T, nq, nkv, slots, mode):
+    """gptoss_qkv_bias_rope_kv with fp32 rows: qkv, keys, value codes and scales are the bits
+    that gptoss_qkv_bias_rope followed by gptoss_kv_cache_write give (and, in fp32 mode, the
+    oracle's)."""
+    pkg, d = gpu, Dev(gpu)
+    flags = {"exact": pkg.EXACT, "exact_fma": pkg.EXACT | pkg.FMA, "fast": 0}[mode]
+    r = rng_of("ropekv", T, nq, nkv, slots)
+    row, n_pos, kv_dim = (nq + 2 * nkv) * 64, 4096, nkv * 64
+    qkv = (r.standard_normal((T, row)) * 2).astype(np.float32)
+    qkv[0, (nq + nkv) * 64:(nq + nkv + 1) * 64] = 0.0  # an all-zero value vector
+    bias = (0.02 * r.standard_normal(row)).astype(np.float32)
+    bias[(nq + nkv) * 64:(nq + nkv + 1) * 64] = 0.0
+    pos = r.integers(0, n_pos, T).astype(np.int32)
+    slot = r.integers(0, slots, T).astype(np.int32)
+    if T > 2:
+        slot[T // 2] = -1  # no place in the cache
+    ct, st = pkg.build_rope_tables(n_pos, head_dim=64)
+    cb, sb, bb, pb, sl = d.put(ct), d.put(st), d.put(bias), d.put(pos), d.put(slot)
+    n_k = T * slots * kv_dim
+    fill = (np.full(n_k, 0x5555, np.uint16), np.full(n_k, 0x55, np.int8), np.full(n_k // 64, np.float32(7.5), np.float32))
+    k1, q1, s1 = (d.put_inout(a) for a in fill)
+    o1 = d.out((T, row), pkg.F32)
+    pkg.qkv_bias_rope_kv(T, d.put(qkv), pkg.F32, row, bb, pb, 0, cb, sb, n_pos, nq, nkv, 64, o1, pkg.F32, row,
+                         k1, q1, s1, slots, slot_of_row=sl, flags=flags)
+    k2, q2, s2 = (d.put_inout(a) for a in fill)
+    o2 = d.out((T, row), pkg.F32)
+    pkg.qkv_bias_rope(T, d.put(qkv), pkg.F32, row, bb, pb, 0, cb, sb, n_pos, nq, nkv, 64, o2, pkg.F32, row, flags=flags)
+    pkg.kv_cache_write(T, o2, pkg.F32, row, nq, nkv, 64, k2, q2, s2, slots, slot_of_row=sl)
+    assert n_bit_diff(o1.get(), o2.get()) == 0
+    assert np.array_equal(k1.get(as_f32=False), k2.get(as_f32=False))
+    assert np.array_equal(q1.get(), q2.get())
+    assert n_bit_diff(s1.get(), s2.get()) == 0
+    if mode == "exact":
+        rotated = orc.bias_rope_rows_table(qkv, bias, pos, ct, st, nq, nkv, 64)
+        want = [a.copy() for a in fill]
+        orc.kv_cache_write(rotated, nq, nkv, want[0], want[1], want[2], slots, slot)
+        assert np.array_equal(k1.get(as_f32=False), want[0]) and np.array_equal(q1.get(), want[1])
+        assert n_bit_diff(s1.get(), want[2]) == 0
+    # in place with one slot and one position for the whole batch: the engine's call shape
+    k3, q3, s3 = (d.put_inout(a) for a in fill)
+    qb = d.put_inout(qkv)
+    pkg.qkv_bias_rope_kv(T, qb, pkg.F32, row, None, None, 77, cb, sb, n_pos, nq, nkv, 64, qb, pkg.F32, row,
+                         k3, q3, s3, slots, slot_scalar=slots - 1, flags=flags)
+    k4, q4, s4 = (d.put_inout(a) for a in fill)
+    pkg.kv_cache_write(T, qb, pkg.F32, row, nq, nkv, 64, k4, q4, s4, slots, slot_scalar=slots - 1)
+    assert np.array_equal(k3.get(as_f32=False), k4.get(as_f32=False)) and np.array_equal(q3.get(), q4.get())
+    assert n_bit_diff(s3.get(), s4.get()) == 0
+
+
+def test_bias_rope_with_cache_write_bf16_rows(gpu, orc):
+    """bf16 rows in and out: the caches are filled from the fp32 values before they are rounded
+    for qkv_out (the reference's order), so keys agree with the oracle's to a bf16 rounding
+    and codes to one step."""
+    pkg, d = gpu, Dev(gpu)
+    T, nq, nkv, slots = 130, 64, 8, 128
+    r = rng_of("ropekv16")
+    row, n_pos, kv_dim = (nq + 2 * nkv) * 64, 4096, nkv * 64
+    qkv = widen(pkg, r.standard_normal((T, row)) * 2, pkg.BF16).reshape(T, row)
+    bias = (0.02 * r.standard_normal(row)).astype(np.float32)
+    pos = r.integers(0, n_pos, T).astype(np.int32)
+    slot = r.integers(0, slots, T).astype(np.int32)
+    ct, st = pkg.build_rope_tables(n_pos, head_dim=64)
+    n_k = T * slots * kv_dim
+    kc, vq, vs = d.put_inout(np.zeros(n_k, np.uint16)), d.put_inout(np.zeros(n_k, np.int8)), \
+        d.put_inout(np.zeros(n_k // 64, np.float32))
+    o = d.out((T, row), pkg.BF16)
+    pkg.qkv_bias_rope_kv(T, d.put(qkv, pkg.BF16), pkg.BF16, row, d.put(bias), d.put(pos), 0, d.put(ct), d.put(st),
+                         n_pos, nq, nkv, 64, o, pkg.BF16, row, kc, vq, vs, slots, slot_of_row=d.put(slot))
+    rotated = orc.bias_rope_rows_table(qkv, bias, pos, ct, st, nq, nkv, 64)
+    assert rel_err(o.get(), rotated) <= TOL_BF16
+    want = [np.zeros(n_k, np.uint16), np.zeros(n_k, np.int8), np.zeros(n_k // 64, np.float32)]
+    orc.kv_cache_write(rotated, nq, nkv, want[0], want[1], want[2], slots, slot)
+    assert rel_err(pkg.from_bf16_bits(kc.get(as_f32=False)), pkg.from_bf16_bits(want[0])) <= TOL_BF16
+    assert np.abs(vq.get().astype(np.int32) - want[1].astype(np.int32)).max() <= 1
+    assert rel_err(vs.get(), want[2]) <= 1e-5
+
+
+def test_bias_rope_with_cache_write_other_shapes(gpu):
+    pkg, d = gpu, Dev(gpu)
+    z = d.put(np.zeros(64 * 64, np.float32))
+    args = lambda hd, slots: (None, 1, z.ptr, pkg.F32, 4 * hd, None, None, 0, z.ptr, z.ptr, 1, 2, 1, hd, z.ptr, pkg.F32,
+                              4 * hd, z.ptr, z.ptr, z.ptr, slots, None, 0, 0)
+    assert pkg.load().gptoss_qkv_bias_rope_kv(*args(128, 64)) == pkg.ERR_UNSUPPORTED
+    assert pkg.load().gptoss_qkv_bias_rope_kv(*args(64, 100)) == pkg.ERR_UNSUPPORTED
+    assert pkg.load().gptoss_qkv_bias_rope_kv(*args(64, 0)) == pkg.ERR_BAD_ARG
