@@ -521,7 +521,8 @@ def test_golden_vectors_through_the_gpu(gpu, golden):
 @pytest.mark.parametrize("T,k,E,e_begin,e_count", [(512, 4, 32, 0, 32), (512, 4, 128, 0, 64), (512, 4, 128, 64, 64),
                                                    (1024, 4, 128, 0, 128), (3, 4, 32, 0, 32), (1, 4, 32, 0, 32),
                                                    (511, 3, 32, 0, 32), (4096, 4, 32, 0, 32), (16384, 4, 128, 0, 128),
-                                                   (77, 8, 200, 10, 150)])
+                                                   (77, 8, 200, 10, 150), (2047, 4, 32, 0, 32), (8193, 4, 32, 8, 16),
+                                                   (20000, 4, 32, 0, 32)])
 def test_moe_group(gpu, orc, T, k, E, e_begin, e_count):
     pkg, d = gpu, Dev(gpu)
     r = rng_of("group", T, k, E, e_begin)
@@ -545,6 +546,12 @@ def test_moe_group(gpu, orc, T, k, E, e_begin, e_count):
     got_own = own.get()
     assert np.array_equal(got_own[want_rp], np.arange(want_rp.size))
     assert (got_own[np.setdiff1d(np.arange(n), local)] == -1).all()
+    # expert ids at an address that is not a multiple of 16 bytes: the same answer
+    shifted = d.put(np.concatenate([np.zeros(1, np.int32), e.ravel()]))
+    rp2, own2 = d.out((n,), np.int32), d.out((n,), np.int32)
+    pkg.check(pkg.load().gptoss_moe_group(None, shifted.ptr + 4, n, e_begin, e_count, counts.ptr, off.ptr, rp2.ptr,
+                                          own2.ptr, 0))
+    assert np.array_equal(rp2.get()[:want_off[-1]], want_rp) and np.array_equal(own2.get(), want_own)
 
 
 @pytest.mark.parametrize("dt", ["bf16", "f32"])
