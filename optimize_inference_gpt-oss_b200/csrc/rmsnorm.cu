@@ -1,8 +1,9 @@
 // Residual add fused with RMSNorm (gptoss_add_rmsnorm).
 //
 // HBM-bound: per row the kernel must read x (4H bytes) and y (aH), and write x
-// (4H) and out (aH).  One thread block works on one row at a time and walks
-// the rows with a grid stride.  Rows are staged through a ring of shared-memory
+// (4H) and out (aH).  Rows of up to 4096 elements take the loop-free form
+// (add_rmsnorm_tile, one row per block, further down); wider rows the ring described
+// here: one thread block works on one row at a time and walks the rows with a grid stride.  Rows are staged through a ring of shared-memory
 // buffers filled by cp.async: while a block normalises row r, the copies of the
 // next STAGES-1 rows of its walk are already in flight, so an SM keeps 100-200
 // KB of reads outstanding regardless of register pressure.  A thread owns NC
@@ -159,6 +160,111 @@ __global__ void add_rmsnorm_rows(float *x, const YT *__restrict__ y, const float
     stage = stage + 1 == STAGES ? 0 : stage + 1;
   }
   cp_async_wait<0>();
+}
+
+// The loop-free form of add_rmsnorm_rows for H <= 4096: a block owns R consecutive rows, asks
+// for all of them at once (x and the delta, cp.async into shared memory), normalises them
+// with one barrier and exits; the hardware scheduler keeps the SMs stocked with fresh
+// blocks.  Same chunk-to-thread mapping and summation order as the ring with one chunk
+// per thread, hence the same bits.
+template <typename YT, typename OT, bool EXACT, int R>
+__global__ void add_rmsnorm_tile(float *x, const YT *__restrict__ y, const float *__restrict__ w, OT *out,
+                                 int T, int H) {
+  pdl_prologue();
+  constexpr bool HAS_Y = !std::is_same<YT, NoY>::value;
+  constexpr int SY = YSize<YT>::value;
+  using Acc = typename std::conditional<EXACT, double, float>::type;
+  extern __shared__ __align__(16) unsigned char rows[]; // R x (x row, delta row)
+  __shared__ Acc scratch[R][32];
+  const int chunk = threadIdx.x;
+  const bool has = chunk < (H >> 3);
+  const long row0 = (long)blockIdx.x * R;
+  const size_t row_bytes = (size_t)H * (4 + SY);
+
+#pragma unroll
+  for (int r = 0; r < R; r++)
+    if (has && row0 + r < T) {
+      unsigned char *sx = rows + r * row_bytes;
+      const float *xr = x + (size_t)(row0 + r) * H + (size_t)chunk * 8;
+      cp_async16(sx + (size_t)chunk * 32, xr);
+      cp_async16(sx + (size_t)chunk * 32 + 16, xr + 4);
+      if constexpr (HAS_Y) {
+        unsigned char *sy = sx + (size_t)H * 4 + (size_t)chunk * 8 * SY;
+        const YT *yr = y + (size_t)(row0 + r) * H + (size_t)chunk * 8;
+        cp_async16(sy, yr);
+        if constexpr (SY == 4)
+          cp_async16(sy + 16, yr + 4);
+      }
+    }
+  cp_async_commit();
+  Vec8 ws;
+  if (has)
+    ws = load8<kTable>(w, (size_t)chunk * 8);
+  cp_async_wait<0>(); // a thread reads back only what it copied itself: no barrier needed
+
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = (blockDim.x + 31) >> 5;
+  Vec8 xs[R];
+#pragma unroll
+  for (int r = 0; r < R; r++) {
+    Acc ss = 0;
+    if (has && row0 + r < T) {
+      const unsigned char *sx = rows + r * row_bytes;
+      const uint4 a = *reinterpret_cast<const uint4 *>(sx + (size_t)chunk * 32);
+      const uint4 b = *reinterpret_cast<const uint4 *>(sx + (size_t)chunk * 32 + 16);
+      xs[r].v[0] = __uint_as_float(a.x), xs[r].v[1] = __uint_as_float(a.y), xs[r].v[2] = __uint_as_float(a.z),
+      xs[r].v[3] = __uint_as_float(a.w), xs[r].v[4] = __uint_as_float(b.x), xs[r].v[5] = __uint_as_float(b.y),
+      xs[r].v[6] = __uint_as_float(b.z), xs[r].v[7] = __uint_as_float(b.w);
+      if constexpr (HAS_Y) {
+        const unsigned char *sy = sx + (size_t)H * 4 + (size_t)chunk * 8 * SY;
+        Vec8 ys;
+        if constexpr (SY == 2) {
+          ys = widen8(*reinterpret_cast<const uint4 *>(sy));
+        } else {
+          const uint4 p = *reinterpret_cast<const uint4 *>(sy), q = *reinterpret_cast<const uint4 *>(sy + 16);
+          ys.v[0] = __uint_as_float(p.x), ys.v[1] = __uint_as_float(p.y), ys.v[2] = __uint_as_float(p.z),
+          ys.v[3] = __uint_as_float(p.w), ys.v[4] = __uint_as_float(q.x), ys.v[5] = __uint_as_float(q.y),
+          ys.v[6] = __uint_as_float(q.z), ys.v[7] = __uint_as_float(q.w);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+          xs[r].v[i] = __fadd_rn(xs[r].v[i], ys.v[i]);
+      }
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        if constexpr (EXACT)
+          ss = __dadd_rn(ss, (double)__fmul_rn(xs[r].v[i], xs[r].v[i]));
+        else
+          ss = fmaf(xs[r].v[i], xs[r].v[i], ss);
+      }
+    }
+    ss = warp_sum(ss);
+    if (lane == 0)
+      scratch[r][warp] = ss;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int r = 0; r < R; r++) {
+    Acc t = lane < n_warps ? scratch[r][lane] : Acc(0);
+    t = warp_sum(t); // every lane takes part, also those without a chunk
+    if (!has || row0 + r >= T)
+      continue;
+    const size_t e = (size_t)chunk * 8;
+    if constexpr (HAS_Y)
+      store8(x + (size_t)(row0 + r) * H, e, xs[r], false);
+    Vec8 o;
+    if constexpr (EXACT) {
+      const double inv = exact_inv_rms(t, H);
+#pragma unroll
+      for (int i = 0; i < 8; i++)
+        o.v[i] = (float)__dmul_rn((double)ws.v[i], __dmul_rn(inv, (double)xs[r].v[i]));
+    } else {
+      const float inv = fast_inv_rms(t, H);
+#pragma unroll
+      for (int i = 0; i < 8; i++)
+        o.v[i] = __fmul_rn(ws.v[i], __fmul_rn(inv, xs[r].v[i]));
+    }
+    store8(out + (size_t)(row0 + r) * H, e, o);
+  }
 }
 
 // Embedding gather fused with the norm that follows it (gptoss_embed_rmsnorm): the same
@@ -462,11 +568,16 @@ int launch(cudaStream_t s, int T, float *x, const void *y, const float *w, void 
     const int threads = ((n_chunks + nc - 1) / nc + 31) / 32 * 32;
     const size_t smem = stage_bytes * stages;
     int st = GPTOSS_ERR_UNSUPPORTED;
+    if (nc == 1) { // H <= 4096: one row per block, no loop (measured against 2 and 4 rows per block and the ring)
+      auto k = add_rmsnorm_tile<YT, OT, EXACT, 1>;
+      if (blocks_per_sm_smem(k, threads, stage_bytes) >= 1) {
+        launch_kernel(k, dim3((unsigned)T), dim3(threads), stage_bytes, s, x, yp, w, op, T, H);
+        return launch_status();
+      }
+    }
 #define GPTOSS_NORM_CASE(NC_, ST_)                                                                \
   if (nc == NC_ && stages == ST_)                                                                 \
   st = launch_pipe<YT, OT, EXACT, NC_, ST_>(s, T, x, yp, w, op, H, threads, smem)
-    GPTOSS_NORM_CASE(1, 4);
-    GPTOSS_NORM_CASE(1, 3);
     GPTOSS_NORM_CASE(2, 4);
     GPTOSS_NORM_CASE(2, 3);
     GPTOSS_NORM_CASE(2, 2);
