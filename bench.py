@@ -55,7 +55,7 @@ def parse_args():
     ap.add_argument("--standin-sets", type=int, default=0, help="distinct per-layer input sets (0 = one per layer)")
     ap.add_argument("--seed", type=int, default=1)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--cpu-seconds", type=float, default=8.0, help="minimum CPU time of the baseline sample")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0, help="minimum CPU time of the baseline sample")
     ap.add_argument("--profile-steps", type=int, default=10)
     ap.add_argument("--ncu-steps", type=int, default=0,
                     help="profiler mode: build the chain, run this many steps kernel by kernel, exit (no timing)")
