@@ -221,91 +221,6 @@ __global__ void bias_rope_rows(const IT *qkv_in, long in_stride, const float *__
   cp_async_wait<0>();
 }
 
-// The loop-free form: a block owns R consecutive rows, asks for all of them (and their
-// cos/sin rows, one copy per warp) at once, rotates them and exits.
-template <typename IT, typename OT, bool EXACT, bool FMA, int R>
-__global__ void bias_rope_tile(const IT *qkv_in, long in_stride, const float *__restrict__ bias,
-                               const int *__restrict__ pos, int pos_scalar,
-                               const float *__restrict__ cos_tab,
-                               const float *__restrict__ sin_tab, int n_pos, int n_rot_heads,
-                               int n_heads, int head_dim, OT *qkv_out, long out_stride, int T) {
-  pdl_prologue();
-  constexpr int SI = sizeof(IT);
-  extern __shared__ __align__(16) unsigned char tile[];
-  const int half = head_dim >> 1, pieces = half >> 3, items = n_heads * pieces;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
-  const size_t row_bytes = (size_t)n_heads * head_dim * SI;
-  const size_t trig_bytes = (size_t)half * 8; // cos + sin of one position
-  const size_t slot_bytes = row_bytes + (size_t)n_warps * trig_bytes;
-  const bool active = (int)threadIdx.x < items;
-  const int head = active ? threadIdx.x / pieces : 0, piece = active ? threadIdx.x - head * pieces : 0;
-  const size_t lo = (size_t)head * head_dim + piece * 8, hi = lo + half;
-  const bool rotates = head < n_rot_heads;
-  const long row0 = (long)blockIdx.x * R;
-
-  int p[R];
-#pragma unroll
-  for (int r = 0; r < R; r++) {
-    int v = (pos && row0 + r < T) ? __ldg(pos + row0 + r) : pos_scalar;
-    p[r] = v < 0 ? 0 : (v >= n_pos ? n_pos - 1 : v);
-  }
-#pragma unroll
-  for (int r = 0; r < R; r++) {
-    if (row0 + r >= T)
-      break;
-    unsigned char *sr = tile + (size_t)r * slot_bytes;
-    if (active) {
-      const IT *in = qkv_in + (size_t)(row0 + r) * in_stride;
-      cp_async16(sr + lo * SI, in + lo);
-      cp_async16(sr + hi * SI, in + hi);
-      if constexpr (SI == 4) {
-        cp_async16(sr + lo * SI + 16, in + lo + 4);
-        cp_async16(sr + hi * SI + 16, in + hi + 4);
-      }
-    }
-    unsigned char *st = sr + row_bytes + (size_t)warp * trig_bytes;
-    const int per_table = half >> 2;
-    for (int q = lane; q < 2 * per_table; q += 32) {
-      const float *src = q < per_table ? cos_tab + (size_t)p[r] * half + q * 4
-                                       : sin_tab + (size_t)p[r] * half + (q - per_table) * 4;
-      cp_async16_cached(st + (size_t)q * 16, src);
-    }
-  }
-  cp_async_commit();
-  Vec8 ba, bb;
-  if (bias && active) {
-    ba = load8<kTable>(bias, lo);
-    bb = load8<kTable>(bias, hi);
-  }
-  cp_async_wait<0>();
-  __syncwarp(); // the cos/sin pieces were copied by other lanes of this warp
-  if (!active)
-    return;
-#pragma unroll
-  for (int r = 0; r < R; r++) {
-    if (row0 + r >= T)
-      break;
-    const unsigned char *sr = tile + (size_t)r * slot_bytes;
-    Vec8 a = smem_load8<IT>(sr + lo * SI), b = smem_load8<IT>(sr + hi * SI);
-    if (bias) {
-#pragma unroll
-      for (int i = 0; i < 8; i++) {
-        a.v[i] = __fadd_rn(a.v[i], ba.v[i]);
-        b.v[i] = __fadd_rn(b.v[i], bb.v[i]);
-      }
-    }
-    if (rotates) {
-      const unsigned char *st = sr + row_bytes + (size_t)warp * trig_bytes;
-      const Vec8 c = smem_load8<float>(st + (size_t)piece * 32);
-      const Vec8 s = smem_load8<float>(st + (size_t)half * 4 + (size_t)piece * 32);
-      rotate8<EXACT, FMA>(a, b, c, s);
-    }
-    OT *out = qkv_out + (size_t)(row0 + r) * out_stride;
-    store8(out, lo, a);
-    store8(out, hi, b);
-  }
-}
-
 // Any head_dim (even) and alignment: one rotation pair per thread step.
 template <typename IT, typename OT, bool EXACT, bool FMA>
 __global__ void bias_rope_rows_generic(const IT *qkv_in, long in_stride,
@@ -388,19 +303,6 @@ template <typename IT, typename OT, bool EXACT, bool FMA> int launch(cudaStream_
                                (size_t)(threads / 32) * (size_t)a.head_dim * 4;
     const int stages = pick_stages(stage_bytes);
     int st = GPTOSS_ERR_UNSUPPORTED;
-#ifdef GPTOSS_ROPE_TILE
-    if (!a.cache.kc) {
-      auto k = bias_rope_tile<IT, OT, EXACT, FMA, GPTOSS_ROPE_TILE>;
-      const size_t smem = stage_bytes * GPTOSS_ROPE_TILE;
-      if (blocks_per_sm_smem(k, threads, smem) >= 1) {
-        launch_kernel(k, dim3((unsigned)((a.T + GPTOSS_ROPE_TILE - 1) / GPTOSS_ROPE_TILE)), dim3(threads), smem, s,
-                      static_cast<const IT *>(a.in), a.in_stride, a.bias, a.pos, a.pos_scalar, a.cos_tab, a.sin_tab,
-                      a.n_pos, a.n_q + a.n_kv, a.n_q + 2 * a.n_kv, a.head_dim, static_cast<OT *>(a.out),
-                      a.out_stride, a.T);
-        return launch_status();
-      }
-    }
-#endif
     if (a.cache.kc) { // with the cache write: the model's shape class only (64-wide heads, a 4-deep ring)
       if (stages == 4 && a.head_dim == 64)
         st = launch_pipe<IT, OT, EXACT, FMA, 4, true>(s, a, threads, stage_bytes * 4);
