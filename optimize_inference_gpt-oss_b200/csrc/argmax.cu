@@ -256,6 +256,7 @@ extern "C" int gptoss_argmax_slices(int T, long V, gptoss_dtype_t logits_dtype, 
 
 // ---- greedy argmax for callers that cannot allocate device memory ---------------------
 #include <stdio.h>
+#include <atomic>
 //
 // gptoss_argmax needs one 64-bit merge word per row from its caller.  Some hosts
 // of this library have no way to provide that: a plug-in running inside a serving
@@ -274,7 +275,9 @@ namespace {
 // use, so the address is asked for once per device (with that device current)
 // and remembered.  Returns nullptr and sets *status on failure.
 unsigned long long *noalloc_keys_on_current_device(int *status) {
-  static unsigned long long *address_of[64] = {nullptr};
+  // two threads asking at once both get the same answer from the runtime; the atomic only
+  // makes the publication of the pointer well defined
+  static std::atomic<unsigned long long *> address_of[64];
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) {
@@ -286,7 +289,7 @@ unsigned long long *noalloc_keys_on_current_device(int *status) {
     *status = GPTOSS_ERR_UNSUPPORTED;
     return nullptr;
   }
-  if (!address_of[dev]) {
+  if (!address_of[dev].load(std::memory_order_acquire)) {
     void *p = nullptr;
     e = cudaGetSymbolAddress(&p, g_noalloc_keys);
     if (e != cudaSuccess || !p) {
@@ -295,9 +298,9 @@ unsigned long long *noalloc_keys_on_current_device(int *status) {
       *status = GPTOSS_ERR_CUDA;
       return nullptr;
     }
-    address_of[dev] = static_cast<unsigned long long *>(p);
+    address_of[dev].store(static_cast<unsigned long long *>(p), std::memory_order_release);
   }
-  return address_of[dev];
+  return address_of[dev].load(std::memory_order_acquire);
 }
 
 } // namespace

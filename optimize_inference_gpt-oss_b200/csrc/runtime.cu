@@ -47,8 +47,18 @@ int occupancy_cached(const void *kernel, int threads, size_t smem) {
         return table[i].blocks;
   }
   int blocks = 0;
+  // Above the 48 KB default the kernel's limit is raised to all the device offers, not to this
+  // request: the attribute belongs to the kernel, and a later, smaller request must not lower
+  // it under the feet of a configuration that is already in this table.
+  // (The limit covers static and dynamic shared memory together, so the dynamic part that can be
+  // asked for is the device's figure less the kernel's static arrays.)
+  int optin = 0;
+  cudaFuncAttributes fa = {};
   if (smem > 48 * 1024 &&
-      cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+      (cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess ||
+       cudaFuncGetAttributes(&fa, kernel) != cudaSuccess || smem + fa.sharedSizeBytes > (size_t)optin ||
+       cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                            optin - (int)fa.sharedSizeBytes) != cudaSuccess)) {
     (void)cudaGetLastError();
     blocks = 0;
   } else if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, kernel, threads, smem) != cudaSuccess) {

@@ -779,3 +779,21 @@ def test_bias_rope_with_cache_write_other_shapes(gpu):
     assert pkg.load().gptoss_qkv_bias_rope_kv(*args(128, 64)) == pkg.ERR_UNSUPPORTED
     assert pkg.load().gptoss_qkv_bias_rope_kv(*args(64, 100)) == pkg.ERR_UNSUPPORTED
     assert pkg.load().gptoss_qkv_bias_rope_kv(*args(64, 0)) == pkg.ERR_BAD_ARG
+
+
+def test_shared_memory_limit_survives_mixed_shapes(gpu):
+    """A kernel's dynamic shared-memory limit is raised once to what the device offers: a
+    launch that needs less must not lower it for a configuration used before (wide rows,
+    then the model's rows, then wide rows again)."""
+    pkg, d = gpu, Dev(gpu)
+    T, k = 64, 4
+    for Hd in (4096, 2880, 4096, 1024, 4096):
+        x = d.put_inout(np.ones((T, Hd), np.float32))
+        Z = d.put(np.ones((T * k, Hd), np.float32), pkg.BF16)
+        w = d.put(np.full((T, k), 0.25, np.float32))
+        e = d.put(np.tile(np.arange(k, dtype=np.int32), (T, 1)))
+        g = d.put(np.ones(Hd, np.float32))
+        o = d.out((T, Hd), pkg.BF16)
+        pkg.moe_combine(T, x, Z, pkg.BF16, None, w, e, k, Hd, None, g, o, pkg.BF16)
+        pkg.synchronize()
+        assert np.allclose(x.get(), 2.0) and np.allclose(o.get(), 1.0, atol=1e-2)
