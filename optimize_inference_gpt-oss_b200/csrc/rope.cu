@@ -7,10 +7,10 @@
 // further on -- the two halves of eight rotation pairs -- so its slice of the
 // bias lives in registers, every access is 128 bits wide, and no thread needs
 // another thread's row data.  Value heads use the same items and skip the
-// rotation.  Rows are staged through a ring of shared-memory buffers filled by
-// cp.async several rows ahead (an SM keeps ~200 KB of reads outstanding); the
-// cos/sin row of each staged token travels with it, one copy per warp, so the
-// arithmetic of a row waits on nothing but its own stage.
+// rotation.  Rows are staged through a ring of two shared-memory buffers filled by
+// cp.async (the next row of the block's walk is in flight while this one is
+// rotated; three blocks per SM); the cos/sin row of each staged token travels with
+// it, one copy per warp, so the arithmetic of a row waits on nothing but its own stage.
 #include "common.cuh"
 
 namespace gptoss {
@@ -301,21 +301,20 @@ template <typename IT, typename OT, bool EXACT, bool FMA> int launch(cudaStream_
     const int threads = (items + 31) / 32 * 32;
     const size_t stage_bytes = (size_t)n_heads * a.head_dim * sizeof(IT) +
                                (size_t)(threads / 32) * (size_t)a.head_dim * 4;
-    const int stages = pick_stages(stage_bytes);
+    // A ring of two: while a row is rotated the next one of the block's walk is in flight.  Deeper
+    // rings (3 and 4 rows, which fit) measured slower on B200 -- 15.3 against 14.8 us per launch at
+    // 4096 rows -- as did capping registers for a fourth resident block.
     int st = GPTOSS_ERR_UNSUPPORTED;
-    if (a.cache.kc) { // with the cache write: the model's shape class only (64-wide heads, a 4-deep ring)
-      if (stages == 4 && a.head_dim == 64)
-        st = launch_pipe<IT, OT, EXACT, FMA, 4, true>(s, a, threads, stage_bytes * 4);
-      return st;
-    }
-    if (stages == 4)
-      st = launch_pipe<IT, OT, EXACT, FMA, 4, false>(s, a, threads, stage_bytes * 4);
-    else if (stages == 3)
-      st = launch_pipe<IT, OT, EXACT, FMA, 3, false>(s, a, threads, stage_bytes * 3);
-    else if (stages == 2)
+    if (stage_bytes * 2 <= 220 * 1024) {
+      if (a.cache.kc) { // with the cache write: 64-wide heads only
+        if (a.head_dim == 64)
+          st = launch_pipe<IT, OT, EXACT, FMA, 2, true>(s, a, threads, stage_bytes * 2);
+        return st;
+      }
       st = launch_pipe<IT, OT, EXACT, FMA, 2, false>(s, a, threads, stage_bytes * 2);
-    if (st != GPTOSS_ERR_UNSUPPORTED)
-      return st;
+      if (st != GPTOSS_ERR_UNSUPPORTED)
+        return st;
+    }
   }
   if (a.cache.kc)
     return GPTOSS_ERR_UNSUPPORTED; // the caller falls back to the two separate launches
