@@ -419,7 +419,7 @@ def main():
     e2e_value = world * T * args.steps / e2e_s
     # ---- the same steps as one wave with the bookkeeping on the GPU: prompts in before, output rows
     # back after, no per-step round trip (one-token prompts, so every step feeds the picked token back)
-    wave_steps = min(args.steps, 4096)
+    wave_steps = min(4 * args.steps, 1024, c.max_pos)  # a wave is long: its set-up and read-back are paid once
     w_tok = np.ascontiguousarray(tok.array, np.int32)
     w_off = np.arange(T + 1, dtype=np.int32)
     w_out = np.empty((T, wave_steps + 2), np.int32)
