@@ -284,3 +284,28 @@ def test_wave_loop_with_finished_rows(gpu, orc):
         assert (ran, total) == (want[2], want[1]) and np.array_equal(out, want[0])
     finally:
         ch.close()
+
+
+def test_wave_of_4096_requests_host_loop_and_device_loop_agree(gpu):
+    """The benchmark's batch (4096 rows, full depth and vocabulary): the wave served step by
+    step from the host and the wave kept on the GPU return the same token lists and counts."""
+    pkg = gpu
+    c = pkg.chain_config(20, pkg.BF16, max_pos=4096)
+    n, steps = 4096, 6
+    ch = pkg.Chain(c, n, 2)
+    try:
+        ch.fill_synthetic(n, seed=31)
+        logits = ch.download(pkg.BUF_LOGITS, 0, np.uint16, (n, c.vocab))
+        big = pkg.to_bf16_bits(np.array([1000.0], np.float32))[0]
+        logits[::5, 199999] = big  # every fifth request picks an end token
+        ch.upload(pkg.BUF_LOGITS, 0, logits)
+        r = np.random.default_rng(8)
+        prompts = [list(r.integers(0, 199000, 1 + b % 4)) for b in range(n)]
+        a = ch.run_wave(prompts, steps)
+        done_a = ch.download(pkg.BUF_ROW_DONE, 0, np.int32, (n,))
+        b = ch.run_wave(prompts, steps, on_device=True)
+        assert a[1:] == b[1:] and np.array_equal(a[0], b[0])
+        assert np.array_equal(done_a, ch.download(pkg.BUF_ROW_DONE, 0, np.int32, (n,)))
+        assert done_a[::5].all() and not done_a[1::5].any() and a[2] == steps
+    finally:
+        ch.close()

@@ -119,7 +119,47 @@ def test_vocab_embedding_gather_8192_ids(gpu):
     rows = table[ids]
     assert np.array_equal(x16.numpy(np.uint16, (8192, H)), rows)
     assert np.array_equal(x32.numpy(np.uint32, (8192, H)), rows.astype(np.uint32) << 16)
-    for b in (tb, x32, x16, ib):
+    # the gather fused with the first norm, from the same table: the two launches' bits
+    gain = pkg.DeviceBuffer.from_numpy(pkg.synth_normal(H, pkg.F32, 24, 2, 1.0, 0.1))
+    xf, of, o2 = pkg.DeviceBuffer(8192 * H * 4), pkg.DeviceBuffer(8192 * H * 2), pkg.DeviceBuffer(8192 * H * 2)
+    pkg.embed_rmsnorm(8192, tb, pkg.BF16, V, ib, xf, gain, of, pkg.BF16, H)
+    pkg.add_rmsnorm(8192, x32, None, pkg.F32, gain, o2, pkg.BF16, H)
+    assert np.array_equal(xf.numpy(np.uint32, (8192, H)), rows.astype(np.uint32) << 16)
+    assert np.array_equal(of.numpy(np.uint16, (8192, H)), o2.numpy(np.uint16, (8192, H)))
+    for b in (tb, x32, x16, ib, gain, xf, of, o2):
+        b.free()
+
+
+def test_decode_rotation_with_cache_write_4096_rows(gpu):
+    """One decode step of 4096 sequences at the model's head counts, 128 cache slots each:
+    rotation + cache write in one launch against the two launches, fp32 rows, every byte of
+    the 0.8 GB of caches."""
+    pkg = gpu
+    T, nq, nkv, slots, n_pos = 4096, 64, 8, 128, 4096
+    kv_dim = nkv * 64
+    qkv = pkg.synth_normal(T * QKV, pkg.F32, 26, 0).reshape(T, QKV)
+    bias = pkg.synth_normal(QKV, pkg.F32, 26, 1, 0.0, 0.02)
+    pos = pkg.synth_uniform_int(T, 26, 2, 0, n_pos)
+    slot = pkg.synth_uniform_int(T, 26, 3, 0, slots)
+    ct, st = pkg.build_rope_tables(n_pos)
+    dev = lambda a: pkg.DeviceBuffer.from_numpy(np.ascontiguousarray(a))
+    qb, bb, pb, sb, cb, tb = dev(qkv), dev(bias), dev(pos), dev(slot), dev(ct), dev(st)
+    n_k = T * slots * kv_dim
+    caches = [[pkg.DeviceBuffer.filled(n_k * 2, 0x11), pkg.DeviceBuffer.filled(n_k, 0x11),
+               pkg.DeviceBuffer.filled(n_k // 64 * 4, 0x11)] for _ in range(2)]
+    o1, o2 = pkg.DeviceBuffer(T * QKV * 4), pkg.DeviceBuffer(T * QKV * 4)
+    pkg.qkv_bias_rope_kv(T, qb, pkg.F32, QKV, bb, pb, 0, cb, tb, n_pos, nq, nkv, 64, o1, pkg.F32, QKV,
+                         caches[0][0], caches[0][1], caches[0][2], slots, slot_of_row=sb)
+    pkg.qkv_bias_rope(T, qb, pkg.F32, QKV, bb, pb, 0, cb, tb, n_pos, nq, nkv, 64, o2, pkg.F32, QKV)
+    pkg.kv_cache_write(T, o2, pkg.F32, QKV, nq, nkv, 64, caches[1][0], caches[1][1], caches[1][2], slots,
+                       slot_of_row=sb)
+    assert np.array_equal(o1.numpy(np.uint32, T * QKV), o2.numpy(np.uint32, T * QKV))
+    for a, b, dt in zip(caches[0], caches[1], (np.uint16, np.uint8, np.uint32)):
+        got, want = a.numpy(dt, a.nbytes // np.dtype(dt).itemsize), b.numpy(dt, b.nbytes // np.dtype(dt).itemsize)
+        assert np.array_equal(got, want)
+    written = caches[0][0].numpy(np.uint16, n_k) != 0x1111
+    assert T * kv_dim * 0.99 <= written.sum() <= T * kv_dim  # one slot per sequence (a key may happen to equal the fill)
+    for b in [qb, bb, pb, sb, cb, tb, o1, o2] + caches[0] + caches[1]:
         b.free()
 
 
