@@ -462,7 +462,7 @@ def main():
         gbs = b / (us * 1e-6) / 1e9
         kernels[kind] = {"launches_per_step": per_step, "us_per_launch": round(us, 3), "bytes_per_launch": b,
                          "achieved_gbs": round(gbs, 1), "frac": round(gbs / peak, 4),
-                         "share_of_step": None}
+                         "pct_of_nominal_8tbs": round(gbs / 80.0, 1), "share_of_step": None}
         chain_bytes += b * per_step
     tot = sum(k["us_per_launch"] * k["launches_per_step"] for k in kernels.values())
     for k in kernels.values():
@@ -473,7 +473,8 @@ def main():
                 "peak_source": peak_src,
                 "chain": {"bytes_per_step": chain_bytes,
                           "achieved_gbs": round(chain_bytes / (ms_per_step * 1e-3) / 1e9, 1),
-                          "frac": round(chain_bytes / (ms_per_step * 1e-3) / 1e9 / peak, 4)}}
+                          "frac": round(chain_bytes / (ms_per_step * 1e-3) / 1e9 / peak, 4),
+                          "pct_of_nominal_8tbs": round(chain_bytes / (ms_per_step * 1e-3) / 1e9 / 80.0, 1)}}
 
     line = {
         "metric": "layer_chain_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
