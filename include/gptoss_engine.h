@@ -93,7 +93,9 @@ GPTOSS_API int gptoss_synth_uniform_int(int *dst_host, size_t count, uint64_t se
  * [k T, H]; and the logits [T,V]); the chain's own outputs that would feed a
  * GEMM (normalised rows, rotated qkv, SwiGLU rows) are written to scratch.  The
  * residual stream, the routing weights and the picked tokens flow through the
- * chain exactly as in the engine. */
+ * chain exactly as in the engine.  A chain owns one stream and is driven by one
+ * host thread at a time (the engine has one thread per device too,
+ * gpu_engine.hpp:916-945); different chains are independent. */
 typedef struct gptoss_chain gptoss_chain_t;
 
 /* Bit of gptoss_chain_config_t.flags that only the chain reads: open the step with the
