@@ -6,8 +6,8 @@
 // with the norm, one normalised row.  One thread block works on one token at a
 // time and walks the tokens with a grid stride; a token's rows (about 34 KB at
 // H = 2880, k = 4, bf16 experts) are staged through a ring of shared-memory
-// buffers filled by cp.async several tokens ahead, so an SM keeps ~200 KB of
-// reads outstanding.  A thread owns NC chunks of 8 consecutive elements, copies
+// buffers filled by cp.async one or more tokens ahead (two buffers at the model's
+// shape: the next token's rows are in flight while this one is summed).  A thread owns NC chunks of 8 consecutive elements, copies
 // those chunks of all k + 1 rows itself and reads only them back.  The small
 // per-token routing data (row numbers, weights, expert ids) is fetched into
 // registers one iteration before it is needed, so no load sits between a
@@ -369,8 +369,9 @@ int launch_stages(cudaStream_t s, const Args &a, int threads, size_t stage_bytes
 template <typename ZT, typename OT, int MODE, bool NORM> int launch(cudaStream_t s, const Args &a) {
   const size_t stage_bytes = (size_t)a.H * (4 + (size_t)a.k * sizeof(ZT));
   int stages = pick_stages(stage_bytes);
-  // Three blocks with a ring of two beat two blocks with a ring of three where both fill the SM's
-  // shared memory (the model's shape: 34.5 KB stages; measured 32.6 against 34.3 us per launch).
+  // A ring of two beats a ring of three where three stages of two blocks fill the SM's shared
+  // memory (the model's shape: 34.5 KB stages, two blocks per SM by registers either way;
+  // measured 32.6 against 34.3 us per launch): fewer requests outstanding stream better.
   if (stages == 3 && stage_bytes * 2 * 3 <= 220 * 1024)
     stages = 2;
   const bool vec = a.H % 8 == 0 && a.H <= 8 * 512 * 4 && aligned16(a.x) && aligned16(a.Z) && stages > 0 &&
