@@ -90,6 +90,11 @@ GPTOSS_API const char *gptoss_status_string(int status);
 /* The cudaError_t (as int) of the last failed CUDA call made by this thread in
  * this library, 0 if none. */
 GPTOSS_API int gptoss_last_cuda_error(void);
+/* How many launches this thread has made so far that fell back to a scalar kernel
+ * (sizes that are not multiples of 8 elements, bases that are not 16-byte aligned,
+ * rows too wide for the vector kernels).  Results are the same; the speed is not.  A
+ * caller that expects the fast path reads it before and after. */
+GPTOSS_API long gptoss_generic_launch_count(void);
 
 /*
  * Token-embedding gather: x[t,:] = table[ids[t],:].

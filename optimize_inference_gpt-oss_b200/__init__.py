@@ -62,6 +62,7 @@ PROTOTYPES = {
     "gptoss_version": (C.c_char_p, []),
     "gptoss_status_string": (C.c_char_p, [_i]),
     "gptoss_last_cuda_error": (_i, []),
+    "gptoss_generic_launch_count": (_l, []),
     "gptoss_embed": (_i, [_p, _i, _p, _i, _i, _p, _p, _i, _i, _u]),
     "gptoss_embed_rmsnorm": (_i, [_p, _i, _p, _i, _i, _p, _p, _p, _p, _i, _i, _u]),
     "gptoss_add_rmsnorm": (_i, [_p, _i, _p, _p, _i, _p, _p, _i, _i, _u]),

@@ -390,6 +390,7 @@ template <typename ZT, typename OT, int MODE, bool NORM> int launch(cudaStream_t
     if (st != GPTOSS_ERR_UNSUPPORTED)
       return st;
   }
+  note_generic_launch();
   launch_kernel(combine_rows_generic<ZT, OT, MODE, NORM>, dim3(row_grid(a.T, 8)), dim3(256), 0, s, 
       a.x, static_cast<const ZT *>(a.Z), a.own_row, a.topk_w, a.topk_e, a.k, a.H, a.phys_of,
       a.norm_w, static_cast<OT *>(a.out), a.T);

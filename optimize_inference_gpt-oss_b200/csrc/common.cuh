@@ -28,6 +28,10 @@ inline cudaStream_t as_stream(gptoss_stream_t s) { return reinterpret_cast<cudaS
 // scheduled while the previous kernel in the stream is still draining.
 extern thread_local bool tl_pdl;
 extern thread_local cudaError_t tl_launch_error;
+// Launches by this thread that fell to a scalar "generic" kernel (odd sizes, misaligned
+// bases, shapes the vector kernels do not take): see gptoss_generic_launch_count().
+extern thread_local long tl_generic_launches;
+inline void note_generic_launch() { tl_generic_launches++; }
 struct PdlScope {
   bool prev;
   explicit PdlScope(unsigned flags) : prev(tl_pdl) { tl_pdl = (flags & GPTOSS_PDL) != 0; }

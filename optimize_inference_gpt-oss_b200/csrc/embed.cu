@@ -75,6 +75,7 @@ int launch(cudaStream_t s, int T, const void *table, int V, const int *ids, void
   constexpr bool widen = sizeof(TT) != sizeof(OT);
   const size_t row_bytes = (size_t)H * sizeof(TT);
   if (row_bytes % 16 != 0 || !aligned16(table) || !aligned16(x)) {
+    note_generic_launch();
     launch_kernel(embed_rows_generic<TT, OT>, dim3(row_grid(T, 8)), dim3(256), 0, s, 
         static_cast<const TT *>(table), ids, static_cast<OT *>(x), T, H, V, id_div);
     return launch_status();

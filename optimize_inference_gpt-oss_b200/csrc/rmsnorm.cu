@@ -587,6 +587,7 @@ int launch(cudaStream_t s, int T, float *x, const void *y, const float *w, void 
     if (st != GPTOSS_ERR_UNSUPPORTED)
       return st;
   }
+  note_generic_launch();
   launch_kernel(add_rmsnorm_rows_generic<YT, OT, EXACT>, dim3(row_grid(T, 8)), dim3(256), 0, s, x, yp, w, op, T, H);
   return launch_status();
 }

@@ -318,6 +318,7 @@ template <typename IT, typename OT, bool EXACT, bool FMA> int launch(cudaStream_
   }
   if (a.cache.kc)
     return GPTOSS_ERR_UNSUPPORTED; // the caller falls back to the two separate launches
+  note_generic_launch();
   launch_kernel(bias_rope_rows_generic<IT, OT, EXACT, FMA>, dim3(row_grid(a.T, 8)), dim3(256), 0, s, 
       static_cast<const IT *>(a.in), a.in_stride, a.bias, a.pos, a.pos_scalar, a.cos_tab, a.sin_tab,
       a.n_pos, n_rot, n_heads, a.head_dim, static_cast<OT *>(a.out), a.out_stride, a.T);

@@ -8,6 +8,7 @@ namespace gptoss {
 
 static thread_local int g_last_cuda_error = 0;
 thread_local bool tl_pdl = false;
+thread_local long tl_generic_launches = 0;
 thread_local cudaError_t tl_launch_error = cudaSuccess;
 
 void note_cuda_error(cudaError_t e) { g_last_cuda_error = (int)e; }
@@ -74,6 +75,8 @@ int occupancy_cached(const void *kernel, int threads, size_t smem) {
 } // namespace gptoss
 
 extern "C" const char *gptoss_version(void) { return "0.1.0"; }
+
+extern "C" long gptoss_generic_launch_count(void) { return gptoss::tl_generic_launches; }
 
 extern "C" const char *gptoss_status_string(int status) {
   switch (status) {

@@ -112,6 +112,7 @@ int launch(cudaStream_t s, const void *Y, void *G, size_t n_out, float limit) {
   if (done < n_out) {
     const size_t rest = n_out - done;
     const long blocks = (long)((rest + threads - 1) / threads);
+    note_generic_launch();
     launch_kernel(swiglu_scalar<YT, GT, EXACT>, dim3(row_grid(blocks, 8)), dim3(threads), 0, s, yp, gp, done, n_out, limit);
     return launch_status();
   }

@@ -7,7 +7,7 @@ from __future__ import annotations
 import numpy as np
 import pytest
 
-from gpu_util import TOL_BF16, TOL_F32, n_bit_diff, rel_err
+from gpu_util import Dev, TOL_BF16, TOL_F32, n_bit_diff, rel_err
 
 pytestmark = pytest.mark.gpu
 
@@ -309,3 +309,27 @@ def test_wave_of_4096_requests_host_loop_and_device_loop_agree(gpu):
         assert done_a[::5].all() and not done_a[1::5].any() and a[2] == steps
     finally:
         ch.close()
+
+
+def test_model_shapes_take_the_vector_kernels(gpu, orc):
+    """No launch of the chain at the model's shapes falls back to a scalar kernel (fp32 and bf16
+    modes, 20b and 120b router widths); an odd hidden size does, and the counter says so."""
+    pkg = gpu
+    count = pkg.load().gptoss_generic_launch_count
+    for which, dt in ((20, pkg.BF16), (20, pkg.F32), (120, pkg.BF16)):
+        c = pkg.chain_config(which, dt, max_pos=4096)
+        c.n_layers, c.vocab = 2, 8192
+        ch = pkg.Chain(c, 300, 1)
+        try:
+            ch.fill_synthetic(300, seed=5)
+            before = count()
+            ch.enqueue(300, use_graph=False)
+            pkg.synchronize()
+            assert count() == before
+        finally:
+            ch.close()
+    d = Dev(pkg)
+    x, w, o = d.put_inout(np.ones((4, 77), np.float32)), d.put(np.ones(77, np.float32)), d.out((4, 77), pkg.F32)
+    before = count()
+    pkg.add_rmsnorm(4, x, None, pkg.F32, w, o, pkg.F32, 77)
+    assert count() == before + 1
