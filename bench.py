@@ -389,20 +389,33 @@ def main():
         pkg.check(lib.gptoss_event_create(C.byref(e)))
     stream = chain.stream
 
-    sampler = ClockSampler(visible_gpu_index(local_rank)) if rank == 0 else None
+    # ---- value: K graph replays, inputs resident, CUDA events on the launching stream.  Clocks are
+    # sampled during exactly this region; a region that saw a thermal or hardware slowdown is
+    # measured a second time (once) and the second measurement is the one reported.
+    def measure_value():
+        sampler = ClockSampler(visible_gpu_index(local_rank)) if rank == 0 else None
+        if sampler:
+            time.sleep(0.3)  # nvidia-smi needs a moment before its first sample
+        for _ in range(max(3, args.warmup)):
+            chain.enqueue(T, True)
+        barrier()
+        pkg.check(lib.gptoss_event_record(ev[0], stream))
+        for _ in range(args.steps):
+            chain.enqueue(T, True)
+        pkg.check(lib.gptoss_event_record(ev[1], stream))
+        barrier()
+        ms = C.c_float()
+        pkg.check(lib.gptoss_event_elapsed_ms(ev[0], ev[1], C.byref(ms)))
+        return sharding.max_over_ranks(ms.value, dist), (sampler.stop() if sampler else None)
 
-    # ---- value: K graph replays, inputs resident, CUDA events on the launching stream
-    for _ in range(max(3, args.warmup)):
-        chain.enqueue(T, True)
-    barrier()
-    pkg.check(lib.gptoss_event_record(ev[0], stream))
-    for _ in range(args.steps):
-        chain.enqueue(T, True)
-    pkg.check(lib.gptoss_event_record(ev[1], stream))
-    barrier()
-    ms = C.c_float()
-    pkg.check(lib.gptoss_event_elapsed_ms(ev[0], ev[1], C.byref(ms)))
-    ms_total = sharding.max_over_ranks(ms.value, dist)
+    SLOW = {"hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown"}
+    ms_total, clocks = measure_value()
+    slowed = 1.0 if (clocks and SLOW & set(clocks.get("reasons", []))) else 0.0
+    if sharding.max_over_ranks(slowed, dist) > 0:  # rank 0 decides for everybody
+        first = clocks
+        ms_total, clocks = measure_value()
+        if clocks is not None:
+            clocks["remeasured_after"] = first
     ms_per_step = ms_total / args.steps
     value = world * T * args.steps / (ms_total * 1e-3)
 
@@ -441,7 +454,6 @@ def main():
                    "d2h_bytes": 4 * T * (wave_steps + 2) + 4 * T,
                    "what": "gptoss_chain_run_wave_on_device: one wave of `steps` positions, token feedback and "
                            "finished-row handling by a kernel behind each step, host queues 16 steps at a time"}
-    clocks = sampler.stop() if sampler else None
 
     # ---- per-kernel device times: per kind, an event pair around its launches of a step
     prof = chain.profile(T, max(1, min(args.profile_steps, args.steps)), mode=2)
