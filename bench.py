@@ -62,6 +62,9 @@ def parse_args():
     ap.add_argument("--pdl", action="store_true",
                     help="launch the chain's kernels with programmatic stream serialization (GPTOSS_PDL); "
                          "measured neutral to slightly negative between these kernels, so off by default")
+    ap.add_argument("--fp32", action="store_true",
+                    help="fp32 mode instead of the headline's bf16-activation mode: fp32 tensors everywhere and the "
+                         "CPU program's rounding sequence (GPTOSS_EXACT); twice the bytes")
     ap.add_argument("--split-embed-norm", action="store_true",
                     help="open the step with the reference's two launches (gather, then layer 0's norm) "
                          "instead of the fused one")
@@ -259,7 +262,8 @@ def reference_arm(pkg, args, rank: int):
 def workload_config(args, c):
     return {
         "workload": f"gpt-oss-{args.model}b decode chain: {c.n_layers} layers, {c.n_experts} experts top-{c.top_k}, "
-                    f"hidden {c.hidden}, bf16 activations, fp32 residual, {args.tokens_per_gpu} tokens per GPU, "
+                    f"hidden {c.hidden}, {'fp32 tensors, CPU rounding order' if getattr(args, 'fp32', False) else 'bf16 activations, fp32 residual'}, "
+                    f"{args.tokens_per_gpu} tokens per GPU, "
                     f"positions uniform in [0,4096)",
         "tokens_per_gpu": args.tokens_per_gpu, "layers": c.n_layers, "experts": c.n_experts,
         "parallelism": f"dp{args.gpus} (token shards, no collective)",
@@ -352,7 +356,7 @@ def main():
         pkg.synchronize()
 
     T = args.tokens_per_gpu
-    c = pkg.chain_config(args.model, pkg.BF16, 4096)
+    c = pkg.chain_config(args.model, pkg.F32 if args.fp32 else pkg.BF16, 4096)
     if args.vocab > 0:
         c.vocab = args.vocab
     if args.pdl:
@@ -460,7 +464,7 @@ def main():
 
     # ---- the strictest reading of "end to end": every operand of every kernel comes from
     # host memory each step (done last: it overwrites the device-side stand-ins)
-    host_operands = None if args.no_host_operands else host_operand_steps(pkg, chain, c, T, sets, tok, pos, nxt,
+    host_operands = None if (args.no_host_operands or args.fp32) else host_operand_steps(pkg, chain, c, T, sets, tok, pos, nxt,
                                                                           barrier, sharding, dist, world)
     peak, peak_src = hbm_peak()
     kernels = {}
@@ -491,7 +495,7 @@ def main():
     line = {
         "metric": "layer_chain_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded, host-generated)",
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32" if args.fp32 else "bf16", "data": "synthetic (seeded, host-generated)",
         "config": workload_config(args, c),
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": 8 * T, "d2h_bytes_per_step": 4 * T,
                 "ms_per_step": 1e3 * e2e_s / args.steps,
