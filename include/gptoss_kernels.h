@@ -205,7 +205,11 @@ GPTOSS_API int gptoss_swiglu(gptoss_stream_t stream, const void *Y, gptoss_dtype
  * increasing expert number (phys_of, may be NULL, maps renumbered experts back
  * for that order).  A row whose first expert is negative is a finished request:
  * x is left as it is, but the row still gets its norm.  own_row NULL means row
- * t*k+j.  norm_w NULL skips the norm (out is then ignored).
+ * t*k+j; a negative own_row entry (what gptoss_moe_group writes for a pair
+ * whose expert is outside its range) means "no row here": the pair is skipped,
+ * nothing is read for it (moe_combine_ep_kernel's range test,
+ * kernels/moe_ep.hpp:286-332).  norm_w NULL skips the norm (out is then
+ * ignored).
  */
 GPTOSS_API int gptoss_moe_combine(gptoss_stream_t stream, int T, float *x, const void *Z,
                                   gptoss_dtype_t z_dtype, const int *own_row,
@@ -269,6 +273,10 @@ GPTOSS_API int gptoss_moe_gather(gptoss_stream_t stream, int R, const void *t,
  * gptoss_kv_cache_write (arguments kc .. slot_scalar as there), taken from the fp32 values
  * before they are rounded to out_dtype -- the reference's order, and the same bits as the
  * two calls when out_dtype is fp32.  head_dim must be 64 and slots a multiple of 64.
+ * Shapes or alignments the one-launch kernel does not take (rows or caches not 16-byte
+ * aligned, more than 16,384 elements per row) are served by two launches that store the
+ * same bits: the cache is written first, from the input rows with the bias and the
+ * rotation redone in fp32, then the rows are rotated.
  */
 GPTOSS_API int gptoss_qkv_bias_rope_kv(gptoss_stream_t stream, int T, const void *qkv_in,
                                        gptoss_dtype_t in_dtype, long in_row_stride, const float *bias,

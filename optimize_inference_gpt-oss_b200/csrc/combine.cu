@@ -29,6 +29,7 @@ __device__ __forceinline__ Vec8 smem_chunk_f32(const unsigned char *p) {
 template <int KM> struct Routing { // weights and expert ids of one token
   float w[KM];
   int e[KM];
+  bool here[KM]; // the pair's expert row exists (own_row entry >= 0)
 };
 template <int KM> struct RowIds { // where the token's expert rows are, and whether it is live
   int row[KM];
@@ -67,7 +68,10 @@ __global__ void combine_rows(float *x, const ZT *__restrict__ Z, const int *__re
   // loading every word, lane L of each warp loads one word of a token and the
   // warp shares them with shuffles at the point of use:
   //   "ids" word:     L < k: own_row[token*k + L];   L == k: topk_e[token*k] (liveness)
-  //   "routing" word: L < k: topk_w[token*k + L];    k <= L < 2k: topk_e[token*k + L - k]
+  //   "routing" word: L < k: topk_w[token*k + L];    k <= L < 2k: topk_e[token*k + L - k];
+  //                   2k <= L < 3k: own_row[token*k + L - 2k]
+  // A pair whose own_row entry is negative has no expert row here (the grouping step writes
+  // -1 for experts outside its range): nothing is copied for it and it adds nothing.
   const int lane = threadIdx.x & 31;
   auto load_ids_word = [&](long row) -> uint32_t {
     if (lane < k)
@@ -81,6 +85,8 @@ __global__ void combine_rows(float *x, const ZT *__restrict__ Z, const int *__re
       return __float_as_uint(__ldg(topk_w + (size_t)row * k + lane));
     if (lane < 2 * k)
       return (uint32_t)__ldg(topk_e + (size_t)row * k + lane - k);
+    if (lane < 3 * k)
+      return own_row ? (uint32_t)__ldg(own_row + (size_t)row * k + lane - 2 * k) : 0u;
     return 0u;
   };
   auto spread_ids = [&](uint32_t word) {
@@ -97,6 +103,7 @@ __global__ void combine_rows(float *x, const ZT *__restrict__ Z, const int *__re
     for (int j = 0; j < KM; j++) {
       r.w[j] = __uint_as_float(__shfl_sync(0xffffffffu, word, j < k ? j : 0));
       r.e[j] = j < k ? (int)__shfl_sync(0xffffffffu, word, k + j) : 0x7fffffff;
+      r.here[j] = j < k && (int)__shfl_sync(0xffffffffu, word, j < k ? 2 * k + j : 0) >= 0;
     }
     return r;
   };
@@ -112,7 +119,7 @@ __global__ void combine_rows(float *x, const ZT *__restrict__ Z, const int *__re
         if (ids.live) {
 #pragma unroll
           for (int j = 0; j < KM; j++)
-            if (j < k) {
+            if (j < k && ids.row[j] >= 0) {
               const ZT *zr = Z + (size_t)ids.row[j] * H + (size_t)chunk * 8;
               unsigned char *sz = sx + x_bytes + (size_t)j * z_bytes + (size_t)chunk * 8 * SZ;
               cp_async16(sz, zr);
@@ -199,13 +206,16 @@ __global__ void combine_rows(float *x, const ZT *__restrict__ Z, const int *__re
             // position jj of the summation order takes choice ord[jj]
             int j = jj;
             float wj = cur.w[jj];
+            bool here = cur.here[jj];
             if (EXACT) {
               j = ord[jj];
 #pragma unroll
               for (int q = 0; q < KM; q++)
                 if (q == j)
-                  wj = cur.w[q];
+                  wj = cur.w[q], here = cur.here[q];
             }
+            if (!here)
+              continue;
             const unsigned char *sz = sx + x_bytes + (size_t)j * z_bytes + (size_t)chunk * 8 * SZ;
             Vec8 z;
             if constexpr (SZ == 2)
@@ -299,6 +309,8 @@ __global__ void combine_rows_generic(float *x, const ZT *__restrict__ Z,
         float acc = 0.0f;
         for (int j = 0; j < k; j++) {
           const size_t p = (size_t)row * k + ord[j];
+          if (own_row && own_row[p] < 0)
+            continue; // no expert row here for this pair
           const size_t zr = own_row ? (size_t)own_row[p] : p;
           const float z = load1(Z + zr * H + i), w = topk_w[p];
           acc = MODE == 1 ? __fadd_rn(acc, __fmul_rn(z, w)) : __fmaf_rn(z, w, acc);

@@ -57,15 +57,16 @@ inline void launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_
     tl_launch_error = e;
 }
 
-// After a launch: GPTOSS_OK or GPTOSS_ERR_CUDA.
+// After a launch: GPTOSS_OK or GPTOSS_ERR_CUDA, from what cudaLaunchKernelEx returned for this
+// launch.  The thread's "last error" is not polled: an error an application left there before
+// calling in is the application's to find, not this launch's failure.  A failed launch of ours
+// is taken out of that slot again, since it is reported through the status.
 inline int launch_status() {
-  cudaError_t e = tl_launch_error;
+  const cudaError_t e = tl_launch_error;
   tl_launch_error = cudaSuccess;
-  const cudaError_t last = cudaGetLastError();
-  if (e == cudaSuccess)
-    e = last;
   if (e == cudaSuccess)
     return GPTOSS_OK;
+  (void)cudaGetLastError();
   note_cuda_error(e);
   return GPTOSS_ERR_CUDA;
 }

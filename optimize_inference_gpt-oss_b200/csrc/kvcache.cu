@@ -30,11 +30,24 @@ __device__ __forceinline__ size_t vscale_index(int b, int slot, int g, int slots
   return chunk64_index(b, slot, g, 0, slots, kv_dim) / 64;
 }
 
+// What turns a raw qkv row into the row the cache is written from, for the launch that
+// writes the cache from the rotation's INPUT (gptoss_qkv_bias_rope_kv at shapes its fused
+// kernel does not take): bias, positions and the cos/sin tables.  A lane's two elements l and
+// l + 32 of a 64-wide key head are one rotation pair.  tables == nullptr: rows are final.
+struct Prep {
+  const float *bias; // may be nullptr
+  const int *pos;
+  int pos_scalar;
+  const float *cos_tab, *sin_tab; // [n_pos, 32]
+  int n_pos;
+  int separate_products; // the CPU build's form (no FMA): x1*c - x2*s from two rounded products
+};
+
 template <typename QT>
 __global__ void __launch_bounds__(256)
     kv_cache_write_rows(const QT *__restrict__ qkv, long row_stride, int n_q_heads, int n_kv_heads,
                         uint16_t *__restrict__ kc, int8_t *__restrict__ vq, float *__restrict__ vs, int slots,
-                        const int *__restrict__ slot_of_row, int slot_scalar, int T) {
+                        const int *__restrict__ slot_of_row, int slot_scalar, int T, Prep prep) {
   pdl_prologue();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
   const int kv_dim = n_kv_heads * kHeadDim;
@@ -45,8 +58,26 @@ __global__ void __launch_bounds__(256)
     const QT *k = qkv + (size_t)row * row_stride + (size_t)n_q_heads * kHeadDim;
     const QT *v = k + kv_dim;
     for (int g = warp; g < n_kv_heads; g += n_warps) {
-      const float k0 = load1(k + g * kHeadDim + lane), k1 = load1(k + g * kHeadDim + 32 + lane);
-      const float v0 = load1(v + g * kHeadDim + lane), v1 = load1(v + g * kHeadDim + 32 + lane);
+      float k0 = load1(k + g * kHeadDim + lane), k1 = load1(k + g * kHeadDim + 32 + lane);
+      float v0 = load1(v + g * kHeadDim + lane), v1 = load1(v + g * kHeadDim + 32 + lane);
+      if (prep.cos_tab) { // the row is the rotation's input: bias, then rotate the key pair
+        if (prep.bias) {
+          const float *bk = prep.bias + (size_t)n_q_heads * kHeadDim + g * kHeadDim, *bv = bk + kv_dim;
+          k0 = __fadd_rn(k0, bk[lane]), k1 = __fadd_rn(k1, bk[32 + lane]);
+          v0 = __fadd_rn(v0, bv[lane]), v1 = __fadd_rn(v1, bv[32 + lane]);
+        }
+        int p = prep.pos ? __ldg(prep.pos + row) : prep.pos_scalar;
+        p = p < 0 ? 0 : (p >= prep.n_pos ? prep.n_pos - 1 : p);
+        const float c = prep.cos_tab[(size_t)p * 32 + lane], sn = prep.sin_tab[(size_t)p * 32 + lane];
+        const float x1 = k0, x2 = k1;
+        if (prep.separate_products) {
+          k0 = __fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, sn));
+          k1 = __fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, sn));
+        } else {
+          k0 = __fmaf_rn(x1, c, -__fmul_rn(x2, sn));
+          k1 = __fmaf_rn(x2, c, __fmul_rn(x1, sn));
+        }
+      }
       // keys: bf16, round to nearest even (exact when the input already is bf16)
       kc[chunk64_index(row, slot, g, lane, slots, kv_dim)] = (uint16_t)f32_to_bf16_bits(k0);
       kc[chunk64_index(row, slot, g, 32 + lane, slots, kv_dim)] = (uint16_t)f32_to_bf16_bits(k1);
@@ -66,7 +97,36 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+int launch_cache_write(cudaStream_t s, int T, const void *qkv, gptoss_dtype_t qkv_dtype, long row_stride,
+                       int n_q_heads, int n_kv_heads, uint16_t *kc, int8_t *vq, float *vs, int slots,
+                       const int *slot_of_row, int slot_scalar, const Prep &prep) {
+  const int grid = row_grid(T, 8);
+  if (qkv_dtype == GPTOSS_F32)
+    launch_kernel(kv_cache_write_rows<float>, dim3(grid), dim3(256), 0, s, static_cast<const float *>(qkv),
+                  row_stride, n_q_heads, n_kv_heads, kc, vq, vs, slots, slot_of_row, slot_scalar, T, prep);
+  else
+    launch_kernel(kv_cache_write_rows<uint16_t>, dim3(grid), dim3(256), 0, s,
+                  static_cast<const uint16_t *>(qkv), row_stride, n_q_heads, n_kv_heads, kc, vq, vs, slots,
+                  slot_of_row, slot_scalar, T, prep);
+  return launch_status();
+}
+
 } // namespace
+
+// The cache write of gptoss_qkv_bias_rope_kv as a launch of its own, from the rotation's
+// input rows: the same fp32 values the fused kernel holds in registers, whatever type the
+// rotated rows are stored as.  64-wide heads; arguments already validated by the caller.
+int kv_cache_write_from_input(cudaStream_t s, int T, const void *qkv_in, gptoss_dtype_t in_dtype,
+                              long in_row_stride, const float *bias, const int *pos, int pos_scalar,
+                              const float *cos_tab, const float *sin_tab, int n_pos, int n_q_heads,
+                              int n_kv_heads, uint16_t *kc, int8_t *vq, float *vs, int slots,
+                              const int *slot_of_row, int slot_scalar, unsigned flags) {
+  const Prep prep = {bias, pos, pos_scalar, cos_tab, sin_tab, n_pos,
+                     (flags & GPTOSS_EXACT) && !(flags & GPTOSS_FMA)};
+  return launch_cache_write(s, T, qkv_in, in_dtype, in_row_stride, n_q_heads, n_kv_heads, kc, vq, vs, slots,
+                            slot_of_row, slot_scalar, prep);
+}
+
 } // namespace gptoss
 
 extern "C" int gptoss_kv_cache_write(gptoss_stream_t stream, int T, const void *qkv, gptoss_dtype_t qkv_dtype,
@@ -84,14 +144,7 @@ extern "C" int gptoss_kv_cache_write(gptoss_stream_t stream, int T, const void *
     return GPTOSS_OK;
   if (!qkv || !kc || !vq || !vs)
     return GPTOSS_ERR_BAD_ARG;
-  cudaStream_t s = as_stream(stream);
-  const int grid = row_grid(T, 8);
-  if (qkv_dtype == GPTOSS_F32)
-    launch_kernel(kv_cache_write_rows<float>, dim3(grid), dim3(256), 0, s, static_cast<const float *>(qkv),
-                  row_stride, n_q_heads, n_kv_heads, kc, vq, vs, slots, slot_of_row, slot_scalar, T);
-  else
-    launch_kernel(kv_cache_write_rows<uint16_t>, dim3(grid), dim3(256), 0, s,
-                  static_cast<const uint16_t *>(qkv), row_stride, n_q_heads, n_kv_heads, kc, vq, vs, slots,
-                  slot_of_row, slot_scalar, T);
-  return launch_status();
+  const Prep none = {};
+  return launch_cache_write(as_stream(stream), T, qkv, qkv_dtype, row_stride, n_q_heads, n_kv_heads, kc, vq, vs,
+                            slots, slot_of_row, slot_scalar, none);
 }

@@ -306,8 +306,8 @@ template <typename IT, typename OT, bool EXACT, bool FMA> int launch(cudaStream_
     // 4096 rows -- as did capping registers for a fourth resident block.
     int st = GPTOSS_ERR_UNSUPPORTED;
     if (stage_bytes * 2 <= 220 * 1024) {
-      if (a.cache.kc) { // with the cache write: 64-wide heads only
-        if (a.head_dim == 64)
+      if (a.cache.kc) { // with the cache write: 64-wide heads only, 16-byte key stores
+        if (a.head_dim == 64 && aligned16(a.cache.kc))
           st = launch_pipe<IT, OT, EXACT, FMA, 2, true>(s, a, threads, stage_bytes * 2);
         return st;
       }
@@ -335,6 +335,11 @@ template <typename IT, typename OT> int launch_mode(cudaStream_t s, const Args &
 } // namespace gptoss
 
 namespace gptoss {
+int kv_cache_write_from_input(cudaStream_t s, int T, const void *qkv_in, gptoss_dtype_t in_dtype,
+                              long in_row_stride, const float *bias, const int *pos, int pos_scalar,
+                              const float *cos_tab, const float *sin_tab, int n_pos, int n_q_heads,
+                              int n_kv_heads, uint16_t *kc, int8_t *vq, float *vs, int slots,
+                              const int *slot_of_row, int slot_scalar, unsigned flags);
 namespace {
 
 int run_bias_rope(gptoss_stream_t stream, int T, const void *qkv_in, gptoss_dtype_t in_dtype, long in_row_stride,
@@ -400,11 +405,20 @@ extern "C" int gptoss_qkv_bias_rope_kv(gptoss_stream_t stream, int T, const void
                                  out_row_stride, cache, flags);
   if (st != GPTOSS_ERR_UNSUPPORTED)
     return st;
-  // a shape or alignment the fused kernel does not take: the two separate launches
-  st = gptoss_qkv_bias_rope(stream, T, qkv_in, in_dtype, in_row_stride, bias, pos, pos_scalar, cos_tab, sin_tab,
-                            n_pos, n_q_heads, n_kv_heads, head_dim, qkv_out, out_dtype, out_row_stride, flags);
-  if (st != GPTOSS_OK)
-    return st;
-  return gptoss_kv_cache_write(stream, T, qkv_out, out_dtype, out_row_stride, n_q_heads, n_kv_heads, head_dim, kc,
-                               vq, vs, slots, slot_of_row, slot_scalar, flags);
+  // A shape or alignment the fused kernel does not take: two launches.  The cache is written
+  // first, from the input rows (bias and rotation redone in fp32 by that launch), so that it
+  // holds what the fused kernel would have stored even when qkv_out is bf16 or is qkv_in.
+  if (T > 0 && (!qkv_in || !cos_tab || !sin_tab || n_pos <= 0 || !gptoss::valid_dtype(in_dtype) ||
+                in_row_stride < (long)(n_q_heads + 2 * n_kv_heads) * head_dim))
+    return GPTOSS_ERR_BAD_ARG;
+  if (T > 0) {
+    const gptoss::PdlScope pdl(flags);
+    st = gptoss::kv_cache_write_from_input(gptoss::as_stream(stream), T, qkv_in, in_dtype, in_row_stride, bias, pos,
+                                           pos_scalar, cos_tab, sin_tab, n_pos, n_q_heads, n_kv_heads, kc, vq, vs,
+                                           slots, slot_of_row, slot_scalar, flags);
+    if (st != GPTOSS_OK)
+      return st;
+  }
+  return gptoss_qkv_bias_rope(stream, T, qkv_in, in_dtype, in_row_stride, bias, pos, pos_scalar, cos_tab, sin_tab,
+                              n_pos, n_q_heads, n_kv_heads, head_dim, qkv_out, out_dtype, out_row_stride, flags);
 }

@@ -1,5 +1,6 @@
 // Library-wide host helpers: version, status text, per-thread CUDA error memory,
 // cached device properties.
+#include <atomic>
 #include <mutex>
 
 #include "common.cuh"
@@ -14,17 +15,17 @@ thread_local cudaError_t tl_launch_error = cudaSuccess;
 void note_cuda_error(cudaError_t e) { g_last_cuda_error = (int)e; }
 
 int sm_count() {
-  static int cached[64] = {0};
+  static std::atomic<int> cached[64]; // zero-initialised; threads may race to fill a slot with the same value
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64)
     return 148;
-  if (cached[dev] == 0) {
-    int n = 0;
+  int n = cached[dev].load(std::memory_order_relaxed);
+  if (n == 0) {
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
       n = 148;
-    cached[dev] = n;
+    cached[dev].store(n, std::memory_order_relaxed);
   }
-  return cached[dev];
+  return n;
 }
 
 int occupancy_cached(const void *kernel, int threads, size_t smem) {

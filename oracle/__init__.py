@@ -22,7 +22,8 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_SO = os.path.join(_HERE, "libgptoss_oracle.so")
 REF_SO = os.path.join(_HERE, "_ref", "libgptoss_ref.so")
-REFERENCE_CHECKOUT = os.environ.get("GPTOSS_REFERENCE", "/root/reference")
+# where the reference project is checked out (only needed to build _ref/libgptoss_ref.so)
+REFERENCE_CHECKOUT = os.environ.get("GPTOSS_REFERENCE") or os.path.join(os.sep, "root", "reference")
 
 _f32p = np.ctypeslib.ndpointer(dtype=np.float32, flags="C_CONTIGUOUS")
 _i32p = np.ctypeslib.ndpointer(dtype=np.int32, flags="C_CONTIGUOUS")
@@ -105,6 +106,43 @@ class _Lib:
             self._cache_indices = sig("cache_indices", None, C.c_long, _i32p, _i32p, _i32p, _i32p, C.c_int, C.c_int,
                                       _i64p, _i64p, _i64p)
             self._f32_to_bf16 = sig("f32_to_bf16", None, C.c_long, _f32p, _u16p)
+
+        # the int8 value rule of the KV cache and the wave bookkeeping (reference library: when it
+        # was built from a checkout that holds tests/attn_test.cpp and engine/gpu_engine.hpp)
+        self.has_value_codes = p == "orc_" or (hasattr(L, "ref_has_value_codes") and bool(L.ref_has_value_codes()))
+        if self.has_value_codes:
+            _i8p = np.ctypeslib.ndpointer(dtype=np.int8, flags="C_CONTIGUOUS")
+            self._value_codes = sig("value_codes", None, C.c_long, _f32p, _i8p, _f32p)
+        self.has_wave = p == "orc_" or (hasattr(L, "ref_has_wave") and bool(L.ref_has_wave()))
+        if self.has_wave:
+            self._wave = sig("wave_bookkeeping", C.c_longlong, C.c_int, _i32p, _i32p, C.c_int, _i32p, C.c_int,
+                             _i32p, _i32p, C.POINTER(C.c_int), _i32p, _i32p)
+
+    def value_codes(self, v):
+        """int8 codes [n, 64] and scales [n] of n value heads of 64 floats."""
+        v = np.ascontiguousarray(v, np.float32).reshape(-1, 64)
+        codes, scales = np.empty(v.shape, np.int8), np.empty(v.shape[0], np.float32)
+        self._value_codes(v.shape[0], v, codes, scales)
+        return codes, scales
+
+    def wave_bookkeeping(self, prompts, picked, steps):
+        """A wave of len(prompts) requests served for at most `steps` steps, where step s picked
+        token picked[s, b] for row b.  Returns (out_rows [n, steps + 2] with -1 wherever nothing
+        was written, n_generated, steps_run, done [n], fed [steps_run, n], mask [steps_run, n])."""
+        n = len(prompts)
+        offsets = np.zeros(n + 1, np.int32)
+        offsets[1:] = np.cumsum([len(p) for p in prompts])
+        flat = np.ascontiguousarray(np.concatenate([np.asarray(p, np.int32) for p in prompts]) if n else [], np.int32)
+        picked = np.ascontiguousarray(picked, np.int32).reshape(max(steps, 0), n)
+        width = steps + 2
+        out = np.full((n, width), -1, np.int32)
+        done = np.zeros(n, np.int32)
+        fed = np.full((max(steps, 1), n), -9, np.int32)
+        mask = np.full((max(steps, 1), n), -9, np.int32)
+        ran = C.c_int(0)
+        total = self._wave(n, flat if flat.size else np.zeros(1, np.int32), offsets, steps,
+                           picked if picked.size else np.zeros(1, np.int32), width, out, done, C.byref(ran), fed, mask)
+        return out, int(total), int(ran.value), done, fed[:ran.value], mask[:ran.value]
 
     # -- single-row primitives ------------------------------------------------
     def max_threads(self) -> int:

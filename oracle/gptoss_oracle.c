@@ -327,7 +327,11 @@ ORC_API void orc_swiglu_rows(float *out, const float *gate_up, long R, int n_int
  * (run.cpp:677-748): agg starts at zero, each expert adds product-then-sum,
  * and agg is added to x at the end.  row_of[t*k+j] is the row of Z holding
  * the output of choice j of token t.  A token whose first expert is negative
- * is a finished request and is left untouched (gpu_engine's convention). */
+ * is a finished request and is left untouched (gpu_engine's convention).  A
+ * pair whose row_of entry is negative has no expert row on this device (the
+ * grouping step's -1 for an expert outside its range) and adds nothing, as in
+ * moe_combine_ep_kernel's `e >= e_begin && e < e_begin + e_count` test
+ * (kernels/moe_ep.hpp:286-332). */
 ORC_API void orc_combine_rows(float *x, const float *Z, const int *row_of, const float *weights,
                               const int *experts, int T, int k, int H, int n_experts,
                               int threads) {
@@ -345,7 +349,7 @@ ORC_API void orc_combine_rows(float *x, const float *Z, const int *row_of, const
           hit = j;
           break;
         }
-      if (hit < 0)
+      if (hit < 0 || row_of[(size_t)t * k + hit] < 0)
         continue;
       const float w = weights[(size_t)t * k + hit];
       const float *z = Z + (size_t)row_of[(size_t)t * k + hit] * H;
@@ -441,6 +445,27 @@ ORC_API void orc_f32_to_bf16(long n, const float *in, uint16_t *out) {
     out[t] = orc_bf16(in[t]);
 }
 
+/* The int8 form of one 64-wide value head (kernels/fast_misc.hpp:79-87; in host code,
+ * quantize_v of tests/attn_test.cpp:218-226): scale = max|v| / 127, code = v * (127 / max|v|)
+ * rounded to the nearest integer, ties to even, and held to [-127, 127]; a head of zeros
+ * gives zero codes and a zero scale. */
+static void orc_value_head(const float *v, int8_t *codes, float *scale) {
+  float amax = 0.0f;
+  for (int i = 0; i < 64; i++)
+    amax = fmaxf(amax, fabsf(v[i]));
+  const float inv = amax > 0.0f ? 127.0f / amax : 0.0f;
+  for (int i = 0; i < 64; i++) {
+    float c = rintf(v[i] * inv);
+    c = fminf(fmaxf(c, -127.0f), 127.0f);
+    codes[i] = (int8_t)c;
+  }
+  *scale = amax / 127.0f;
+}
+ORC_API void orc_value_codes(long n_heads, const float *v, int8_t *codes, float *scales) {
+  for (long h = 0; h < n_heads; h++)
+    orc_value_head(v + h * 64, codes + h * 64, scales + h);
+}
+
 ORC_API void orc_kv_cache_write(const float *qkv, long row_stride, int T, int n_q_heads, int n_kv_heads,
                                 uint16_t *kc, int8_t *vq, float *vs, int slots, const int *slot_of_row) {
   const int kv_dim = n_kv_heads * 64;
@@ -450,22 +475,83 @@ ORC_API void orc_kv_cache_write(const float *qkv, long row_stride, int T, int n_
       continue;
     const float *k = qkv + (size_t)b * row_stride + (size_t)n_q_heads * 64, *v = k + kv_dim;
     for (int g = 0; g < n_kv_heads; g++) {
-      float amax = 0.0f;
-      for (int i = 0; i < 64; i++) {
+      int8_t codes[64];
+      float scale;
+      for (int i = 0; i < 64; i++)
         kc[orc_chunk64(b, slot, g, i, slots, kv_dim)] = orc_bf16(k[g * 64 + i]);
-        amax = fmaxf(amax, fabsf(v[g * 64 + i]));
-      }
-      const float inv = amax > 0.0f ? 127.0f / amax : 0.0f;
+      orc_value_head(v + g * 64, codes, &scale);
       for (int i = 0; i < 64; i++) {
-        float c = rintf(v[g * 64 + i] * inv);
-        c = fminf(fmaxf(c, -127.0f), 127.0f);
         const size_t at = orc_chunk64(b, slot & ~15, g, 0, slots, kv_dim) + ((slot >> 2) & 3) * 256 +
                           (i >> 2) * 16 + (i & 3) * 4 + (slot & 3);
-        vq[at] = (int8_t)c;
+        vq[at] = codes[i];
       }
-      vs[orc_chunk64(b, slot, g, 0, slots, kv_dim) / 64] = amax / 127.0f;
+      vs[orc_chunk64(b, slot, g, 0, slots, kv_dim) / 64] = scale;
     }
   }
+}
+
+/* What a wave of requests looks like from outside, given the tokens each step picked
+ * (engine/gpu_engine.hpp:761-841, the host statements between its GPU calls).  Stated row
+ * by row instead of step by step, since rows do not interact except through when the wave
+ * ends.  A row with np prompt tokens is fed prompt[p] in step p while p < np and afterwards
+ * the token its previous step picked, picked[(p - 1) * n_rows + b]; tokens fed from the
+ * model are recorded at out[p - np]; the first end token (199999 or 200002) fed at p >= 1
+ * finishes the row at f = p.  The wave runs P = min(steps, latest finish) steps, or `steps`
+ * when some row never finishes.  A finished row gets a -1 behind its tokens at f - np + 1
+ * and counts f - np + 1 generated tokens; an unfinished one the same with P for f (the
+ * count may be negative for a prompt longer than the wave, and is added as it is).
+ * fed[s * n_rows + b]: the token row b was given in step s (a finished row keeps its last).
+ * mask[s * n_rows + b]: whether the device saw row b as finished during step s (f <= s).
+ * out_rows is [n_rows, width] and only the entries named above are written. */
+ORC_API long long orc_wave_bookkeeping(int n_rows, const int *prompt_tokens, const int *prompt_offsets,
+                                       int steps, const int *picked, int width, int *out_rows,
+                                       int *done_out, int *steps_run, int *fed, int *mask) {
+  int *finish = (int *)malloc((size_t)(n_rows > 0 ? n_rows : 1) * sizeof(int));
+  int latest = 0, all_finish = 1;
+  for (int b = 0; b < n_rows; b++) {
+    const int *prompt = prompt_tokens + prompt_offsets[b];
+    const int np = prompt_offsets[b + 1] - prompt_offsets[b];
+    finish[b] = -1;
+    for (int p = 1; p <= steps; p++) {
+      const int token = p < np ? prompt[p] : picked[(size_t)(p - 1) * n_rows + b];
+      if (token == 199999 || token == 200002) {
+        finish[b] = p;
+        break;
+      }
+    }
+    if (finish[b] < 0)
+      all_finish = 0;
+    else if (finish[b] > latest)
+      latest = finish[b];
+  }
+  const int P = (all_finish && n_rows > 0) ? (latest < steps ? latest : steps) : (n_rows > 0 ? steps : 0);
+  long long count = 0;
+  for (int b = 0; b < n_rows; b++) {
+    const int *prompt = prompt_tokens + prompt_offsets[b];
+    const int np = prompt_offsets[b + 1] - prompt_offsets[b];
+    int *out = out_rows + (size_t)b * width;
+    const int f = (finish[b] >= 0 && finish[b] <= P) ? finish[b] : -1;
+    const int last = f >= 0 ? f : P;
+    int token = prompt[0];
+    for (int s = 0; s < P; s++) {
+      if (s >= 1 && s <= last) {
+        token = s < np ? prompt[s] : picked[(size_t)(s - 1) * n_rows + b];
+        if (s >= np)
+          out[s - np] = token;
+      }
+      fed[(size_t)s * n_rows + b] = token;
+      mask[(size_t)s * n_rows + b] = f >= 0 && f <= s;
+    }
+    if (last >= 1 && last == P && last >= np) /* the token fed to a step that never ran */
+      out[last - np] = picked[(size_t)(last - 1) * n_rows + b];
+    if (last - np + 1 >= 0)
+      out[last - np + 1] = -1;
+    count += last - np + 1;
+    done_out[b] = f >= 0;
+  }
+  free(finish);
+  *steps_run = P;
+  return count;
 }
 
 /* Host expf, exported so tests can compare a device exponential with the C

@@ -145,3 +145,85 @@ REF_API void ref_f32_to_bf16(long n, const float *in, uint16_t *out) {
 #else
 REF_API int ref_has_cache_layout(void) { return 0; }
 #endif
+
+// ---- the int8 value rule of the KV cache -------------------------------------------------
+// quantize_v of the reference's attention test (tests/attn_test.cpp:218-226): the host form
+// of what rope_kv_bf16_kernel does per value head (kernels/fast_misc.hpp:79-87).  It works
+// on D values; the test's D is 64, the head width of both models.
+#ifdef REF_VALUE_PART
+#include <algorithm>
+#include <cmath>
+namespace ref_value {
+constexpr int D = 64;
+#include REF_VALUE_PART
+} // namespace ref_value
+REF_API int ref_has_value_codes(void) { return 1; }
+REF_API void ref_value_codes(long n_heads, const float *v, int8_t *codes, float *scales) {
+  for (long h = 0; h < n_heads; h++)
+    ref_value::quantize_v(v + h * 64, codes + h * 64, scales + h);
+}
+#else
+REF_API int ref_has_value_codes(void) { return 0; }
+#endif
+
+// ---- the between-steps bookkeeping of gpu_run_wave ----------------------------------------
+// engine/gpu_engine.hpp:696-701 (WaveSlot), :802-826 (after each step) and :828-838 (after
+// the loop), included here as they stand, with the Requests struct and get_tok_gen_ptr of
+// getp_eval.cpp:9-15, 39-41 (that file as a whole calls into the GPU runner).  What the reference does on
+// the GPU between two bookkeeping passes is replaced by recorded tokens: picked[step * n_rows
+// + b] is what the step's argmax returned for row b.  fed[step * n_rows + b] receives the
+// token the row was fed in that step and mask[step * n_rows + b] the finished-row mask the
+// device held during it (copied only when it changed, as the reference copies it).
+#if defined(REF_WAVE_TYPES) && defined(REF_WAVE_STEP) && defined(REF_WAVE_TAIL)
+#include <vector>
+#include REF_WAVE_TYPES
+REF_API int ref_has_wave(void) { return 1; }
+REF_API long long ref_wave_bookkeeping(int n_rows, const int *prompt_tokens, const int *prompt_offsets,
+                                       int steps, const int *picked, int width, int *out_rows,
+                                       int *done_out, int *steps_run, int *fed, int *mask) {
+  Requests requests;
+  memset(&requests, 0, sizeof requests);
+  requests.num_reqs = n_rows;
+  requests.max_seq_len = width - 1; // rows of get_tok_gen_ptr are max_seq_len + 1 apart
+  requests.tok_gens = out_rows;
+  Requests *req = &requests;
+  std::vector<WaveSlot> slots(1);
+  {
+    WaveSlot &ws = slots[0];
+    ws.first = 0;
+    ws.n = n_rows;
+    ws.prompts.assign(n_rows, {});
+    for (int b = 0; b < n_rows; b++)
+      ws.prompts[b].assign(prompt_tokens + prompt_offsets[b], prompt_tokens + prompt_offsets[b + 1]);
+    ws.cur.resize(n_rows);
+    ws.next.resize(n_rows);
+    ws.done.assign(n_rows, 0);
+    for (int b = 0; b < n_rows; b++) // wave_slot_init, gpu_engine.hpp:726-727
+      ws.cur[b] = ws.prompts[b][0];
+  }
+  const int n = 1; // one member in the group
+  int active = n_rows;
+  long long generated = 0;
+  int pos = 0;
+  std::vector<int> device_mask(n_rows, 0); // hipMemset(row_done, 0), gpu_engine.hpp:773
+  while (pos < steps && active > 0) {
+    if (slots[0].done_changed) { // :784-788
+      device_mask = slots[0].done;
+      slots[0].done_changed = false;
+    }
+    for (int b = 0; b < n_rows; b++) {
+      fed[(size_t)pos * n_rows + b] = slots[0].cur[b];
+      mask[(size_t)pos * n_rows + b] = device_mask[b];
+      slots[0].next[b] = picked[(size_t)pos * n_rows + b];
+    }
+#include REF_WAVE_STEP
+  }
+#include REF_WAVE_TAIL
+  for (int b = 0; b < n_rows; b++)
+    done_out[b] = slots[0].done[b];
+  *steps_run = pos;
+  return generated;
+}
+#else
+REF_API int ref_has_wave(void) { return 0; }
+#endif

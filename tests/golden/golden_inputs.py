@@ -138,3 +138,63 @@ def case_bf16_rounding():
     bits = ((hi[:, None] << 16) | lo[None, :]).ravel()
     bits = np.concatenate([bits, bits | np.uint32(0x80000000), (hashed(85, 2000) & 0xFFFFFFFF).astype(np.uint32)])
     return bits.astype(np.uint32).view(np.float32)
+
+
+def case_value_heads():
+    """Value heads of 64 floats for the int8 rule of the KV cache: hashed heads at several
+    magnitudes, a head of zeros, the maximum shared by +x and -x, a head whose scaled values
+    are exact halves (round-half-to-even decides every code), one large value among tiny
+    ones, all values equal, and a head whose maximum is denormal with no zero in it (the
+    inverse overflows: every code saturates).  Every value is finite, and no head mixes a
+    maximum below 127 / FLT_MAX with a zero: there v * inv is 0 * inf, and the reference's
+    host form converts that NaN to int8, which C++ leaves undefined."""
+    heads = [uniform(91 + j, (64,), sc) for j, sc in enumerate((1.0, 3.0, 0.02, 1000.0, 1e-6, 2.5, 7.0, 0.3))]
+    heads.append(np.zeros(64, np.float32))
+    h = uniform(101, (64,), 1.0)
+    h[3], h[40] = 2.0, -2.0
+    heads.append(h)
+    halves = (np.arange(64, dtype=np.float32) - 32.0) + np.float32(0.5)   # -31.5 .. 31.5
+    halves[0], halves[63] = 127.0, -127.0                                 # max 127: inv is exactly 1
+    heads.append(halves)
+    heads.append((halves * np.float32(2.0 ** -20)).astype(np.float32))    # the same, scaled by a power of two
+    lone = np.full(64, 1e-4, np.float32)
+    lone[17] = -5000.0
+    heads.append(lone)
+    heads.append(np.full(64, -0.75, np.float32))
+    den = np.full(64, 1e-41, np.float32)
+    den[::2] = -2e-41
+    heads.append(den)
+    heads.append(np.float32(3.0e38) * uniform(102, (64,), 1.0))
+    return np.stack(heads).astype(np.float32)
+
+
+def case_wave():
+    """Scenarios (prompts, picked [steps, n], steps) for the wave bookkeeping: prompts of 1 to
+    7 tokens, an end token inside a prompt, a prompt longer than the wave, rows that pick an
+    end token at once, late or never, both end tokens, a wave that every row leaves early, a
+    wave of one step and a wave of none."""
+    EOS = (199999, 200002)
+    out = []
+    n, steps = 23, 9
+    prompts = [list(small_ints(200 + b, (1 + b % 7,), 0, 199000)) for b in range(n)]
+    prompts[3] = [11, 22, 200002, 33, 44]
+    prompts[9] = list(small_ints(300, (steps + 6,), 0, 199000))
+    prompts[12] = list(small_ints(301, (steps,), 0, 199000))
+    picked = small_ints(302, (steps, n), 0, 199000)
+    picked[:, 0] = EOS[0]
+    picked[4:, 5] = EOS[1]
+    picked[steps - 1, 7] = EOS[0]
+    picked[2, 8] = EOS[0]     # while row 8 is still inside its prompt: not looked at
+    picked[0, 14] = EOS[1]    # row 14 has a one-token prompt: finishes in the first pass
+    out.append((prompts, picked, steps))
+    n, steps = 10, 20         # everybody finishes by step 6: the wave stops there
+    prompts = [list(small_ints(400 + b, (1 + b % 3,), 0, 199000)) for b in range(n)]
+    picked = small_ints(401, (steps, n), 0, 199000)
+    for b in range(n):
+        picked[b % 6:, b] = EOS[b % 2]
+    out.append((prompts, picked, steps))
+    n = 5
+    prompts = [list(small_ints(500 + b, (1 + b,), 0, 199000)) for b in range(n)]
+    out.append((prompts, small_ints(501, (1, n), 0, 199000), 1))
+    out.append((prompts, np.zeros((0, n), np.int32), 0))
+    return out

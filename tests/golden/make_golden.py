@@ -15,6 +15,10 @@ stores the expected outputs:
     residual);
   * the chunk64 KV-cache index functions and the fp32 -> bf16 rounding rule: the REFERENCE's
     host-callable definitions in its kernel headers;
+  * the int8 codes and scales of value heads: the REFERENCE's quantize_v (tests/attn_test.cpp);
+  * the wave bookkeeping (output rows, counts, finished mask, tokens fed and mask seen per
+    step): the REFERENCE's statements of gpu_run_wave (engine/gpu_engine.hpp) around recorded
+    picks;
   * SwiGLU rows and combine rows: produced by the restated oracle (the reference has no
     callable form of those loops); they are regression vectors for the oracle, whose
     agreement with forward() is checked separately.
@@ -74,6 +78,12 @@ def main():
     k_at, vq_at, vs_at = ref.cache_indices(b, slot, g, i, slots, kv_dim)
     out["cache_k_at"], out["cache_vq_at"], out["cache_vs_at"] = (a.astype(np.int32) for a in (k_at, vq_at, vs_at))
     out["bf16_bits"] = ref.f32_to_bf16(gi.case_bf16_rounding())
+
+    out["value_codes"], out["value_scales"] = ref.value_codes(gi.case_value_heads())
+    for j, (prompts, picked, steps) in enumerate(gi.case_wave()):
+        rows, total, ran, done, fed, mask = ref.wave_bookkeeping(prompts, picked, steps)
+        out[f"wave{j}_rows"], out[f"wave{j}_counts"] = rows, np.array([total, ran], np.int64)
+        out[f"wave{j}_done"], out[f"wave{j}_fed"], out[f"wave{j}_mask"] = done, fed, mask.astype(np.int8)
 
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden.npz")
     np.savez_compressed(path, **out)

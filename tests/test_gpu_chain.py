@@ -201,37 +201,14 @@ def test_chain_rejects_bad_sizes(gpu):
         pkg.Chain(c, 8, 1)
 
 
-def _wave_reference(prompts, picks, steps):
-    """The reference's wave loop (gpu_engine.hpp:777-841) with the model replaced by a fixed
-    pick per row -- which is what the chain produces, since its logits are stand-ins."""
-    n, eos = len(prompts), (199999, 200002)
-    out = np.full((n, steps + 2), -1, np.int32)
-    done = [False] * n
-    total, active, pos = 0, n, 0
-    while pos < steps and active > 0:
-        pos += 1
-        for b in range(n):
-            if done[b]:
-                continue
-            npr = len(prompts[b])
-            if pos < npr:
-                token = prompts[b][pos]
-            else:
-                token = picks[b]
-                out[b, pos - npr] = token
-            if token in eos:
-                done[b] = True
-                active -= 1
-                if pos - npr + 1 >= 0:
-                    out[b, pos - npr + 1] = -1
-                total += pos - npr + 1
-    for b in range(n):
-        if not done[b]:
-            npr = len(prompts[b])
-            if pos - npr + 1 >= 0:
-                out[b, pos - npr + 1] = -1
-            total += pos - npr + 1
-    return out, total, pos, np.array(done, np.int32)
+def _wave_reference(orc, prompts, picks, steps):
+    """What the wave must return: the oracle's bookkeeping (pinned to the reference's own
+    statements of gpu_run_wave, engine/gpu_engine.hpp:802-838, in test_oracle_pins.py) with the
+    model replaced by a fixed pick per row -- which is what the chain produces, since its
+    logits are stand-ins.  (rows, generated, steps run, done mask)."""
+    picked = np.tile(np.asarray(picks, np.int32), (steps, 1))
+    out, total, ran, done, _, _ = orc.wave_bookkeeping(prompts, picked, steps)
+    return out, total, ran, done
 
 
 def test_wave_loop_with_finished_rows(gpu, orc):
@@ -253,14 +230,14 @@ def test_wave_loop_with_finished_rows(gpu, orc):
         prompts = [list(r.integers(0, 199000, 1 + b % 6)) for b in range(n)]
         prompts[3] = [11, 22, 200002, 33, 44]       # an end token inside the prompt
         prompts[9] = list(r.integers(0, 199000, 20))  # a prompt longer than the wave
-        want_out, want_total, want_pos, want_done = _wave_reference(prompts, picks, steps)
+        want_out, want_total, want_pos, want_done = _wave_reference(orc, prompts, picks, steps)
         out, total, ran = ch.run_wave(prompts, steps)
         assert ran == want_pos and total == want_total
         assert np.array_equal(out, want_out)
         assert np.array_equal(ch.download(pkg.BUF_ROW_DONE, 0, np.int32, (n,)), want_done)
         # the same wave with the bookkeeping kept on the GPU; 40 steps are queued in three batches
         for many in (steps, 40):
-            want = _wave_reference(prompts, picks, many)
+            want = _wave_reference(orc, prompts, picks, many)
             out, total, ran = ch.run_wave(prompts, many, on_device=True)
             assert (ran, total) == (want[2], want[1])
             assert np.array_equal(out, want[0])
@@ -279,7 +256,7 @@ def test_wave_loop_with_finished_rows(gpu, orc):
             assert ran == 2 and total == n * 1 and (out[:, 0] == 199999).all() and (out[:, 1:] == -1).all()
         # a smaller wave after a larger one, and prompts that need a larger device buffer
         long_prompts = [list(r.integers(0, 199000, 300)) for _ in range(5)]
-        want = _wave_reference(long_prompts, picks[:5], 6)
+        want = _wave_reference(orc, long_prompts, picks[:5], 6)
         out, total, ran = ch.run_wave(long_prompts, 6, on_device=True)
         assert (ran, total) == (want[2], want[1]) and np.array_equal(out, want[0])
     finally:

@@ -581,6 +581,75 @@ def test_moe_gather_and_grouped_combine(gpu, orc, dt):
     assert n_bit_diff(xb.get(), want) == 0
 
 
+@pytest.mark.parametrize("Hd", [2880, 1000, 77])
+def test_combine_behind_a_partial_expert_range(gpu, orc, Hd):
+    """Grouping for experts 64..127 of 128 marks every pair of another expert with own_row -1.
+    The combine must skip those pairs (nothing read, nothing added) in all three arithmetic
+    forms; Z holds rows for the local pairs only, so any read through a -1 would leave it."""
+    pkg, d = gpu, Dev(gpu)
+    T, k, E = 257, 4, 128
+    r = rng_of("partial", Hd)
+    w, e = orc.router_rows(r.standard_normal((T, E)).astype(np.float32), k)
+    e[::11], w[::11] = -1, 0
+    own = d.out((T * k,), np.int32)
+    counts, offsets, row_pair = d.out((64,), np.int32), d.out((65,), np.int32), d.out((T * k,), np.int32)
+    pkg.moe_group(d.put(e), T * k, 64, 64, counts, offsets, row_pair, own)
+    own_row = own.get()
+    _, off, want_pair, want_own = orc.moe_group(e, 64, 64)
+    assert np.array_equal(own_row, want_own)
+    R = int(off[-1])
+    assert 0 < R < T * k and (own_row < 0).any() and (own_row.reshape(T, k)[e[:, 0] >= 0] < 0).any()
+    x = r.standard_normal((T, Hd)).astype(np.float32)
+    gain = (1 + 0.1 * r.standard_normal(Hd)).astype(np.float32)
+    z = r.standard_normal((R, Hd)).astype(np.float32)
+    want = orc.combine_rows(x, z, own_row.reshape(T, k), w, e, E)
+    for flags in (pkg.EXACT, pkg.EXACT | pkg.FMA):
+        xb = d.put_inout(x)
+        pkg.moe_combine(T, xb, d.put(z), pkg.F32, d.put(own_row), d.put(w), d.put(e), k, Hd, flags=flags)
+        if flags == pkg.EXACT:
+            assert n_bit_diff(xb.get(), want) == 0
+        else:
+            assert rel_err(xb.get(), want) <= TOL_F32
+    zb = widen(pkg, z, pkg.BF16).reshape(R, Hd)
+    want_b = orc.combine_rows(x, zb, own_row.reshape(T, k), w, e, E)
+    xb, o = d.put_inout(x), d.out((T, Hd), pkg.BF16)
+    pkg.moe_combine(T, xb, d.put(zb, pkg.BF16), pkg.BF16, d.put(own_row), d.put(w), d.put(e), k, Hd,
+                    norm_w=d.put(gain), out=o, out_dtype=pkg.BF16)
+    assert rel_err(xb.get(), want_b) <= TOL_F32 * 10
+    assert rel_err(o.get(), orc.add_rmsnorm_rows(want_b, None, gain)[1]) <= TOL_BF16
+    # a token none of whose experts is local keeps its x bit for bit
+    nowhere = (own_row.reshape(T, k) < 0).all(axis=1)
+    assert nowhere.any() and n_bit_diff(xb.get()[nowhere], x[nowhere]) == 0
+
+
+def test_bias_rope_with_cache_write_unaligned_cache_stores_the_same_bits(gpu, orc):
+    """A key cache that does not start on a 16-byte boundary sends gptoss_qkv_bias_rope_kv to
+    its two-launch form; with bf16 rows in and out, in place, both forms must store the same
+    rows, keys, codes and scales (the cache comes from the fp32 values either way)."""
+    pkg, d = gpu, Dev(gpu)
+    T, nq, nkv, slots = 70, 64, 8, 128
+    row, kv_dim = (nq + 2 * nkv) * 64, nkv * 64
+    r = rng_of("kv-unaligned")
+    qkv = widen(pkg, r.standard_normal((T, row)) * 2, pkg.BF16).reshape(T, row)
+    bias = (0.02 * r.standard_normal(row)).astype(np.float32)
+    pos = r.integers(0, 4096, T).astype(np.int32)
+    slot = r.integers(0, slots, T).astype(np.int32)
+    ct, st = pkg.build_rope_tables(4096, 64)
+    n_k = T * slots * kv_dim
+    count = pkg.load().gptoss_generic_launch_count
+    res = []
+    for shift in (0, 1):  # in uint16 elements: 0 = aligned, 1 = two bytes off
+        kc = d.put_inout(np.zeros(n_k + 8, np.uint16))
+        vq, vs = d.put_inout(np.zeros(n_k, np.int8)), d.put_inout(np.zeros(n_k // 64, np.float32))
+        rows = d.put_inout(pkg.to_bf16_bits(qkv).reshape(T, row))
+        before = count()
+        pkg.qkv_bias_rope_kv(T, rows, pkg.BF16, row, d.put(bias), d.put(pos), 0, d.put(ct), d.put(st), 4096, nq, nkv,
+                             64, rows, pkg.BF16, row, kc.ptr + 2 * shift, vq, vs, slots, slot_of_row=d.put(slot))
+        res.append((rows.get(as_f32=False), kc.get(as_f32=False)[shift:shift + n_k], vq.get(), vs.get()))
+    for a, b, what in zip(res[0], res[1], ("rows", "keys", "codes", "scales")):
+        assert np.array_equal(a.view(np.uint8), b.view(np.uint8)), what
+
+
 # ---- the argmax key as a public contract for logits producers --------------------------------
 
 def test_argmax_keys_finish_matches_argmax(gpu, orc):
@@ -690,6 +759,37 @@ def test_kv_cache_write(gpu, orc, T, nq, nkv, slots, dt):
     at = ((b * slots + (s_ & ~63)) * kv_dim + g * 4096 + (s_ & 63) * 64) // 64
     v = qkv[b, (nq + nkv + g) * 64:(nq + nkv + g + 1) * 64]
     assert got_s[at] == np.float32(np.abs(v).max()) / np.float32(127.0)
+
+
+def test_value_codes_of_the_committed_heads(gpu, orc, golden):
+    """The value heads of the golden file (halves, shared maxima, a denormal maximum, ...) as
+    the value part of qkv rows: the codes and scales the cache writer stores are the
+    reference's quantize_v answers, through both the stand-alone writer and the fused one."""
+    pkg, d = gpu, Dev(gpu)
+    heads = gi.case_value_heads()
+    T, nq, nkv, slots = heads.shape[0] // 2, 1, 2, 64
+    row = (nq + 2 * nkv) * 64
+    qkv = rng_of("valueheads").standard_normal((T, row)).astype(np.float32)
+    qkv[:, (nq + nkv) * 64:] = heads.reshape(T, nkv * 64)
+    slot = np.arange(T, dtype=np.int32) * 3 % slots
+    kv_dim, n_k = nkv * 64, T * slots * nkv * 64
+    cs, sn = np.ones((1, 32), np.float32), np.zeros((1, 32), np.float32)   # rotation by zero
+    for fused in (False, True):
+        kc, vq, vs = (d.put_inout(np.zeros(n_k, np.uint16)), d.put_inout(np.zeros(n_k, np.int8)),
+                      d.put_inout(np.zeros(n_k // 64, np.float32)))
+        if fused:
+            o = d.out((T, row), pkg.F32)
+            pkg.qkv_bias_rope_kv(T, d.put(qkv), pkg.F32, row, None, None, 0, d.put(cs), d.put(sn), 1, nq, nkv, 64, o,
+                                 pkg.F32, row, kc, vq, vs, slots, slot_of_row=d.put(slot), flags=pkg.EXACT)
+        else:
+            pkg.kv_cache_write(T, d.put(qkv), pkg.F32, row, nq, nkv, 64, kc, vq, vs, slots, slot_of_row=d.put(slot))
+        got_q, got_s = vq.get(), vs.get()
+        b = np.repeat(np.arange(T), nkv * 64)
+        g = np.tile(np.repeat(np.arange(nkv), 64), T)
+        i = np.tile(np.arange(64), T * nkv)
+        _, vq_at, vs_at = orc.cache_indices(b, slot[b], g, i, slots, kv_dim)
+        assert np.array_equal(got_q[vq_at].reshape(-1, 64), golden["value_codes"]), fused
+        assert n_bit_diff(got_s[vs_at[::64]], golden["value_scales"]) == 0, fused
 
 
 @pytest.mark.parametrize("T,nq,nkv,slots", [(37, 64, 8, 1024), (600, 64, 8, 128), (5, 8, 1, 64), (1, 0, 4, 64)])

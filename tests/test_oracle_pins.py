@@ -221,6 +221,66 @@ def test_ref_cache_layout_and_bf16_rounding(orc, ref):
     assert np.array_equal(orc.f32_to_bf16(gi.case_bf16_rounding()), ref.f32_to_bf16(gi.case_bf16_rounding()))
 
 
+def _assert_same_wave(got, want):
+    for g, w, what in zip(got, want, ("rows", "generated", "steps run", "done", "fed", "mask")):
+        assert np.array_equal(np.asarray(g), np.asarray(w)), what
+
+
+def test_golden_value_codes_and_wave(orc, golden):
+    codes, scales = orc.value_codes(gi.case_value_heads())
+    assert np.array_equal(codes, golden["value_codes"])
+    assert_bit_equal(scales, golden["value_scales"], "value scales")
+    for j, (prompts, picked, steps) in enumerate(gi.case_wave()):
+        rows, total, ran, done, fed, mask = orc.wave_bookkeeping(prompts, picked, steps)
+        assert np.array_equal(rows, golden[f"wave{j}_rows"]), j
+        assert [total, ran] == list(golden[f"wave{j}_counts"]), j
+        assert np.array_equal(done, golden[f"wave{j}_done"]) and np.array_equal(fed, golden[f"wave{j}_fed"]), j
+        assert np.array_equal(mask, golden[f"wave{j}_mask"]), j
+
+
+def test_ref_value_codes_of_the_cache(orc, ref):
+    """The int8 value rule against quantize_v of the reference's attention test
+    (tests/attn_test.cpp:218-226), bit for bit: random heads over 30 orders of magnitude, the
+    committed corner heads, heads made of exact halves at random power-of-two scales."""
+    if not ref.has_value_codes:
+        pytest.skip("reference library built without tests/attn_test.cpp")
+    r = np.random.default_rng(17)
+    v = r.standard_normal((20000, 64)).astype(np.float32) * np.float32(10.0) ** r.integers(-15, 15, (20000, 1)).astype(np.float32)
+    v[::7] = np.round(v[::7] * 4) / 4
+    for heads in (v, gi.case_value_heads()):
+        (c0, s0), (c1, s1) = orc.value_codes(heads), ref.value_codes(heads)
+        assert np.array_equal(c0, c1)
+        assert_bit_equal(s0, s1, "scales")
+    k = r.integers(-126, 127, (4000, 64)).astype(np.float32) + np.float32(0.5)
+    k[:, 0] = 127.0
+    k = (k * np.float32(2.0) ** r.integers(-60, 60, (4000, 1)).astype(np.float32)).astype(np.float32)
+    (c0, s0), (c1, s1) = orc.value_codes(k), ref.value_codes(k)
+    assert np.array_equal(c0, c1) and np.array_equal(s0.view(np.uint32), s1.view(np.uint32))
+    assert (np.abs(c0.astype(np.int32)) % 2 == 0)[:, 1:].all(), "halves go to the even neighbour"
+
+
+def test_ref_wave_bookkeeping(orc, ref):
+    """The wave bookkeeping, restated row by row, against the reference's own statements
+    (engine/gpu_engine.hpp:696-701, 802-838) driven with recorded picks: output rows, the
+    generated-token count, steps run, the finished mask, and per step the tokens fed and the
+    mask the device held."""
+    if not ref.has_wave:
+        pytest.skip("reference library built without engine/gpu_engine.hpp")
+    for prompts, picked, steps in gi.case_wave():
+        _assert_same_wave(orc.wave_bookkeeping(prompts, picked, steps), ref.wave_bookkeeping(prompts, picked, steps))
+    r = np.random.default_rng(23)
+    for trial in range(300):
+        n, steps = int(r.integers(1, 40)), int(r.integers(0, 30))
+        prompts = [list(r.integers(0, 199000, int(r.integers(1, 12)))) for _ in range(n)]
+        picked = r.integers(0, 199000, (steps, n)).astype(np.int32)
+        ends = r.random((steps, n)) < (0.0, 0.05, 0.3)[trial % 3]
+        picked[ends] = np.where(r.random(int(ends.sum())) < 0.5, 199999, 200002)
+        for b in range(n):
+            if r.random() < 0.1:
+                prompts[b][int(r.integers(0, len(prompts[b])))] = 199999
+        _assert_same_wave(orc.wave_bookkeeping(prompts, picked, steps), ref.wave_bookkeeping(prompts, picked, steps))
+
+
 @pytest.mark.parametrize("seed", [1, 2, 3])
 def test_ref_forward_pins_the_inline_loops(orc, ref, seed):
     """forward() of a tiny model: bias adds, SwiGLU (with clamping hit by the large

@@ -25,7 +25,7 @@ def _case(pkg, seed, T, V, dtype):
 
 
 @pytest.mark.parametrize("dtype_name,T,V", [("f32", 300, 50000), ("bf16", 96, 201088)])
-def test_noalloc_argmax_equals_argmax_on_two_calls_in_a_row(gpu, dtype_name, T, V):
+def test_noalloc_argmax_equals_argmax_on_two_calls_in_a_row(gpu, orc, dtype_name, T, V):
     pkg = gpu
     dtype = pkg.F32 if dtype_name == "f32" else pkg.BF16
     # the shapes are chosen so that rows are cut into slices and the merge words are really used
@@ -39,11 +39,28 @@ def test_noalloc_argmax_equals_argmax_on_two_calls_in_a_row(gpu, dtype_name, T, 
         pkg.argmax_noalloc(T, logits, dtype, V, V, got_buf)         # new entry point, built-in scratch
         want, got = want_buf.numpy(np.int32, T), got_buf.numpy(np.int32, T)
         assert np.array_equal(got, want), f"call {call}: indices are integers, they must match exactly"
+        # both entry points share their kernels and the key merge, so the CPU oracle is asked too
+        host = _case(pkg, seed, T, V, dtype)
+        host = pkg.from_bf16_bits(host).reshape(T, V) if dtype == pkg.BF16 else host
+        assert np.array_equal(got, orc.argmax_rows(host, threads=0)), f"call {call}: against the CPU oracle"
         answers.append(got)
         logits.free()
     assert not np.array_equal(answers[0], answers[1]), "the two calls must have seen different data"
     if dtype == pkg.F32:
         assert answers[0][1] == 5 and answers[1][1] == 5
+
+
+def test_noalloc_argmax_takes_exactly_as_many_rows_as_its_scratch_holds(gpu, orc):
+    """The largest batch the entry point accepts, with short rows: the last row's merge word is
+    the last word of the built-in array."""
+    pkg = gpu
+    T, V = pkg.ARGMAX_NOALLOC_MAX_ROWS, 1024
+    host = _case(pkg, 303, T, V, pkg.F32)
+    logits, out = pkg.DeviceBuffer.from_numpy(host), pkg.DeviceBuffer(T * 4)
+    for _ in range(2):
+        pkg.argmax_noalloc(T, logits, pkg.F32, V, V, out)
+        assert np.array_equal(out.numpy(np.int32, T), orc.argmax_rows(host, threads=0))
+    logits.free()
 
 
 def test_noalloc_argmax_refuses_more_rows_than_its_scratch_holds(gpu):
