@@ -1,17 +1,28 @@
 #!/usr/bin/env python
 """Benchmark of the fused-kernel layer chain.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python bench.py [--config 0..4] [--gpus N] [--steps K] [--warmup W] [--impl reference]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
-One "step" is one decode step of the gpt-oss-20b chain (embedding gather, first norm,
-24 x [qkv bias + RoPE, residual add + RMSNorm, router top-4 + softmax, SwiGLU, expert
-combine + residual + next norm], greedy argmax over the vocabulary) for 4096 tokens per
-GPU in bf16-activation mode, with seeded synthetic tensors of the real shapes standing in
-for the GEMM and attention outputs.  Rank 0 prints one JSON line:
+--config picks one of the five benchmark configurations (default 1, the one the headline
+metric is quoted on):
+
+  0  fp32 mode, layer 0 only, 64 tokens per GPU at positions 0..63 (the CPU-runnable case)
+  1  gpt-oss-20b decode chain, bf16 activations, 4096 tokens per GPU, positions uniform in
+     [0, 4096): embedding gather + first norm, 24 x [qkv bias + RoPE, residual add + RMSNorm,
+     router top-4 + softmax, SwiGLU, expert combine + residual + next norm], greedy argmax
+  2  the same chain as a prefill: 16 sequences x 1024 positions (16,384 tokens in all,
+     position = t mod 1024), whole sequences sharded over the GPUs (strong scaling)
+  3  gpt-oss-120b shapes: 36 layers, 128 experts, 4096 tokens per GPU
+  4  the vocabulary-sized ops on their own: final RMSNorm of 4096 rows, greedy argmax over
+     [4096, 201088] bf16 logits, embedding gather of 8192 ids from the bf16 table
+
+Seeded synthetic tensors of the real shapes stand in for the GEMM and attention outputs.
+Rank 0 prints one JSON line:
 
   value       tokens/s over all GPUs, inputs resident in HBM, K CUDA-graph replays timed
               with CUDA events on the launching stream, max over ranks
+  sustained   the same replays held for two seconds or more, with the SM clock seen
   e2e         the same through the engine-step call (gptoss_chain_step): token ids and
               positions copied from pinned host memory and the picked tokens copied back
               inside the timed region every step (what the reference engine moves per
@@ -19,7 +30,10 @@ for the GEMM and attention outputs.  Rank 0 prints one JSON line:
   roofline    the dominant kernel: algorithmic bytes per launch / mean launch time (CUDA
               events on the launching stream around that kernel's launches of a step, one
               per layer, each on its own layer's tensors), against the measured HBM copy peak
-  kernels     the same for every kernel kind
+  kernels     the same for every kernel kind, with the DRAM traffic of the ncu capture
+  strong      under torchrun: one batch of 4096 tokens split over the ranks (512 per GPU at
+              8), the literal shard of configurations 1 and 3; at N = 1 `literal_shard`
+              runs that 512-token share on the one GPU
   cpu_baseline  the reference's CPU code (OpenMP over tokens, all host threads) on a
               bounded sample of the same workload; rank 0 at N = 1 only
 
@@ -30,6 +44,7 @@ from __future__ import annotations
 import argparse
 import importlib
 import json
+import math
 import os
 import subprocess
 import sys
@@ -42,6 +57,25 @@ sys.path.insert(0, ROOT)
 PKG = "optimize_inference_gpt-oss_b200"
 
 FALLBACK_HBM_GBS = 6650.0  # an earlier measurement on this pool, used only without MEASURED_PEAKS.json
+L2_BYTES = 126 << 20
+
+# gpt-oss shapes (export_model_bin/gpt-oss-*/config.json of the reference)
+DIMS = dict(vocab=201088, hidden=2880, top_k=4, inter=2880, head_dim=64, n_q_heads=64, n_kv_heads=8,
+            swiglu_limit=7.0)
+MODELS = {20: dict(n_layers=24, n_experts=32), 120: dict(n_layers=36, n_experts=128)}
+
+CONFIGS = {
+    0: dict(model=20, fp32=True, layers=1, tokens=64, positions="0..T-1", scaling="weak",
+            what="fp32 mode (CPU rounding order), layer 0 only"),
+    1: dict(model=20, fp32=False, layers=None, tokens=4096, positions="uniform", scaling="weak",
+            what="decode chain, bf16 activations, fp32 residual"),
+    2: dict(model=20, fp32=False, layers=None, total=16384, seq=1024, positions="t mod 1024", scaling="strong",
+            what="prefill chain, 16 sequences x 1024 positions, bf16 activations, fp32 residual"),
+    3: dict(model=120, fp32=False, layers=None, tokens=4096, positions="uniform", scaling="weak",
+            what="decode chain, bf16 activations, fp32 residual"),
+    4: dict(model=20, fp32=False, layers=1, tokens=4096, positions="uniform", scaling="weak",
+            what="vocabulary-sized ops: final RMSNorm, greedy argmax, embedding gather of 2 ids per row"),
+}
 
 
 def parse_args():
@@ -50,12 +84,14 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--model", type=int, default=20, choices=[20, 120])
-    ap.add_argument("--tokens-per-gpu", type=int, default=4096)
+    ap.add_argument("--config", type=int, default=1, choices=sorted(CONFIGS))
+    ap.add_argument("--model", type=int, default=None, choices=[20, 120], help="override the configuration's model")
+    ap.add_argument("--tokens-per-gpu", type=int, default=None, help="override the configuration's tokens per GPU")
     ap.add_argument("--standin-sets", type=int, default=0, help="distinct per-layer input sets (0 = one per layer)")
     ap.add_argument("--seed", type=int, default=1)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="minimum CPU time of the baseline sample")
+    ap.add_argument("--sustain-seconds", type=float, default=2.0, help="length of the sustained leg (0 = skip)")
     ap.add_argument("--profile-steps", type=int, default=10)
     ap.add_argument("--ncu-steps", type=int, default=0,
                     help="profiler mode: build the chain, run this many steps kernel by kernel, exit (no timing)")
@@ -63,7 +99,7 @@ def parse_args():
                     help="launch the chain's kernels with programmatic stream serialization (GPTOSS_PDL); "
                          "measured neutral to slightly negative between these kernels, so off by default")
     ap.add_argument("--fp32", action="store_true",
-                    help="fp32 mode instead of the headline's bf16-activation mode: fp32 tensors everywhere and the "
+                    help="fp32 mode at the configuration's size: fp32 tensors everywhere and the "
                          "CPU program's rounding sequence (GPTOSS_EXACT); twice the bytes")
     ap.add_argument("--split-embed-norm", action="store_true",
                     help="open the step with the reference's two launches (gather, then layer 0's norm) "
@@ -72,6 +108,64 @@ def parse_args():
                     help="skip the extra e2e leg that re-sends every stand-in tensor from host memory each step")
     ap.add_argument("--vocab", type=int, default=0, help="override the vocabulary size (profiler mode: smaller footprint)")
     return ap.parse_args()
+
+
+def shard_range(total: int, world: int, rank: int, granule: int = 1):
+    """The package's split (sharding.shard_range), restated so that the CPU arm needs no package."""
+    units = total // granule
+    base, extra = divmod(units, world)
+    begin = rank * base + min(rank, extra)
+    return begin * granule, (begin + base + (1 if rank < extra else 0)) * granule
+
+
+class Work:
+    """What one rank runs: the configuration resolved against the command line and the rank."""
+
+    def __init__(self, args, world: int, rank: int):
+        cfg = CONFIGS[args.config]
+        self.config = args.config
+        self.model = args.model or cfg["model"]
+        self.fp32 = bool(args.fp32 or cfg["fp32"])
+        self.layers = cfg["layers"] or MODELS[self.model]["n_layers"]
+        self.experts = MODELS[self.model]["n_experts"]
+        self.scaling = cfg["scaling"]
+        self.world, self.rank = world, rank
+        if "total" in cfg and args.tokens_per_gpu is None:  # a fixed batch split by whole sequences
+            self.total = cfg["total"]
+            self.begin, end = shard_range(self.total, world, rank, cfg["seq"])
+            self.T = end - self.begin
+            self.T_max = shard_range(self.total, world, 0, cfg["seq"])[1]
+        else:
+            self.T = self.T_max = args.tokens_per_gpu or cfg.get("tokens", 4096)
+            self.total = self.T * world
+            self.begin = self.T * rank
+            self.scaling = "weak"
+        self.positions = cfg["positions"]
+        self.what = cfg["what"]
+        self.seed = args.seed
+
+    def pos_array(self, T=None, begin=None):
+        T = self.T if T is None else T
+        begin = self.begin if begin is None else begin
+        if self.positions == "t mod 1024":
+            return ((begin + np.arange(T)) % 1024).astype(np.int32)
+        if self.positions == "0..T-1":
+            return np.arange(T, dtype=np.int32)
+        r = np.random.default_rng([self.seed, 200, self.rank])
+        return r.integers(0, 4096, T).astype(np.int32)
+
+    def describe(self):
+        per = (f"{self.T} tokens per GPU" if self.scaling == "weak"
+               else f"{self.total} tokens in all, {self.T_max} on the fullest GPU")
+        return {
+            "workload": f"config {self.config}: gpt-oss-{self.model}b {self.what}: {self.layers} layer"
+                        f"{'s' if self.layers > 1 else ''}, {self.experts} experts top-{DIMS['top_k']}, hidden "
+                        f"{DIMS['hidden']}, {'fp32 tensors' if self.fp32 else 'bf16 tensors'}, {per}, positions "
+                        f"{'uniform in [0,4096)' if self.positions == 'uniform' else self.positions}",
+            "baseline_config": self.config, "tokens_per_gpu": self.T_max, "total_tokens": self.total,
+            "layers": self.layers, "experts": self.experts,
+            "parallelism": f"dp{self.world} (token shards, no collective)",
+        }
 
 
 def hbm_peak():
@@ -83,11 +177,17 @@ def hbm_peak():
 
 
 def ncu_traffic(kind: str):
-    """DRAM bytes per launch from the committed ncu capture, if one has been taken."""
+    """DRAM bytes per launch at 4096 tokens from the committed ncu captures (profiles/), if taken:
+    (bytes moved inside the launch, the record)."""
     try:
-        return json.load(open(os.path.join(ROOT, "profiles", "ncu_traffic.json"))).get(kind)
+        rec = json.load(open(os.path.join(ROOT, "profiles", "ncu_traffic.json"))).get(kind)
     except Exception:
-        return None
+        return None, None
+    if not isinstance(rec, dict):
+        return rec, None
+    if "dram_total_in_launch" in rec:
+        return rec["dram_total_in_launch"], rec
+    return rec.get("dram_read", 0) + rec.get("dram_write_in_launch", 0), rec
 
 
 # ---- clocks ------------------------------------------------------------------------------
@@ -105,10 +205,6 @@ class ClockSampler:
                  "-i", str(gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except Exception:
             self.proc = None
-        self.marks = []
-
-    def mark(self):
-        self.marks.append(time.time())
 
     def stop(self):
         if self.proc is None:
@@ -160,6 +256,15 @@ def visible_gpu_index(local_rank: int) -> int:
 
 
 # ---- the CPU implementation (cpu_baseline leg and --impl reference) ----------------------
+# Nothing below this line up to run_cpu() touches the CUDA library: inputs are drawn with
+# NumPy and the model's shapes are the literals above, so the reference arm loads oracle/ only.
+
+def bf16_values(a: np.ndarray) -> np.ndarray:
+    """fp32 values rounded to the nearest bf16 (ties to even), kept as fp32."""
+    u = np.ascontiguousarray(a, np.float32).view(np.uint32)
+    r = (u + np.uint32(0x7FFF) + ((u >> np.uint32(16)) & np.uint32(1))) & np.uint32(0xFFFF0000)
+    return r.view(np.float32)
+
 
 class CpuChain:
     """The reference's CPU functions looped over a sample of tokens, OpenMP over tokens.
@@ -169,7 +274,9 @@ class CpuChain:
     loops that exist only inline in forward() (embedding copy, bias add, SwiGLU, expert
     combine, residual adds) come from the restated oracle, as they do when it is absent."""
 
-    def __init__(self, pkg, model: int, tokens: int, seed: int, sets: int = 2):
+    OPS_FROM_PORT = ["embed", "bias", "swiglu", "combine", "residual"]
+
+    def __init__(self, work: Work, tokens: int, sets: int = 2):
         import oracle
         if not os.path.exists(oracle.ORACLE_SO):
             oracle.build(ref=None)
@@ -180,54 +287,92 @@ class CpuChain:
         # every core this process may run on; passed explicitly to each call, because launchers
         # such as torchrun export OMP_NUM_THREADS=1
         self.threads = host_cores()
-        c = pkg.chain_config(model, pkg.BF16, 4096)
-        self.c, self.T, self.sets = c, tokens, sets
-        T, K, H = tokens, c.top_k, c.hidden
+        self.work, self.T, self.sets = work, tokens, min(sets, work.layers)
+        T, K, H, E = tokens, DIMS["top_k"], DIMS["hidden"], work.experts
+        self.qkv_dim = (DIMS["n_q_heads"] + 2 * DIMS["n_kv_heads"]) * DIMS["head_dim"]
+        r = np.random.default_rng([work.seed, 977])
+        act = (lambda a: a) if work.fp32 else bf16_values
 
-        def normal(shape, sid, mean=0.0, sd=1.0):  # bf16 values widened exactly to fp32
-            bits = pkg.synth_normal(int(np.prod(shape)), pkg.BF16, seed + 977, sid, mean, sd)
-            return pkg.from_bf16_bits(bits).reshape(shape)
+        def normal(shape, sd=1.0):
+            return act((sd * r.standard_normal(shape, dtype=np.float32)).astype(np.float32))
 
-        self.vocab_rows = min(c.vocab, 8192)  # the gather only touches the sampled rows
-        self.emb = normal((self.vocab_rows, H), 0, 0.0, 0.02)
-        self.tokens = pkg.synth_uniform_int(T, seed, 1, 0, self.vocab_rows)
-        self.pos = pkg.synth_uniform_int(T, seed, 2, 0, 4096)
-        self.gain = (1 + 0.1 * normal((3, H), 3)).astype(np.float32)
-        self.bias = normal((c.qkv_dim,), 4, 0.0, 0.02)
-        self.proj = [normal((T, H), 10 + s) for s in range(sets)]
-        self.qkv = [normal((T, c.qkv_dim), 20 + s) for s in range(sets)]
-        self.router = [normal((T, c.n_experts), 30 + s) for s in range(sets)]
-        self.mlp1 = [normal((K * T, 2 * c.inter), 40 + s, 0.0, 2.0) for s in range(sets)]
-        self.expert = [normal((K * T, H), 50 + s) for s in range(sets)]
-        self.logits = normal((T, c.vocab), 60, 0.0, 3.0)
+        self.vocab_rows = min(DIMS["vocab"], 8192)  # the gather only touches the sampled rows
+        self.emb = normal((self.vocab_rows, H), 0.02)
+        self.tokens = r.integers(0, self.vocab_rows, T).astype(np.int32)
+        self.pos = work.pos_array(T, 0)
+        self.gain = (1 + 0.1 * r.standard_normal((3, H), dtype=np.float32)).astype(np.float32)
+        self.bias = (0.02 * r.standard_normal(self.qkv_dim, dtype=np.float32)).astype(np.float32)
+        self.proj = [normal((T, H)) for _ in range(self.sets)]
+        self.qkv = [normal((T, self.qkv_dim)) for _ in range(self.sets)]
+        self.router = [normal((T, E)) for _ in range(self.sets)]
+        self.mlp1 = [normal((K * T, 2 * DIMS["inter"]), 2.0) for _ in range(self.sets)]
+        self.expert = [normal((K * T, H)) for _ in range(self.sets)]
+        self.logits = normal((T, DIMS["vocab"]), 3.0)
         self.ident = np.arange(T * K, dtype=np.int32).reshape(T, K)
 
     def step(self):
-        c, fn, orc, th = self.c, self.fn, self.orc, self.threads
+        fn, orc, th, w = self.fn, self.orc, self.threads, self.work
+        nq, nkv, hd = DIMS["n_q_heads"], DIMS["n_kv_heads"], DIMS["head_dim"]
         x = orc.embed_rows(self.emb, self.tokens, threads=th)
         fn.add_rmsnorm_rows(x, None, self.gain[0], threads=th)
-        for l in range(c.n_layers):
+        for l in range(w.layers):
             s = l % self.sets
-            fn.bias_rope_rows(self.qkv[s], self.bias, self.pos, c.n_q_heads, c.n_kv_heads, c.head_dim, threads=th)
+            fn.bias_rope_rows(self.qkv[s], self.bias, self.pos, nq, nkv, hd, threads=th)
             x, _ = fn.add_rmsnorm_rows(x, self.proj[s], self.gain[1], threads=th)
-            w, e = fn.router_rows(self.router[s], c.top_k, threads=th)
-            orc.swiglu_rows(self.mlp1[s], c.swiglu_limit, threads=th)
-            x = orc.combine_rows(x, self.expert[s], self.ident, w, e, c.n_experts, threads=th)
+            wt, e = fn.router_rows(self.router[s], DIMS["top_k"], threads=th)
+            orc.swiglu_rows(self.mlp1[s], DIMS["swiglu_limit"], threads=th)
+            x = orc.combine_rows(x, self.expert[s], self.ident, wt, e, w.experts, threads=th)
             fn.add_rmsnorm_rows(x, None, self.gain[2], threads=th)
         return fn.argmax_rows(self.logits, threads=th)
 
     def describe(self):
-        return (f"{self.T} tokens through the whole {self.c.n_layers}-layer chain per pass, fp32 on the host, "
+        return (f"{self.T} tokens through the whole {self.work.layers}-layer chain per pass, fp32 on the host, "
                 f"OpenMP over tokens; rmsnorm/rope/top-k/softmax/argmax "
                 f"{'are the reference functions compiled from run.cpp (-O3 -fopenmp)' if self.ref else 'from the restated oracle'}"
                 f", SwiGLU/combine/bias/residual loops (inline in forward()) from the restated oracle")
 
 
-def run_cpu(pkg, args, min_seconds: float, steps: int | None, warmup: int):
-    """Times the CPU chain.  steps=None: repeat passes until min_seconds have gone by."""
+class CpuVocabOps(CpuChain):
+    """Configuration 4 on the host: final norm, greedy argmax and the gather of two ids per row."""
+
+    OPS_FROM_PORT = ["embed"]
+
+    def __init__(self, work: Work, tokens: int, sets: int = 1):
+        import oracle
+        if not os.path.exists(oracle.ORACLE_SO):
+            oracle.build(ref=None)
+        self.orc = oracle.Oracle()
+        self.ref = oracle.Reference() if oracle.have_reference() else None
+        self.kind = "reference" if self.ref is not None else "port"
+        self.fn = self.ref if self.ref is not None else self.orc
+        self.threads = host_cores()
+        self.work, self.T = work, tokens
+        r = np.random.default_rng([work.seed, 978])
+        H = DIMS["hidden"]
+        self.x = r.standard_normal((tokens, H), dtype=np.float32)
+        self.gain = (1 + 0.1 * r.standard_normal(H, dtype=np.float32)).astype(np.float32)
+        self.logits = bf16_values(3.0 * r.standard_normal((tokens, DIMS["vocab"]), dtype=np.float32))
+        self.vocab_rows = 8192
+        self.emb = bf16_values(0.02 * r.standard_normal((self.vocab_rows, H), dtype=np.float32))
+        self.ids = r.integers(0, self.vocab_rows, 2 * tokens).astype(np.int32)
+
+    def step(self):
+        self.fn.add_rmsnorm_rows(self.x, None, self.gain, threads=self.threads)
+        self.orc.embed_rows(self.emb, self.ids, threads=self.threads)
+        return self.fn.argmax_rows(self.logits, threads=self.threads)
+
+    def describe(self):
+        return (f"{self.T} rows per pass: rmsnorm of [{self.T}, 2880], sample_argmax over [{self.T}, 201088], a gather "
+                f"of {2 * self.T} table rows; fp32 on the host, OpenMP over rows; rmsnorm and argmax "
+                f"{'are the reference functions compiled from run.cpp (-O3 -fopenmp)' if self.ref else 'from the restated oracle'}"
+                f", the row copy from the restated oracle")
+
+
+def run_cpu(work: Work, min_seconds: float, steps: int | None, warmup: int):
+    """Times the CPU implementation.  steps=None: repeat passes until min_seconds have gone by."""
     threads = host_cores()
-    tokens = int(min(args.tokens_per_gpu, max(128, 8 * threads)))
-    cpu = CpuChain(pkg, args.model, tokens, args.seed)
+    tokens = int(min(work.T_max, max(128, 8 * threads)))
+    cpu = (CpuVocabOps if work.config == 4 else CpuChain)(work, tokens)
     for _ in range(max(1, warmup)):
         cpu.step()
     t0 = time.perf_counter()
@@ -241,34 +386,22 @@ def run_cpu(pkg, args, min_seconds: float, steps: int | None, warmup: int):
     return cpu, n, el
 
 
-def reference_arm(pkg, args, rank: int):
+def reference_arm(args, work: Work, rank: int):
     if rank != 0:
         return
-    cpu, n, el = run_cpu(pkg, args, 0.0, args.steps, args.warmup)
+    cpu, n, el = run_cpu(work, 0.0, args.steps, args.warmup)
     value = cpu.T * n / el
     line = {
         "impl": "reference", "metric": "layer_chain_tokens_per_s", "value": value, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": n, "warmup": args.warmup, "ms_per_step": 1e3 * el / n,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(args, cpu.c),
+        "higher_is_better": True, "scaling": work.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": work.describe(),
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cpu.threads, "kind": cpu.kind,
-                         "sample": cpu.describe()},
+                         "tokens_per_pass": cpu.T, "ops_from_port": cpu.OPS_FROM_PORT, "sample": cpu.describe()},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
-
-
-def workload_config(args, c):
-    return {
-        "workload": f"gpt-oss-{args.model}b decode chain: {c.n_layers} layers, {c.n_experts} experts top-{c.top_k}, "
-                    f"hidden {c.hidden}, {'fp32 tensors, CPU rounding order' if getattr(args, 'fp32', False) else 'bf16 activations, fp32 residual'}, "
-                    f"{args.tokens_per_gpu} tokens per GPU, "
-                    f"positions uniform in [0,4096)",
-        "tokens_per_gpu": args.tokens_per_gpu, "layers": c.n_layers, "experts": c.n_experts,
-        "parallelism": f"dp{args.gpus} (token shards, no collective)",
-        "l2": "inputs larger than L2: every layer reads its own seeded tensors, several GB per step",
-    }
 
 
 def host_operand_steps(pkg, chain, c, T, sets, tok, pos, nxt, barrier, sharding, dist, world, steps=3):
@@ -321,24 +454,207 @@ def host_operand_steps(pkg, chain, c, T, sets, tok, pos, nxt, barrier, sharding,
 
 # ---- our arm -------------------------------------------------------------------------------
 
+class Timer:
+    """CUDA events on one stream of the library."""
+
+    def __init__(self, pkg, stream):
+        import ctypes as C
+        self.pkg, self.lib, self.stream, self.C = pkg, pkg.load(), stream, C
+        self.ev = [C.c_void_p(), C.c_void_p()]
+        for e in self.ev:
+            pkg.check(self.lib.gptoss_event_create(C.byref(e)))
+
+    def start(self):
+        self.pkg.check(self.lib.gptoss_event_record(self.ev[0], self.stream))
+
+    def stop(self):
+        self.pkg.check(self.lib.gptoss_event_record(self.ev[1], self.stream))
+
+    def ms(self) -> float:
+        ms = self.C.c_float()
+        self.pkg.check(self.lib.gptoss_event_synchronize(self.ev[1]))
+        self.pkg.check(self.lib.gptoss_event_elapsed_ms(self.ev[0], self.ev[1], self.C.byref(ms)))
+        return float(ms.value)
+
+
+def vocab_ops(pkg, args, work: Work, world, rank, local_rank, dist, sharding, barrier):
+    """Configuration 4: the three vocabulary-sized ops through their own entry points."""
+    T, H, V = work.T, DIMS["hidden"], args.vocab or DIMS["vocab"]
+    n_ids = 2 * T
+    c = pkg.chain_config(20, pkg.BF16, 4096)
+    c.n_layers, c.vocab = 1, V
+    t_setup = time.perf_counter()
+    chain = pkg.Chain(c, T, 1)  # holds the table, the logits, x, the gain and the key words; one layer of the rest
+    chain.fill_synthetic(T, seed=args.seed + 7919 * rank)
+    stream = chain.stream
+    r = np.random.default_rng([args.seed, 300, rank])
+    ids_host = pkg.PinnedArray(n_ids, np.int32)
+    ids_host.array[:] = r.integers(0, V, n_ids)
+    picked_host = pkg.PinnedArray(T, np.int32)
+    ids = pkg.DeviceBuffer.from_numpy(ids_host.array)
+    rows = pkg.DeviceBuffer(n_ids * H * 4)
+    xs = pkg.DeviceBuffer.from_numpy(r.standard_normal((T, H), dtype=np.float32))
+    flush = pkg.DeviceBuffer(256 << 20)
+    buf = lambda which: chain.buffer(which, 0)[0]
+    table, logits, gain, normed, keys_out = (buf(pkg.BUF_EMBEDDING), buf(pkg.BUF_LOGITS), buf(pkg.BUF_GAIN_OUT),
+                                             buf(pkg.BUF_NORMED), buf(pkg.BUF_NEXT))
+    keys = pkg.DeviceBuffer.from_numpy(np.zeros(T, np.uint64))
+    setup_s = time.perf_counter() - t_setup
+    lib = pkg.load()
+
+    ops = {
+        "final_norm": (lambda: pkg.add_rmsnorm(T, xs, None, pkg.F32, gain, normed, pkg.BF16, H, stream=stream),
+                       T * (H * 4 + H * 2) + H * 4, 1),
+        "argmax": (lambda: pkg.argmax(T, logits, pkg.BF16, V, V, keys, keys_out, stream=stream),
+                   T * (V * 2 + 4), 2 if lib.gptoss_argmax_slices(T, V, pkg.BF16, 1) > 1 else 1),
+        "embed": (lambda: pkg.embed(n_ids, table, pkg.BF16, V, ids, rows, pkg.F32, H, stream=stream),
+                  n_ids * (4 + H * 2 + H * 4), 1),
+    }
+
+    def step():
+        for fn, _, _ in ops.values():
+            fn()
+
+    step()
+    pkg.synchronize()
+    if args.ncu_steps > 0:
+        for _ in range(args.ncu_steps):
+            step()
+        pkg.synchronize()
+        print(json.dumps({"ncu_steps": args.ncu_steps, "launches_per_step": sum(n for _, _, n in ops.values())}), flush=True)
+        chain.close()
+        return
+    g_step = pkg.Graph(stream)
+    with g_step:
+        step()
+    timer = Timer(pkg, stream)
+
+    def replays(n):
+        barrier()
+        timer.start()
+        for _ in range(n):
+            g_step.launch()
+        timer.stop()
+        barrier()
+        return sharding.max_over_ranks(timer.ms(), dist)
+
+    sampler = ClockSampler(visible_gpu_index(local_rank)) if rank == 0 else None
+    if sampler:
+        time.sleep(0.3)
+    replays(max(3, args.warmup))
+    ms_total = replays(args.steps)
+    clocks = sampler.stop() if sampler else None
+    ms_per_step = ms_total / args.steps
+    value = world * T * args.steps / (ms_total * 1e-3)
+    sustained = None
+    if args.sustain_seconds > 0:
+        n = max(10, int(math.ceil(args.sustain_seconds * 1e3 / ms_per_step)))
+        s2 = ClockSampler(visible_gpu_index(local_rank)) if rank == 0 else None
+        ms2 = replays(n)
+        ck = s2.stop() if s2 else None
+        sustained = {"steps": n, "seconds": round(ms2 * 1e-3, 2), "ms_per_step": ms2 / n,
+                     "value": world * T * n / (ms2 * 1e-3), "clocks": ck}
+
+    # per op: [flush, op] replayed from a graph minus [flush] alone, so each launch starts cold
+    g_flush = pkg.Graph(stream)
+    pkg.check(lib.gptoss_flush_l2(flush.ptr, flush.nbytes, stream))
+    with g_flush:
+        pkg.check(lib.gptoss_flush_l2(flush.ptr, flush.nbytes, stream))
+    peak, peak_src = hbm_peak()
+    kernels = {}
+
+    def timed(g, n=10):
+        g.launch()
+        pkg.synchronize()
+        tot = 0.0
+        for _ in range(n):
+            timer.start()
+            g.launch()
+            timer.stop()
+            tot += timer.ms()
+        return tot / n
+
+    flush_ms = timed(g_flush)
+    for name, (fn, nbytes, launches) in ops.items():
+        g = pkg.Graph(stream)
+        with g:
+            pkg.check(lib.gptoss_flush_l2(flush.ptr, flush.nbytes, stream))
+            fn()
+        us = 1e3 * max(0.0, timed(g) - flush_ms)
+        g.close()
+        gbs = nbytes / (us * 1e-6) / 1e9 if us > 0 else 0.0
+        kernels[name] = {"launches_per_step": launches, "us_per_launch": round(us, 3), "bytes_per_launch": nbytes,
+                         "achieved_gbs": round(gbs, 1), "frac": round(gbs / peak, 4),
+                         "pct_of_nominal_8tbs": round(gbs / 80.0, 1)}
+    step_bytes = sum(k["bytes_per_launch"] for k in kernels.values())
+    top = max(kernels, key=lambda k: kernels[k]["us_per_launch"])
+    traffic, rec = ncu_traffic(top)
+
+    # e2e: ids from pinned host memory in, the three ops, picked ids back, stream synchronised
+    def e2e_step():
+        pkg.check(lib.gptoss_upload(ids.ptr, ids_host.ptr, n_ids * 4, stream))
+        g_step.launch()
+        pkg.check(lib.gptoss_download(picked_host.ptr, keys_out, T * 4, stream))
+        pkg.check(lib.gptoss_stream_synchronize(stream))
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        e2e_step()
+    e2e_s = sharding.max_over_ranks(time.perf_counter() - t0, dist)
+    barrier()
+
+    line = {
+        "metric": "layer_chain_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded, host-generated)",
+        "config": dict(work.describe(), l2="inputs larger than L2: every step sweeps 1.65 GB of logits; the per-op "
+                                           "times are taken behind an L2 flush"),
+        "sustained": sustained,
+        "e2e": {"value": world * T * args.steps / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": 4 * n_ids,
+                "d2h_bytes_per_step": 4 * T, "ms_per_step": 1e3 * e2e_s / args.steps,
+                "what": "gather ids from pinned host memory in, gptoss_add_rmsnorm + gptoss_argmax + gptoss_embed "
+                        "(one graph launch), picked ids out, stream synchronised every step"},
+        "gpu_launches": sum(k["launches_per_step"] for k in kernels.values()) * args.steps,
+        "launches_per_step": sum(k["launches_per_step"] for k in kernels.values()),
+        "roofline": {"kernel": top, "bound": "hbm", "achieved": kernels[top]["achieved_gbs"], "peak": peak,
+                     "unit": "GB/s", "frac": kernels[top]["frac"], "traffic": traffic, "traffic_record": rec,
+                     "peak_source": peak_src,
+                     "chain": {"bytes_per_step": step_bytes,
+                               "achieved_gbs": round(step_bytes / (ms_per_step * 1e-3) / 1e9, 1),
+                               "frac": round(step_bytes / (ms_per_step * 1e-3) / 1e9 / peak, 4)}},
+        "kernels": kernels, "clocks": clocks, "device": pkg.device_name(local_rank), "setup_s": round(setup_s, 1),
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu, n, el = run_cpu(work, args.cpu_seconds, None, 1)
+        line["cpu_baseline"] = {"value": cpu.T * n / el, "unit": "tokens/s", "cores": cpu.threads, "kind": cpu.kind,
+                                "tokens_per_pass": cpu.T, "ops_from_port": cpu.OPS_FROM_PORT,
+                                "sample": f"{n} passes in {el:.1f} s; " + cpu.describe()}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    chain.close()
+
+
 def main():
     args = parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.gpus > 1 and world == 1:
+    if args.gpus > 1 and world == 1 and args.impl == "ours":
         # launched by hand without torchrun: start one process per GPU
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
                "--master-addr", "127.0.0.1", "--master-port", "29533", os.path.abspath(__file__), *sys.argv[1:]]
         sys.exit(subprocess.call(cmd))
 
-    pkg = importlib.import_module(PKG)
-    pkg.load()
-
-    if args.impl == "reference":
-        reference_arm(pkg, args, rank)
+    work = Work(args, world if args.impl == "ours" else max(world, args.gpus), rank)
+    if args.impl == "reference":  # the CPU arm: oracle/ only, no CUDA library
+        reference_arm(args, work, rank)
         return
 
+    pkg = importlib.import_module(PKG)
+    pkg.load()
     dist = None
     if world > 1:
         import torch
@@ -348,6 +664,7 @@ def main():
     assert pkg.device_count() > local_rank, "no CUDA device for this rank"
     pkg.set_device(local_rank)
     sharding = importlib.import_module(PKG + ".sharding")
+    assert sharding.shard_range(16384, 8, 3, 1024) == shard_range(16384, 8, 3, 1024)
 
     def barrier():
         pkg.synchronize()
@@ -355,8 +672,19 @@ def main():
             dist.barrier()
         pkg.synchronize()
 
-    T = args.tokens_per_gpu
-    c = pkg.chain_config(args.model, pkg.F32 if args.fp32 else pkg.BF16, 4096)
+    def finish():
+        if dist is not None:
+            dist.barrier()
+            dist.destroy_process_group()
+
+    if work.config == 4:
+        vocab_ops(pkg, args, work, world, rank, local_rank, dist, sharding, barrier)
+        finish()
+        return
+
+    T = work.T
+    c = pkg.chain_config(work.model, pkg.F32 if work.fp32 else pkg.BF16, 4096)
+    c.n_layers = work.layers
     if args.vocab > 0:
         c.vocab = args.vocab
     if args.pdl:
@@ -372,7 +700,7 @@ def main():
     pos = pkg.PinnedArray(T, np.int32)
     nxt = pkg.PinnedArray(T, np.int32)
     tok.array[:] = pkg.synth_uniform_int(T, args.seed, 100 + rank, 0, c.vocab)
-    pos.array[:] = pkg.synth_uniform_int(T, args.seed, 200 + rank, 0, 4096)
+    pos.array[:] = work.pos_array()
     chain.upload(pkg.BUF_TOKENS, 0, tok.array)
     chain.upload(pkg.BUF_POS, 0, pos.array)
     setup_s = time.perf_counter() - t_setup
@@ -384,14 +712,45 @@ def main():
         print(json.dumps({"ncu_steps": args.ncu_steps, "launches_per_step": chain.launches_per_step(T),
                           "device_bytes": chain.device_bytes}), flush=True)
         chain.close()
+        finish()
         return
 
     lib = pkg.load()
-    import ctypes as C
-    ev = [C.c_void_p(), C.c_void_p()]
-    for e in ev:
-        pkg.check(lib.gptoss_event_create(C.byref(e)))
     stream = chain.stream
+    timer = Timer(pkg, stream)
+    # A step's inputs must not be served from L2.  With one seeded tensor set per layer a step reads
+    # far more than the cache holds; a small case (configuration 0: 64 tokens) is flushed instead.
+    step_bytes = sum(chain.kernel_bytes(k, T) * (c.n_layers if k in ("rope", "add_norm", "router", "swiglu", "combine") else 1)
+                     for k in pkg.KERNEL_KINDS)
+    use_flush = step_bytes < 4 * L2_BYTES
+    flush = pkg.DeviceBuffer(256 << 20) if use_flush else None
+
+    def replays(n, T_run, with_flush):
+        """Device ms of n graph replays of a T_run-row step (max over ranks)."""
+        barrier()
+        timer.start()
+        for _ in range(n):
+            if with_flush:
+                pkg.check(lib.gptoss_flush_l2(flush.ptr, flush.nbytes, stream))
+            chain.enqueue(T_run, True)
+        timer.stop()
+        barrier()
+        return sharding.max_over_ranks(timer.ms(), dist)
+
+    def flush_only(n):
+        barrier()
+        timer.start()
+        for _ in range(n):
+            pkg.check(lib.gptoss_flush_l2(flush.ptr, flush.nbytes, stream))
+        timer.stop()
+        barrier()
+        return sharding.max_over_ranks(timer.ms(), dist)
+
+    def timed_steps(n, T_run):
+        ms = replays(n, T_run, use_flush)
+        if use_flush:
+            ms = max(0.0, ms - flush_only(n))
+        return ms
 
     # ---- value: K graph replays, inputs resident, CUDA events on the launching stream.  Clocks are
     # sampled during exactly this region; a region that saw a thermal or hardware slowdown is
@@ -400,17 +759,9 @@ def main():
         sampler = ClockSampler(visible_gpu_index(local_rank)) if rank == 0 else None
         if sampler:
             time.sleep(0.3)  # nvidia-smi needs a moment before its first sample
-        for _ in range(max(3, args.warmup)):
-            chain.enqueue(T, True)
-        barrier()
-        pkg.check(lib.gptoss_event_record(ev[0], stream))
-        for _ in range(args.steps):
-            chain.enqueue(T, True)
-        pkg.check(lib.gptoss_event_record(ev[1], stream))
-        barrier()
-        ms = C.c_float()
-        pkg.check(lib.gptoss_event_elapsed_ms(ev[0], ev[1], C.byref(ms)))
-        return sharding.max_over_ranks(ms.value, dist), (sampler.stop() if sampler else None)
+        replays(max(3, args.warmup), T, use_flush)
+        ms = timed_steps(args.steps, T)
+        return ms, (sampler.stop() if sampler else None)
 
     SLOW = {"hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown"}
     ms_total, clocks = measure_value()
@@ -421,7 +772,20 @@ def main():
         if clocks is not None:
             clocks["remeasured_after"] = first
     ms_per_step = ms_total / args.steps
-    value = world * T * args.steps / (ms_total * 1e-3)
+    value = work.total * args.steps / (ms_total * 1e-3)
+
+    # ---- sustained: the same replays for seconds, so that the power limit's clock shows
+    sustained = None
+    if args.sustain_seconds > 0:
+        n = min(20000, max(10, int(math.ceil(args.sustain_seconds * 1e3 / max(ms_per_step, 1e-3)))))
+        sampler = ClockSampler(visible_gpu_index(local_rank)) if rank == 0 else None
+        ms2 = timed_steps(n, T)
+        ck = sampler.stop() if sampler else None
+        sustained = {"steps": n, "seconds": round(ms2 * 1e-3, 2), "ms_per_step": ms2 / n,
+                     "value": work.total * n / (ms2 * 1e-3), "clocks": ck,
+                     "ms_x_mhz": (round(ms2 / n * ck["sm_mhz"], 1) if ck and ck.get("sm_mhz") else None)}
+        if clocks and clocks.get("sm_mhz"):
+            sustained["burst_ms_x_mhz"] = round(ms_per_step * clocks["sm_mhz"], 1)
 
     # ---- e2e: the engine-step call with host buffers, wall clock
     for _ in range(3):
@@ -433,39 +797,73 @@ def main():
     e2e_s = time.perf_counter() - t0
     barrier()
     e2e_s = sharding.max_over_ranks(e2e_s, dist)
-    e2e_value = world * T * args.steps / e2e_s
+    e2e_value = work.total * args.steps / e2e_s
     # ---- the same steps as one wave with the bookkeeping on the GPU: prompts in before, output rows
     # back after, no per-step round trip (one-token prompts, so every step feeds the picked token back)
-    wave_steps = min(4 * args.steps, 1024, c.max_pos)  # a wave is long: its set-up and read-back are paid once
-    w_tok = np.ascontiguousarray(tok.array, np.int32)
-    w_off = np.arange(T + 1, dtype=np.int32)
-    w_out = np.empty((T, wave_steps + 2), np.int32)
-    w_total, w_ran = C.c_longlong(0), C.c_int(0)
+    device_loop = None
+    if work.config in (1, 3):
+        import ctypes as C
+        wave_steps = min(4 * args.steps, 1024, c.max_pos)  # a wave is long: its set-up and read-back are paid once
+        w_tok = np.ascontiguousarray(tok.array, np.int32)
+        w_off = np.arange(T + 1, dtype=np.int32)
+        w_out = np.empty((T, wave_steps + 2), np.int32)
+        w_total, w_ran = C.c_longlong(0), C.c_int(0)
 
-    def wave(steps):
-        pkg.check(lib.gptoss_chain_run_wave_on_device(chain.h, w_tok.ctypes.data, w_off.ctypes.data, T, steps,
-                                                      w_out.ctypes.data, C.byref(w_total), C.byref(w_ran)))
-        return int(w_ran.value)
+        def wave(steps):
+            pkg.check(lib.gptoss_chain_run_wave_on_device(chain.h, w_tok.ctypes.data, w_off.ctypes.data, T, steps,
+                                                          w_out.ctypes.data, C.byref(w_total), C.byref(w_ran)))
+            return int(w_ran.value)
 
-    wave(min(3, wave_steps))
-    barrier()
-    t0 = time.perf_counter()
-    wave_ran = wave(wave_steps)
-    wave_s = sharding.max_over_ranks(time.perf_counter() - t0, dist)
-    barrier()
-    device_loop = {"value": world * T * wave_ran / wave_s, "unit": "tokens/s", "steps": wave_ran,
-                   "ms_per_step": 1e3 * wave_s / max(1, wave_ran), "h2d_bytes": 8 * T + 4,
-                   "d2h_bytes": 4 * T * (wave_steps + 2) + 4 * T,
-                   "what": "gptoss_chain_run_wave_on_device: one wave of `steps` positions, token feedback and "
-                           "finished-row handling by a kernel behind each step, host queues 16 steps at a time"}
+        wave(min(3, wave_steps))
+        barrier()
+        t0 = time.perf_counter()
+        wave_ran = wave(wave_steps)
+        wave_s = sharding.max_over_ranks(time.perf_counter() - t0, dist)
+        barrier()
+        device_loop = {"value": world * T * wave_ran / wave_s, "unit": "tokens/s", "steps": wave_ran,
+                       "ms_per_step": 1e3 * wave_s / max(1, wave_ran), "h2d_bytes": 8 * T + 4,
+                       "d2h_bytes": 4 * T * (wave_steps + 2) + 4 * T,
+                       "what": "gptoss_chain_run_wave_on_device: one wave of `steps` positions, token feedback and "
+                               "finished-row handling by a kernel behind each step, host queues 16 steps at a time"}
+        chain.upload(pkg.BUF_POS, 0, pos.array)  # the wave left its own positions behind
 
     # ---- per-kernel device times: per kind, an event pair around its launches of a step
     prof = chain.profile(T, max(1, min(args.profile_steps, args.steps)), mode=2)
 
+    # ---- the literal shard of the decode configurations: one batch of 4096 tokens over the ranks
+    strong = literal = None
+    if work.config in (1, 3) and args.tokens_per_gpu is None:
+        batch = 4096
+        if world > 1:
+            b, e = sharding.shard_range(batch, world, rank)
+            Ts = e - b
+            replays(3, Ts, False)
+            n = max(args.steps, 50)
+            ms = replays(n, Ts, False)
+            strong = {"total_tokens": batch, "tokens_per_gpu": batch // world, "steps": n, "ms_per_step": ms / n,
+                      "value": batch * n / (ms * 1e-3), "unit": "tokens/s", "scaling": "strong",
+                      "what": "one 4096-token batch split by sharding.shard_range, each rank's share through the "
+                              "whole chain (graph replays, CUDA events, max over ranks)"}
+        else:
+            Ts = batch // 8
+            replays(3, Ts, False)
+            n = max(args.steps, 50)
+            ms = replays(n, Ts, False)
+            sb = sum(chain.kernel_bytes(k, Ts) * (c.n_layers if k in ("rope", "add_norm", "router", "swiglu", "combine") else 1)
+                     for k in pkg.KERNEL_KINDS)
+            peak0 = hbm_peak()[0]
+            literal = {"tokens_per_gpu": Ts, "steps": n, "ms_per_step": ms / n, "value": Ts * n / (ms * 1e-3),
+                       "unit": "tokens/s", "bytes_per_step": sb,
+                       "chain_frac": round(sb / (ms / n * 1e-3) / 1e9 / peak0, 4),
+                       "launches_per_step": chain.launches_per_step(Ts),
+                       "what": "this GPU's share when the 4096-token batch is split over 8 GPUs (512 tokens): each of "
+                               "the step's launches then moves a few MB and sits on the floor of a dependent launch"}
+
     # ---- the strictest reading of "end to end": every operand of every kernel comes from
     # host memory each step (done last: it overwrites the device-side stand-ins)
-    host_operands = None if (args.no_host_operands or args.fp32) else host_operand_steps(pkg, chain, c, T, sets, tok, pos, nxt,
-                                                                          barrier, sharding, dist, world)
+    host_operands = None
+    if work.config == 1 and not (args.no_host_operands or work.fp32):
+        host_operands = host_operand_steps(pkg, chain, c, T, sets, tok, pos, nxt, barrier, sharding, dist, world)
     peak, peak_src = hbm_peak()
     kernels = {}
     chain_bytes = 0
@@ -476,27 +874,37 @@ def main():
         b = chain.kernel_bytes(kind, T)
         us = 1e3 * kms / n
         gbs = b / (us * 1e-6) / 1e9
+        traffic, rec = ncu_traffic(kind)
         kernels[kind] = {"launches_per_step": per_step, "us_per_launch": round(us, 3), "bytes_per_launch": b,
                          "achieved_gbs": round(gbs, 1), "frac": round(gbs / peak, 4),
-                         "pct_of_nominal_8tbs": round(gbs / 80.0, 1), "share_of_step": None}
+                         "pct_of_nominal_8tbs": round(gbs / 80.0, 1), "share_of_step": None,
+                         "traffic_ncu_T4096": traffic, "traffic_record": rec}
         chain_bytes += b * per_step
     tot = sum(k["us_per_launch"] * k["launches_per_step"] for k in kernels.values())
     for k in kernels.values():
         k["share_of_step"] = round(k["us_per_launch"] * k["launches_per_step"] / tot, 4)
     top = max(kernels, key=lambda k: kernels[k]["share_of_step"])
     roofline = {"kernel": top, "bound": "hbm", "achieved": kernels[top]["achieved_gbs"], "peak": peak,
-                "unit": "GB/s", "frac": kernels[top]["frac"], "traffic": ncu_traffic(top),
+                "unit": "GB/s", "frac": kernels[top]["frac"],
+                "traffic": kernels[top]["traffic_ncu_T4096"] if T == 4096 else None,
                 "peak_source": peak_src,
                 "chain": {"bytes_per_step": chain_bytes,
                           "achieved_gbs": round(chain_bytes / (ms_per_step * 1e-3) / 1e9, 1),
                           "frac": round(chain_bytes / (ms_per_step * 1e-3) / 1e9 / peak, 4),
                           "pct_of_nominal_8tbs": round(chain_bytes / (ms_per_step * 1e-3) / 1e9 / 80.0, 1)}}
+    if sustained:
+        sustained["chain_frac"] = round(chain_bytes / (sustained["ms_per_step"] * 1e-3) / 1e9 / peak, 4)
 
+    cfg = work.describe()
+    cfg["l2"] = ("L2 flushed before every step (its inputs are smaller than the cache); the flush's own time, measured "
+                 "the same way, is subtracted" if use_flush else
+                 "inputs larger than L2: every layer reads its own seeded tensors, several GB per step")
     line = {
         "metric": "layer_chain_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32" if args.fp32 else "bf16", "data": "synthetic (seeded, host-generated)",
-        "config": workload_config(args, c),
+        "scaling": work.scaling, "vs_baseline": None, "dtype": "f32" if work.fp32 else "bf16",
+        "data": "synthetic (seeded, host-generated)", "config": cfg,
+        "sustained": sustained,
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": 8 * T, "d2h_bytes_per_step": 4 * T,
                 "ms_per_step": 1e3 * e2e_s / args.steps,
                 "what": "gptoss_chain_step: token ids + positions from pinned host memory in, picked tokens out, "
@@ -505,12 +913,14 @@ def main():
         "gpu_launches": chain.launches_per_step(T) * args.steps,
         "launches_per_step": chain.launches_per_step(T),
         "roofline": roofline, "kernels": kernels, "clocks": clocks,
+        "strong": strong, "literal_shard": literal, "wait_giveups": int(lib.gptoss_wait_giveups()),
         "device": pkg.device_name(local_rank), "device_bytes": chain.device_bytes, "setup_s": round(setup_s, 1),
     }
 
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        cpu, n, el = run_cpu(pkg, args, args.cpu_seconds, None, 1)
+        cpu, n, el = run_cpu(work, args.cpu_seconds, None, 1)
         line["cpu_baseline"] = {"value": cpu.T * n / el, "unit": "tokens/s", "cores": cpu.threads, "kind": cpu.kind,
+                                "tokens_per_pass": cpu.T, "ops_from_port": cpu.OPS_FROM_PORT,
                                 "sample": f"{n} passes in {el:.1f} s; " + cpu.describe()}
         # the reference as it ships runs these ops serially per token: the same pass on one thread
         cpu.threads = 1
@@ -521,9 +931,7 @@ def main():
     if rank == 0:
         print(json.dumps(line), flush=True)
     chain.close()
-    if dist is not None:
-        dist.barrier()
-        dist.destroy_process_group()
+    finish()
 
 
 if __name__ == "__main__":

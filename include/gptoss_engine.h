@@ -54,6 +54,17 @@ GPTOSS_API int gptoss_event_elapsed_ms(gptoss_event_t start, gptoss_event_t stop
  * cache) so that the next kernel finds none of its inputs cached. */
 GPTOSS_API int gptoss_flush_l2(void *scratch, size_t bytes, gptoss_stream_t stream);
 
+/* Stream capture into a replayable graph, the way the reference engine would batch a step's
+ * launches (it has no graphs: HIP launches one kernel at a time, gpu_engine.hpp:459-690).
+ * Between gptoss_graph_begin and gptoss_graph_end every launch made by this thread on `stream`
+ * is recorded instead of run; a kernel should have been launched once outside capture first.
+ * The stream must be one made by gptoss_stream_create (not the default stream). */
+typedef void *gptoss_graph_t;
+GPTOSS_API int gptoss_graph_begin(gptoss_stream_t stream);
+GPTOSS_API int gptoss_graph_end(gptoss_stream_t stream, gptoss_graph_t *graph);
+GPTOSS_API int gptoss_graph_launch(gptoss_graph_t graph, gptoss_stream_t stream);
+GPTOSS_API int gptoss_graph_destroy(gptoss_graph_t graph);
+
 /* ---- RoPE tables --------------------------------------------------------------
  * cos/sin of every position 0..n_pos-1, [n_pos, head_dim/2] fp32 each, computed
  * on the host with the C library's powf/logf/cosf/sinf exactly as the engine

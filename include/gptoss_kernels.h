@@ -90,6 +90,13 @@ GPTOSS_API const char *gptoss_status_string(int status);
 /* The cudaError_t (as int) of the last failed CUDA call made by this thread in
  * this library, 0 if none. */
 GPTOSS_API int gptoss_last_cuda_error(void);
+/* How many times, on the current device since the library was loaded, a kernel gave up a
+ * bounded wait for one of its own bulk copies (about half a second without the copy
+ * arriving) and stopped early instead of hanging the GPU; the output of that launch is
+ * incomplete.  0 in normal operation; -1 if the counter cannot be read.  Synchronises with
+ * the device.  No counterpart in the reference, whose kernels never wait in software on this
+ * path (its expert-parallel ep_wait_kernel spins without a limit, kernels/moe_ep.hpp). */
+GPTOSS_API long gptoss_wait_giveups(void);
 /* How many launches this thread has made so far that fell back to a scalar kernel
  * (sizes that are not multiples of 8 elements, bases that are not 16-byte aligned,
  * rows too wide for the vector kernels).  Results are the same; the speed is not.  A

@@ -63,6 +63,7 @@ PROTOTYPES = {
     "gptoss_status_string": (C.c_char_p, [_i]),
     "gptoss_last_cuda_error": (_i, []),
     "gptoss_generic_launch_count": (_l, []),
+    "gptoss_wait_giveups": (_l, []),
     "gptoss_embed": (_i, [_p, _i, _p, _i, _i, _p, _p, _i, _i, _u]),
     "gptoss_embed_rmsnorm": (_i, [_p, _i, _p, _i, _i, _p, _p, _p, _p, _i, _i, _u]),
     "gptoss_add_rmsnorm": (_i, [_p, _i, _p, _p, _i, _p, _p, _i, _i, _u]),
@@ -99,6 +100,10 @@ PROTOTYPES = {
     "gptoss_event_synchronize": (_i, [_p]),
     "gptoss_event_elapsed_ms": (_i, [_p, _p, C.POINTER(_f)]),
     "gptoss_flush_l2": (_i, [_p, _z, _p]),
+    "gptoss_graph_begin": (_i, [_p]),
+    "gptoss_graph_end": (_i, [_p, C.POINTER(_p)]),
+    "gptoss_graph_launch": (_i, [_p, _p]),
+    "gptoss_graph_destroy": (_i, [_p]),
     "gptoss_build_rope_tables": (_i, [_i, _i, _f, _f, _f, _f, _f, _p, _p]),
     "gptoss_synth_normal": (_i, [_p, _i, _z, C.c_uint64, C.c_uint64, _f, _f, _i]),
     "gptoss_synth_uniform_int": (_i, [_p, _z, C.c_uint64, C.c_uint64, _i, _i]),
@@ -381,6 +386,56 @@ class PinnedArray:
             self.free()
         except Exception:
             pass
+
+
+class Stream:
+    """A stream of this library (gptoss_stream_create)."""
+
+    def __init__(self):
+        h = _p()
+        check(load().gptoss_stream_create(C.byref(h)), "stream_create")
+        self.h = h.value
+
+    def synchronize(self):
+        check(load().gptoss_stream_synchronize(self.h), "stream_synchronize")
+
+    def close(self):
+        if getattr(self, "h", None):
+            load().gptoss_stream_destroy(self.h)
+            self.h = None
+
+
+class Graph:
+    """Launches captured on a stream, replayable with one call (gptoss_graph_*).
+
+        g = Graph(stream)
+        with g:             # everything launched on `stream` by this thread is recorded
+            pkg.swiglu(..., stream=stream)
+        g.launch()
+    """
+
+    def __init__(self, stream):
+        self.stream, self.h = stream, None
+
+    def __enter__(self):
+        check(load().gptoss_graph_begin(self.stream), "graph_begin")
+        return self
+
+    def __exit__(self, exc_type, exc, tb):
+        h = _p()
+        st = load().gptoss_graph_end(self.stream, C.byref(h))
+        self.h = h.value
+        if exc_type is None:
+            check(st, "graph_end")
+        return False
+
+    def launch(self):
+        check(load().gptoss_graph_launch(self.h, self.stream), "graph_launch")
+
+    def close(self):
+        if self.h:
+            load().gptoss_graph_destroy(self.h)
+            self.h = None
 
 
 def chain_config(which: int, act_dtype: int = BF16, max_pos: int = 4096) -> ChainConfig:

@@ -29,7 +29,6 @@ __device__ __forceinline__ Vec8 smem_chunk_f32(const unsigned char *p) {
 template <int KM> struct Routing { // weights and expert ids of one token
   float w[KM];
   int e[KM];
-  bool here[KM]; // the pair's expert row exists (own_row entry >= 0)
 };
 template <int KM> struct RowIds { // where the token's expert rows are, and whether it is live
   int row[KM];
@@ -68,10 +67,10 @@ __global__ void combine_rows(float *x, const ZT *__restrict__ Z, const int *__re
   // loading every word, lane L of each warp loads one word of a token and the
   // warp shares them with shuffles at the point of use:
   //   "ids" word:     L < k: own_row[token*k + L];   L == k: topk_e[token*k] (liveness)
-  //   "routing" word: L < k: topk_w[token*k + L];    k <= L < 2k: topk_e[token*k + L - k];
-  //                   2k <= L < 3k: own_row[token*k + L - 2k]
+  //   "routing" word: L < k: topk_w[token*k + L];    k <= L < 2k: topk_e[token*k + L - k]
   // A pair whose own_row entry is negative has no expert row here (the grouping step writes
-  // -1 for experts outside its range): nothing is copied for it and it adds nothing.
+  // -1 for experts outside its range): nothing is read for it; its part of the stage is
+  // filled with zeros instead, so it adds nothing and the sum needs no test per pair.
   const int lane = threadIdx.x & 31;
   auto load_ids_word = [&](long row) -> uint32_t {
     if (lane < k)
@@ -85,8 +84,6 @@ __global__ void combine_rows(float *x, const ZT *__restrict__ Z, const int *__re
       return __float_as_uint(__ldg(topk_w + (size_t)row * k + lane));
     if (lane < 2 * k)
       return (uint32_t)__ldg(topk_e + (size_t)row * k + lane - k);
-    if (lane < 3 * k)
-      return own_row ? (uint32_t)__ldg(own_row + (size_t)row * k + lane - 2 * k) : 0u;
     return 0u;
   };
   auto spread_ids = [&](uint32_t word) {
@@ -103,7 +100,6 @@ __global__ void combine_rows(float *x, const ZT *__restrict__ Z, const int *__re
     for (int j = 0; j < KM; j++) {
       r.w[j] = __uint_as_float(__shfl_sync(0xffffffffu, word, j < k ? j : 0));
       r.e[j] = j < k ? (int)__shfl_sync(0xffffffffu, word, k + j) : 0x7fffffff;
-      r.here[j] = j < k && (int)__shfl_sync(0xffffffffu, word, j < k ? 2 * k + j : 0) >= 0;
     }
     return r;
   };
@@ -119,12 +115,18 @@ __global__ void combine_rows(float *x, const ZT *__restrict__ Z, const int *__re
         if (ids.live) {
 #pragma unroll
           for (int j = 0; j < KM; j++)
-            if (j < k && ids.row[j] >= 0) {
-              const ZT *zr = Z + (size_t)ids.row[j] * H + (size_t)chunk * 8;
+            if (j < k) {
               unsigned char *sz = sx + x_bytes + (size_t)j * z_bytes + (size_t)chunk * 8 * SZ;
-              cp_async16(sz, zr);
-              if constexpr (SZ == 4)
-                cp_async16(sz + 16, zr + 4);
+              if (ids.row[j] >= 0) {
+                const ZT *zr = Z + (size_t)ids.row[j] * H + (size_t)chunk * 8;
+                cp_async16(sz, zr);
+                if constexpr (SZ == 4)
+                  cp_async16(sz + 16, zr + 4);
+              } else { // no row here: zeros (this thread is the only reader of the chunk)
+                *reinterpret_cast<uint4 *>(sz) = make_uint4(0u, 0u, 0u, 0u);
+                if constexpr (SZ == 4)
+                  *reinterpret_cast<uint4 *>(sz + 16) = make_uint4(0u, 0u, 0u, 0u);
+              }
             }
         }
       }
@@ -206,16 +208,13 @@ __global__ void combine_rows(float *x, const ZT *__restrict__ Z, const int *__re
             // position jj of the summation order takes choice ord[jj]
             int j = jj;
             float wj = cur.w[jj];
-            bool here = cur.here[jj];
             if (EXACT) {
               j = ord[jj];
 #pragma unroll
               for (int q = 0; q < KM; q++)
                 if (q == j)
-                  wj = cur.w[q], here = cur.here[q];
+                  wj = cur.w[q];
             }
-            if (!here)
-              continue;
             const unsigned char *sz = sx + x_bytes + (size_t)j * z_bytes + (size_t)chunk * 8 * SZ;
             Vec8 z;
             if constexpr (SZ == 2)

@@ -190,6 +190,72 @@ template <int N> __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
+// ---- bulk asynchronous copies (one instruction per row) ----------------------------
+//
+// cp.async.bulk moves a whole contiguous run (a row of 5-20 KB here) between global and
+// this block's shared memory with one instruction issued by one thread; the copy engine
+// does the address generation that the 16-byte cp.async form spends hundreds of LSU
+// instructions per row on.  A load signals an mbarrier in shared memory with the bytes it
+// delivered; a store belongs to the issuing thread's bulk group.  Both ends must be 16-byte
+// aligned and the size a multiple of 16.  Source and destination are this GPU's memory and
+// this block's shared memory only.
+//
+// Waiting on an mbarrier is the one software wait in the library, so it is bounded: after
+// kWaitCycles SM clocks (half a second) without the phase completing, mbar_wait gives up and returns false;
+// the kernel then counts the event in a device word (wait_giveups_word(), read back by
+// gptoss_wait_giveups) and winds down instead of hanging the GPU.
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(void *bar, unsigned arrivals) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(arrivals) : "memory");
+}
+// Makes freshly initialised barriers visible to the copy engine (then __syncthreads()).
+__device__ __forceinline__ void mbar_init_fence() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+// One arrival that also announces `bytes` of copies to come in this phase.
+__device__ __forceinline__ void mbar_expect(void *bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+constexpr long long kWaitCycles = 1000000000ll; // about half a second of SM clock
+__device__ __forceinline__ bool mbar_wait(void *bar, uint32_t parity) {
+  const uint32_t a = smem_u32(bar);
+  const long long t0 = clock64();
+  for (;;) {
+    uint32_t done;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(done)
+                 : "r"(a), "r"(parity)
+                 : "memory");
+    if (done)
+      return true;
+    if (clock64() - t0 > kWaitCycles)
+      return false;
+  }
+}
+__device__ __forceinline__ void bulk_load(void *smem_dst, const void *gmem_src, uint32_t bytes, void *bar) {
+  asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void bulk_store(void *gmem_dst, const void *smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gmem_dst), "r"(smem_u32(smem_src)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Until at most N of this thread's bulk groups are still reading their shared-memory source.
+template <int N> __device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+// Orders this thread's ordinary shared-memory writes before later reads by the copy engine.
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// Device word counting bounded waits that ran out (current device); nullptr if unavailable.
+unsigned int *wait_giveups_word();
+
 // Ring depth for a row kernel whose stage takes stage_bytes of shared memory:
 // deep enough to keep >= ~100 KB per SM in flight, shallow enough that two or
 // more blocks still fit on an SM (227 KB); 0 if even two stages do not fit.

@@ -198,8 +198,39 @@ int gptoss_flush_l2(void *scratch, size_t bytes, gptoss_stream_t stream) {
   if (!scratch || bytes < 16 || !aligned16(scratch))
     return GPTOSS_ERR_BAD_ARG;
   static unsigned salt = 0;
-  flush_kernel<<<sm_count() * 4, 512, 0, as_stream(stream)>>>((uint4 *)scratch, bytes / 16, ++salt);
+  launch_kernel(flush_kernel, dim3(sm_count() * 4), dim3(512), 0, as_stream(stream), (uint4 *)scratch, bytes / 16,
+                ++salt);
   return launch_status();
+}
+
+// Stream capture into an executable graph: what the chain driver does for a whole step, for
+// callers (and the benchmark) that want to replay a few launches of their own without the
+// per-launch host cost.
+int gptoss_graph_begin(gptoss_stream_t stream) {
+  return cuda_status(cudaStreamBeginCapture(as_stream(stream), cudaStreamCaptureModeThreadLocal));
+}
+int gptoss_graph_end(gptoss_stream_t stream, gptoss_graph_t *graph) {
+  if (!graph)
+    return GPTOSS_ERR_BAD_ARG;
+  *graph = nullptr;
+  cudaGraph_t g = nullptr;
+  int st = cuda_status(cudaStreamEndCapture(as_stream(stream), &g));
+  if (st != GPTOSS_OK || !g)
+    return st != GPTOSS_OK ? st : GPTOSS_ERR_CUDA;
+  cudaGraphExec_t exec = nullptr;
+  st = cuda_status(cudaGraphInstantiate(&exec, g, 0));
+  (void)cudaGraphDestroy(g);
+  if (st == GPTOSS_OK)
+    *graph = exec;
+  return st;
+}
+int gptoss_graph_launch(gptoss_graph_t graph, gptoss_stream_t stream) {
+  if (!graph)
+    return GPTOSS_ERR_BAD_ARG;
+  return cuda_status(cudaGraphLaunch((cudaGraphExec_t)graph, as_stream(stream)));
+}
+int gptoss_graph_destroy(gptoss_graph_t graph) {
+  return graph ? cuda_status(cudaGraphExecDestroy((cudaGraphExec_t)graph)) : GPTOSS_OK;
 }
 
 int gptoss_build_rope_tables(int n_pos, int head_dim, float theta, float factor, float orig_ctx,

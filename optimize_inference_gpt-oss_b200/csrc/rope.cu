@@ -29,6 +29,18 @@ template <typename T> __device__ __forceinline__ Vec8 smem_load8(const unsigned 
   }
 }
 
+template <typename T> __device__ __forceinline__ void smem_store8(unsigned char *p, const Vec8 &v) {
+  if constexpr (sizeof(T) == 2) {
+    *reinterpret_cast<uint4 *>(p) = make_uint4(pack_bf16(v.v[0], v.v[1]), pack_bf16(v.v[2], v.v[3]),
+                                               pack_bf16(v.v[4], v.v[5]), pack_bf16(v.v[6], v.v[7]));
+  } else {
+    *reinterpret_cast<uint4 *>(p) = make_uint4(__float_as_uint(v.v[0]), __float_as_uint(v.v[1]),
+                                               __float_as_uint(v.v[2]), __float_as_uint(v.v[3]));
+    *reinterpret_cast<uint4 *>(p + 16) = make_uint4(__float_as_uint(v.v[4]), __float_as_uint(v.v[5]),
+                                                    __float_as_uint(v.v[6]), __float_as_uint(v.v[7]));
+  }
+}
+
 template <bool EXACT, bool FMA>
 __device__ __forceinline__ void rotate8(Vec8 &a, Vec8 &b, const Vec8 &c, const Vec8 &s) {
 #pragma unroll
@@ -221,6 +233,154 @@ __global__ void bias_rope_rows(const IT *qkv_in, long in_stride, const float *__
   cp_async_wait<0>();
 }
 
+// The same operation with every row moved by the copy engine.  One thread asks for a whole
+// qkv row and the cos and sin rows of its position with three bulk copies that signal the
+// stage's mbarrier; the block rotates the row out of shared memory into one of OUTS output
+// buffers, also in shared memory, and one bulk store sends that to global memory.  Rows in
+// flight per block are set by the ring (STAGES) and cost no registers or LSU instructions;
+// the bias slice stays in registers as above.  A stage is refilled right after the barrier
+// that ends its row's reads; an output buffer is reused only after the bulk store that read
+// it has finished reading (the issuing thread checks before the barrier of the row before).
+#ifndef GPTOSS_ROPE_BULK_STAGES
+#define GPTOSS_ROPE_BULK_STAGES 3
+#endif
+#ifndef GPTOSS_ROPE_BULK_OUTS
+#define GPTOSS_ROPE_BULK_OUTS 2
+#endif
+#ifdef GPTOSS_ROPE_BULK_MINBLOCKS // blocks of up to 320 threads (the models' row) per SM to compile for
+#define GPTOSS_ROPE_BULK_BOUNDS __launch_bounds__(320, GPTOSS_ROPE_BULK_MINBLOCKS)
+#else
+#define GPTOSS_ROPE_BULK_BOUNDS
+#endif
+template <typename IT, typename OT, bool EXACT, bool FMA, int STAGES, int OUTS>
+__global__ void GPTOSS_ROPE_BULK_BOUNDS bias_rope_rows_bulk(const IT *qkv_in, long in_stride, const float *__restrict__ bias,
+                                    const int *__restrict__ pos, int pos_scalar,
+                                    const float *__restrict__ cos_tab, const float *__restrict__ sin_tab,
+                                    int n_pos, int n_rot_heads, int n_heads, int head_dim, OT *qkv_out,
+                                    long out_stride, int T, unsigned int *giveups) {
+  pdl_prologue();
+  constexpr int SI = sizeof(IT), SO = sizeof(OT);
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ __align__(8) unsigned long long full[STAGES];
+  const int half = head_dim >> 1, pieces = half >> 3, items = n_heads * pieces;
+  const uint32_t in_bytes = (uint32_t)n_heads * head_dim * SI, out_bytes = (uint32_t)n_heads * head_dim * SO;
+  const uint32_t trig_bytes = (uint32_t)half * 4, stage_bytes = in_bytes + 2 * trig_bytes;
+  unsigned char *outs = smem + (size_t)STAGES * stage_bytes;
+
+  const bool active = (int)threadIdx.x < items;
+  const int head = active ? threadIdx.x / pieces : 0, piece = active ? threadIdx.x - head * pieces : 0;
+  const size_t lo = (size_t)head * head_dim + piece * 8, hi = lo + half;
+  const bool rotates = head < n_rot_heads;
+
+  const long step = gridDim.x;
+  long row = blockIdx.x;
+  if (row >= T)
+    return;
+  auto position = [&](long r) {
+    int p = pos ? __ldg(pos + r) : pos_scalar;
+    return p < 0 ? 0 : (p >= n_pos ? n_pos - 1 : p);
+  };
+  auto issue = [&](long r, int stage, int p) { // one thread
+    unsigned char *sr = smem + (size_t)stage * stage_bytes;
+    mbar_expect(&full[stage], stage_bytes);
+    bulk_load(sr, qkv_in + (size_t)r * in_stride, in_bytes, &full[stage]);
+    bulk_load(sr + in_bytes, cos_tab + (size_t)p * half, trig_bytes, &full[stage]);
+    bulk_load(sr + in_bytes + trig_bytes, sin_tab + (size_t)p * half, trig_bytes, &full[stage]);
+  };
+  int next_pos = 0; // thread 0: position of the row the next refill asks for
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES; s++)
+      mbar_init(&full[s], 1);
+    mbar_init_fence();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int first[STAGES + 1]; // all position reads before the first copy is asked for
+#pragma unroll
+    for (int s = 0; s <= STAGES; s++)
+      first[s] = row + s * step < T ? position(row + s * step) : 0;
+#pragma unroll
+    for (int s = 0; s < STAGES; s++)
+      if (row + s * step < T)
+        issue(row + s * step, s, first[s]);
+    next_pos = first[STAGES];
+  }
+  Vec8 ba, bb;
+#pragma unroll
+  for (int i = 0; i < 8; i++)
+    ba.v[i] = bb.v[i] = 0.0f;
+  if (bias && active) {
+    ba = load8<kTable>(bias, lo);
+    bb = load8<kTable>(bias, hi);
+  }
+
+  int stage = 0, ob = 0;
+  uint32_t parity = 0;
+  bool gave_up = false;
+  for (; row < T; row += step) {
+    if (!mbar_wait(&full[stage], parity)) {
+      gave_up = true;
+      break;
+    }
+    unsigned char *sr = smem + (size_t)stage * stage_bytes;
+    unsigned char *so = outs + (size_t)ob * out_bytes;
+    if (active) {
+      Vec8 a = smem_load8<IT>(sr + lo * SI), b = smem_load8<IT>(sr + hi * SI);
+      if (bias) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          a.v[i] = __fadd_rn(a.v[i], ba.v[i]);
+          b.v[i] = __fadd_rn(b.v[i], bb.v[i]);
+        }
+      }
+      if (rotates) {
+        const Vec8 c = smem_load8<float>(sr + in_bytes + (size_t)piece * 32);
+        const Vec8 sn = smem_load8<float>(sr + in_bytes + trig_bytes + (size_t)piece * 32);
+        rotate8<EXACT, FMA>(a, b, c, sn);
+      }
+      smem_store8<OT>(so + lo * SO, a);
+      smem_store8<OT>(so + hi * SO, b);
+    }
+    fence_async_smem();
+    if (threadIdx.x == 0)
+      bulk_wait_read<OUTS - 2>(); // the buffer the next row writes is no longer being read
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      bulk_store(qkv_out + (size_t)row * out_stride, so, out_bytes);
+      bulk_commit();
+      const long refill = row + (long)STAGES * step;
+      if (refill < T) {
+        issue(refill, stage, next_pos);
+        if (refill + step < T)
+          next_pos = position(refill + step);
+      }
+    }
+    ob = ob + 1 == OUTS ? 0 : ob + 1;
+    if (++stage == STAGES) {
+      stage = 0;
+      parity ^= 1;
+    }
+  }
+  if (threadIdx.x == 0) {
+    bulk_wait_read<0>(); // shared memory must outlive the stores that read it
+    if (gave_up) {
+      if (giveups)
+        atomicAdd(giveups, 1u);
+      // copies that were asked for and not consumed: each gets one more bounded chance to
+      // land before the block, and with it their destination, goes away
+      for (int k = 0; k < STAGES; k++) {
+        if (row + (long)k * step < T)
+          (void)mbar_wait(&full[stage], parity);
+        if (++stage == STAGES) {
+          stage = 0;
+          parity ^= 1;
+        }
+      }
+    }
+  }
+}
+
 // Any head_dim (even) and alignment: one rotation pair per thread step.
 template <typename IT, typename OT, bool EXACT, bool FMA>
 __global__ void bias_rope_rows_generic(const IT *qkv_in, long in_stride,
@@ -290,6 +450,26 @@ int launch_pipe(cudaStream_t s, const Args &a, int threads, size_t smem) {
   return launch_status();
 }
 
+template <typename IT, typename OT, bool EXACT, bool FMA>
+int launch_bulk(cudaStream_t s, const Args &a, int threads) {
+  constexpr int STAGES = GPTOSS_ROPE_BULK_STAGES, OUTS = GPTOSS_ROPE_BULK_OUTS;
+  static_assert(STAGES >= 1 && OUTS >= 2, "ring of at least one row, two output buffers");
+  auto k = bias_rope_rows_bulk<IT, OT, EXACT, FMA, STAGES, OUTS>;
+  const size_t width = (size_t)(a.n_q + 2 * a.n_kv) * a.head_dim;
+  const size_t smem = STAGES * (width * sizeof(IT) + (size_t)a.head_dim * 4) + OUTS * width * sizeof(OT);
+#ifdef GPTOSS_ROPE_BULK_MINBLOCKS
+  if (threads > 320)
+    return GPTOSS_ERR_UNSUPPORTED;
+#endif
+  const int per_sm = smem <= 200 * 1024 ? blocks_per_sm_smem(k, threads, smem) : 0;
+  if (per_sm < 1)
+    return GPTOSS_ERR_UNSUPPORTED;
+  launch_kernel(k, dim3(row_grid(a.T, per_sm)), dim3(threads), smem, s, static_cast<const IT *>(a.in), a.in_stride,
+                a.bias, a.pos, a.pos_scalar, a.cos_tab, a.sin_tab, a.n_pos, a.n_q + a.n_kv, a.n_q + 2 * a.n_kv,
+                a.head_dim, static_cast<OT *>(a.out), a.out_stride, a.T, wait_giveups_word());
+  return launch_status();
+}
+
 template <typename IT, typename OT, bool EXACT, bool FMA> int launch(cudaStream_t s, const Args &a) {
   const int n_heads = a.n_q + 2 * a.n_kv, n_rot = a.n_q + a.n_kv;
   const bool vec = a.head_dim % 16 == 0 && aligned16(a.in) && aligned16(a.out) &&
@@ -305,6 +485,13 @@ template <typename IT, typename OT, bool EXACT, bool FMA> int launch(cudaStream_
     // rings (3 and 4 rows, which fit) measured slower on B200 -- 15.3 against 14.8 us per launch at
     // 4096 rows -- as did capping registers for a fourth resident block.
     int st = GPTOSS_ERR_UNSUPPORTED;
+#ifdef GPTOSS_ROPE_BULK
+    if (!a.cache.kc) {
+      st = launch_bulk<IT, OT, EXACT, FMA>(s, a, threads);
+      if (st != GPTOSS_ERR_UNSUPPORTED)
+        return st;
+    }
+#endif
     if (stage_bytes * 2 <= 220 * 1024) {
       if (a.cache.kc) { // with the cache write: 64-wide heads only, 16-byte key stores
         if (a.head_dim == 64 && aligned16(a.cache.kc))

@@ -28,6 +28,27 @@ int sm_count() {
   return n;
 }
 
+// Bounded waits that ran out, per device; kernels get the word's address as an argument.
+static __device__ unsigned int g_wait_giveups;
+
+unsigned int *wait_giveups_word() {
+  static std::atomic<unsigned int *> cached[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64)
+    return nullptr;
+  unsigned int *p = cached[dev].load(std::memory_order_acquire);
+  if (!p) {
+    void *q = nullptr;
+    if (cudaGetSymbolAddress(&q, g_wait_giveups) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return nullptr;
+    }
+    p = static_cast<unsigned int *>(q);
+    cached[dev].store(p, std::memory_order_release);
+  }
+  return p;
+}
+
 int occupancy_cached(const void *kernel, int threads, size_t smem) {
   struct Entry {
     const void *fn;
@@ -95,3 +116,10 @@ extern "C" const char *gptoss_status_string(int status) {
 }
 
 extern "C" int gptoss_last_cuda_error(void) { return gptoss::g_last_cuda_error; }
+
+extern "C" long gptoss_wait_giveups(void) {
+  unsigned int *p = gptoss::wait_giveups_word(), v = 0;
+  if (!p || cudaMemcpy(&v, p, sizeof v, cudaMemcpyDeviceToHost) != cudaSuccess)
+    return -1;
+  return (long)v;
+}

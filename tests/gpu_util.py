@@ -29,6 +29,15 @@ def rel_err(got, want) -> float:
     return float(np.max(np.abs(got - want) / np.maximum(np.abs(want), floor_of(want))))
 
 
+def rel_err_unfloored(got, want) -> float:
+    """max |got - want| / |want| over the elements whose reference is not zero: the plain
+    relative error, with no floor under small references."""
+    got = np.asarray(got, np.float64).ravel()
+    want = np.asarray(want, np.float64).ravel()
+    nz = want != 0
+    return float(np.max(np.abs(got[nz] - want[nz]) / np.abs(want[nz]))) if nz.any() else 0.0
+
+
 def n_bit_diff(a, b) -> int:
     a, b = np.ascontiguousarray(a), np.ascontiguousarray(b)
     v = {4: np.uint32, 2: np.uint16}[a.dtype.itemsize]
