@@ -97,6 +97,19 @@ GPTOSS_API int gptoss_last_cuda_error(void);
  * the device.  No counterpart in the reference, whose kernels never wait in software on this
  * path (its expert-parallel ep_wait_kernel spins without a limit, kernels/moe_ep.hpp). */
 GPTOSS_API long gptoss_wait_giveups(void);
+/* The checked build of the library (compiled with -DGPTOSS_BOUNDS; build.py makes it as
+ * libgptoss_b200_bounds.so) stands in for a memory checker: it knows the device allocations
+ * made through gptoss_device_alloc and the chain, refuses (GPTOSS_ERR_BAD_ARG, nothing
+ * launched) a call whose shape arguments would walk a pointer past the end of its allocation,
+ * and has the kernels skip and count any row or expert number read from device data that
+ * points outside the array it indexes.  gptoss_bounds_enabled: 1 in that build, 0 otherwise.
+ * gptoss_bounds_violations: refused calls plus skipped accesses so far (0 in the ordinary
+ * build; -1 if the device counter cannot be read).  gptoss_bounds_checked_spans: how many
+ * pointer arguments have been checked against a known allocation.  The reference has no
+ * counterpart; its tests rely on canaries around outputs (tests/small_kernels_test.cpp). */
+GPTOSS_API int gptoss_bounds_enabled(void);
+GPTOSS_API long gptoss_bounds_violations(void);
+GPTOSS_API long gptoss_bounds_checked_spans(void);
 /* How many launches this thread has made so far that fell back to a scalar kernel
  * (sizes that are not multiples of 8 elements, bases that are not 16-byte aligned,
  * rows too wide for the vector kernels).  Results are the same; the speed is not.  A

@@ -64,6 +64,9 @@ PROTOTYPES = {
     "gptoss_last_cuda_error": (_i, []),
     "gptoss_generic_launch_count": (_l, []),
     "gptoss_wait_giveups": (_l, []),
+    "gptoss_bounds_enabled": (_i, []),
+    "gptoss_bounds_violations": (_l, []),
+    "gptoss_bounds_checked_spans": (_l, []),
     "gptoss_embed": (_i, [_p, _i, _p, _i, _i, _p, _p, _i, _i, _u]),
     "gptoss_embed_rmsnorm": (_i, [_p, _i, _p, _i, _i, _p, _p, _p, _p, _i, _i, _u]),
     "gptoss_add_rmsnorm": (_i, [_p, _i, _p, _p, _i, _p, _p, _i, _i, _u]),

@@ -43,9 +43,9 @@ def _newer(target: str, deps) -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def _compile(src: str, verbose: bool) -> str:
-    obj = os.path.join(OBJ, src[:-3] + ".o")
-    cmd = [NVCC, *ARCH, *CFLAGS, "-c", os.path.join(CSRC, src), "-o", obj]
+def _compile(src: str, verbose: bool, obj_dir: str = OBJ, defines=()) -> str:
+    obj = os.path.join(obj_dir, src[:-3] + ".o")
+    cmd = [NVCC, *ARCH, *CFLAGS, *defines, "-c", os.path.join(CSRC, src), "-o", obj]
     if verbose:
         cmd.insert(1, "-Xptxas=-v")
         print(" ".join(cmd), flush=True)
@@ -57,25 +57,37 @@ def _compile(src: str, verbose: bool) -> str:
     return obj
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    os.makedirs(OBJ, exist_ok=True)
+def build(force: bool = False, verbose: bool = False, lib: str = LIB, obj_dir: str = OBJ, defines=()) -> str:
+    os.makedirs(obj_dir, exist_ok=True)
     hdrs = _headers()
     todo, objs = [], []
     for s in _sources():
-        obj = os.path.join(OBJ, s[:-3] + ".o")
+        obj = os.path.join(obj_dir, s[:-3] + ".o")
         objs.append(obj)
         if force or _newer(obj, [os.path.join(CSRC, s), *hdrs]):
             todo.append(s)
     if todo:
         with cf.ThreadPoolExecutor(max_workers=min(8, len(todo))) as ex:
-            list(ex.map(lambda s: _compile(s, verbose), todo))
-    if todo or not os.path.exists(LIB):
-        cmd = [NVCC, *ARCH, "-shared", "-Xcompiler", "-fPIC,-pthread", "-ccbin", "g++", "-o", LIB, *objs]
+            list(ex.map(lambda s: _compile(s, verbose, obj_dir, defines), todo))
+    if todo or not os.path.exists(lib):
+        cmd = [NVCC, *ARCH, "-shared", "-Xcompiler", "-fPIC,-pthread", "-ccbin", "g++", "-o", lib, *objs]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
-    return LIB
+    return lib
+
+
+# The checked build: the same sources with -DGPTOSS_BOUNDS (every pointer argument held against
+# the allocation it lies in, data-dependent row numbers held against their arrays; see
+# csrc/common.cuh).  The GPU tests run their small cases through it as well.
+BOUNDS_LIB = os.path.join(HERE, "libgptoss_b200_bounds.so")
+
+
+def build_bounds(force: bool = False, verbose: bool = False) -> str:
+    return build(force, verbose, BOUNDS_LIB, os.path.join(CSRC, "_build_bounds"), ("-DGPTOSS_BOUNDS",))
 
 
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    if "--bounds" in sys.argv:
+        print(build_bounds(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

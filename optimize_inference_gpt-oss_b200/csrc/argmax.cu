@@ -227,6 +227,9 @@ extern "C" int gptoss_argmax(gptoss_stream_t stream, int T, const void *logits,
     return GPTOSS_OK;
   if (!logits || !out)
     return GPTOSS_ERR_BAD_ARG;
+  GPTOSS_SPAN(logits, strided_bytes(T, row_stride, V, dtype_size(logits_dtype)));
+  GPTOSS_SPAN(keys, (size_t)T * 8);
+  GPTOSS_SPAN(out, (size_t)T * 4);
   cudaStream_t s = as_stream(stream);
   return logits_dtype == GPTOSS_F32 ? launch<float>(s, T, logits, V, row_stride, keys, out)
                                     : launch<uint16_t>(s, T, logits, V, row_stride, keys, out);
@@ -242,6 +245,8 @@ extern "C" int gptoss_argmax_keys_finish(gptoss_stream_t stream, int T, unsigned
     return GPTOSS_OK;
   if (!keys || !out)
     return GPTOSS_ERR_BAD_ARG;
+  GPTOSS_SPAN(keys, (size_t)T * 8);
+  GPTOSS_SPAN(out, (size_t)T * 4);
   launch_kernel(argmax_keys_decode, dim3((T + 255) / 256), dim3(256), 0, as_stream(stream), keys, T, out);
   return launch_status();
 }

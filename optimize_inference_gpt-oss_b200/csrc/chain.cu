@@ -127,6 +127,7 @@ template <typename P> int dev_alloc(gptoss_chain *c, P **p, size_t bytes) {
   if (st != GPTOSS_OK)
     return st;
   c->allocs.push_back(q);
+  bounds_register(q, bytes ? bytes : 16);
   c->total_bytes += bytes;
   *p = static_cast<P *>(q);
   return GPTOSS_OK;
@@ -411,6 +412,8 @@ int gptoss_chain_destroy(gptoss_chain_t *c) {
   if (c->wave_state_host)
     (void)cudaFreeHost(c->wave_state_host);
   // wave_prompts / wave_generated are not in `allocs`: they are replaced when a wave needs more room
+  bounds_unregister(c->wave_prompts);
+  bounds_unregister(c->wave_generated);
   if (c->wave_prompts)
     (void)cudaFree(c->wave_prompts);
   if (c->wave_generated)
@@ -419,8 +422,10 @@ int gptoss_chain_destroy(gptoss_chain_t *c) {
     (void)cudaFreeHost(c->io_host);
   for (cudaEvent_t e : c->events)
     (void)cudaEventDestroy(e);
-  for (void *p : c->allocs)
+  for (void *p : c->allocs) {
+    bounds_unregister(p);
     (void)cudaFree(p);
+  }
   if (c->stream)
     (void)cudaStreamDestroy(c->stream);
   delete c;
@@ -705,12 +710,15 @@ static int wave_reserve(gptoss_chain *c, size_t prompt_ints, size_t generated_in
     if (st != GPTOSS_OK || want <= *cap)
       return;
     (void)cudaStreamSynchronize(c->stream);
+    bounds_unregister(*buf);
     if (*buf)
       (void)cudaFree(*buf);
     *buf = nullptr;
     *cap = 0;
     void *q = nullptr;
     st = cuda_status(cudaMalloc(&q, want * 4));
+    if (st == GPTOSS_OK)
+      bounds_register(q, want * 4);
     if (st == GPTOSS_OK) {
       *buf = static_cast<int *>(q);
       *cap = want;

@@ -41,7 +41,8 @@ template <typename ZT, typename OT, int MODE, bool NORM, int KM, int NC, int STA
 __global__ void combine_rows(float *x, const ZT *__restrict__ Z, const int *__restrict__ own_row,
                              const float *__restrict__ topk_w, const int *__restrict__ topk_e,
                              int k, int H, const int *__restrict__ phys_of,
-                             const float *__restrict__ norm_w, OT *__restrict__ out, int T) {
+                             const float *__restrict__ norm_w, OT *__restrict__ out, int T, int z_rows,
+                             int phys_n, unsigned int *oob) {
   pdl_prologue();
   constexpr bool EXACT = MODE != 0;
   constexpr int SZ = sizeof(ZT);
@@ -70,7 +71,8 @@ __global__ void combine_rows(float *x, const ZT *__restrict__ Z, const int *__re
   //   "routing" word: L < k: topk_w[token*k + L];    k <= L < 2k: topk_e[token*k + L - k]
   // A pair whose own_row entry is negative has no expert row here (the grouping step writes
   // -1 for experts outside its range): nothing is read for it; its part of the stage is
-  // filled with zeros instead, so it adds nothing and the sum needs no test per pair.
+  // filled with zeros by the copy instruction itself, so it adds nothing and neither the
+  // copies nor the sum branch on it.
   const int lane = threadIdx.x & 31;
   auto load_ids_word = [&](long row) -> uint32_t {
     if (lane < k)
@@ -117,16 +119,16 @@ __global__ void combine_rows(float *x, const ZT *__restrict__ Z, const int *__re
           for (int j = 0; j < KM; j++)
             if (j < k) {
               unsigned char *sz = sx + x_bytes + (size_t)j * z_bytes + (size_t)chunk * 8 * SZ;
-              if (ids.row[j] >= 0) {
-                const ZT *zr = Z + (size_t)ids.row[j] * H + (size_t)chunk * 8;
-                cp_async16(sz, zr);
-                if constexpr (SZ == 4)
-                  cp_async16(sz + 16, zr + 4);
-              } else { // no row here: zeros (this thread is the only reader of the chunk)
-                *reinterpret_cast<uint4 *>(sz) = make_uint4(0u, 0u, 0u, 0u);
-                if constexpr (SZ == 4)
-                  *reinterpret_cast<uint4 *>(sz + 16) = make_uint4(0u, 0u, 0u, 0u);
-              }
+              // no row here (a negative entry, or one past the end of Z): zeros, and no read
+              const bool here = (unsigned)ids.row[j] < (unsigned)z_rows;
+              const ZT *zr = Z + (size_t)(here ? ids.row[j] : 0) * H + (size_t)chunk * 8;
+              cp_async16_or_zeros(sz, zr, here);
+              if constexpr (SZ == 4)
+                cp_async16_or_zeros(sz + 16, zr + 4, here);
+#ifdef GPTOSS_BOUNDS
+              if (!here && ids.row[j] >= 0 && threadIdx.x == 0 && c == 0)
+                atomicAdd(oob, 1u); // a row number past the end of Z's allocation
+#endif
             }
         }
       }
@@ -175,7 +177,8 @@ __global__ void combine_rows(float *x, const ZT *__restrict__ Z, const int *__re
       int key[KM];
 #pragma unroll
       for (int j = 0; j < KM; j++)
-        key[j] = (phys_of && cur.e[j] >= 0 && cur.e[j] != 0x7fffffff) ? __ldg(phys_of + cur.e[j]) : cur.e[j];
+        key[j] = (phys_of && cur.e[j] >= 0 && cur.e[j] < phys_n && cur.e[j] != 0x7fffffff) ? __ldg(phys_of + cur.e[j])
+                                                                                           : cur.e[j];
 #pragma unroll
       for (int i = 1; i < KM; i++)
 #pragma unroll
@@ -278,7 +281,7 @@ __global__ void combine_rows_generic(float *x, const ZT *__restrict__ Z,
                                      const int *__restrict__ topk_e, int k, int H,
                                      const int *__restrict__ phys_of,
                                      const float *__restrict__ norm_w, OT *__restrict__ out,
-                                     int T) {
+                                     int T, int z_rows, int phys_n, unsigned int *oob) {
   pdl_prologue();
   constexpr bool EXACT = MODE != 0;
   using Acc = typename std::conditional<EXACT, double, float>::type;
@@ -294,7 +297,8 @@ __global__ void combine_rows_generic(float *x, const ZT *__restrict__ Z,
       for (int i = 1; i < k; i++)
         for (int j = i; j > 0; j--) {
           const int ea = topk_e[(size_t)row * k + ord[j]], eb = topk_e[(size_t)row * k + ord[j - 1]];
-          const int ka = phys_of && ea >= 0 ? phys_of[ea] : ea, kb = phys_of && eb >= 0 ? phys_of[eb] : eb;
+          const int ka = phys_of && ea >= 0 && ea < phys_n ? phys_of[ea] : ea;
+          const int kb = phys_of && eb >= 0 && eb < phys_n ? phys_of[eb] : eb;
           if (!(ka < kb))
             break;
           const int t = ord[j];
@@ -308,8 +312,13 @@ __global__ void combine_rows_generic(float *x, const ZT *__restrict__ Z,
         float acc = 0.0f;
         for (int j = 0; j < k; j++) {
           const size_t p = (size_t)row * k + ord[j];
-          if (own_row && own_row[p] < 0)
+          if (own_row && (unsigned)own_row[p] >= (unsigned)z_rows) {
+#ifdef GPTOSS_BOUNDS
+            if (own_row[p] >= 0 && i == 0)
+              atomicAdd(oob, 1u);
+#endif
             continue; // no expert row here for this pair
+          }
           const size_t zr = own_row ? (size_t)own_row[p] : p;
           const float z = load1(Z + zr * H + i), w = topk_w[p];
           acc = MODE == 1 ? __fadd_rn(acc, __fmul_rn(z, w)) : __fmaf_rn(z, w, acc);
@@ -352,6 +361,8 @@ struct Args {
   const int *phys_of;
   const float *norm_w;
   void *out;
+  int z_rows, phys_n; // extents of Z (rows) and phys_of (entries); INT_MAX when not known
+  unsigned int *oob;  // the checked build's device counter
 };
 
 template <typename ZT, typename OT, int MODE, bool NORM, int KM, int NC, int STAGES>
@@ -362,7 +373,7 @@ int launch_variant(cudaStream_t s, const Args &a, int threads, size_t smem) {
     return GPTOSS_ERR_UNSUPPORTED;
   launch_kernel(kern, dim3(row_grid(a.T, per_sm)), dim3(threads), smem, s, a.x, static_cast<const ZT *>(a.Z), a.own_row,
                                                    a.topk_w, a.topk_e, a.k, a.H, a.phys_of, a.norm_w,
-                                                   static_cast<OT *>(a.out), a.T);
+                                                   static_cast<OT *>(a.out), a.T, a.z_rows, a.phys_n, a.oob);
   return launch_status();
 }
 
@@ -404,7 +415,7 @@ template <typename ZT, typename OT, int MODE, bool NORM> int launch(cudaStream_t
   note_generic_launch();
   launch_kernel(combine_rows_generic<ZT, OT, MODE, NORM>, dim3(row_grid(a.T, 8)), dim3(256), 0, s, 
       a.x, static_cast<const ZT *>(a.Z), a.own_row, a.topk_w, a.topk_e, a.k, a.H, a.phys_of,
-      a.norm_w, static_cast<OT *>(a.out), a.T);
+      a.norm_w, static_cast<OT *>(a.out), a.T, a.z_rows, a.phys_n, a.oob);
   return launch_status();
 }
 
@@ -442,7 +453,31 @@ extern "C" int gptoss_moe_combine(gptoss_stream_t stream, int T, float *x, const
     return GPTOSS_OK;
   if (!x || !Z || !topk_w || !topk_e || (norm_w && !out))
     return GPTOSS_ERR_BAD_ARG;
-  const Args a{T, x, Z, own_row, topk_w, topk_e, k, H, phys_of, norm_w, out};
+  int z_rows = 0x7fffffff, phys_n = 0x7fffffff;
+  unsigned int *oob = nullptr;
+  GPTOSS_SPAN(x, (size_t)T * H * 4);
+  GPTOSS_SPAN(topk_w, (size_t)T * k * 4);
+  GPTOSS_SPAN(topk_e, (size_t)T * k * 4);
+  GPTOSS_SPAN(own_row, (size_t)T * k * 4);
+  GPTOSS_SPAN(norm_w, (size_t)H * 4);
+  if (norm_w)
+    GPTOSS_SPAN(out, (size_t)T * H * dtype_size(out_dtype));
+#ifdef GPTOSS_BOUNDS
+  { // the row map and the expert renumbering index arrays whose length the call does not state
+    const size_t z_room = bounds_room(Z), p_room = phys_of ? bounds_room(phys_of) : SIZE_MAX;
+    const size_t row_bytes = (size_t)H * dtype_size(z_dtype);
+    if (z_room != SIZE_MAX && z_room / row_bytes < (size_t)z_rows)
+      z_rows = (int)(z_room / row_bytes);
+    if (p_room != SIZE_MAX && p_room / 4 < (size_t)phys_n)
+      phys_n = (int)(p_room / 4);
+    if (!own_row)
+      GPTOSS_SPAN(Z, (size_t)T * k * row_bytes);
+    oob = bounds_device_word();
+    if (!oob)
+      return GPTOSS_ERR_CUDA;
+  }
+#endif
+  const Args a{T, x, Z, own_row, topk_w, topk_e, k, H, phys_of, norm_w, out, z_rows, phys_n, oob};
   cudaStream_t s = as_stream(stream);
   return z_dtype == GPTOSS_F32 ? launch_mode<float>(s, a, out_dtype, flags)
                                : launch_mode<uint16_t>(s, a, out_dtype, flags);

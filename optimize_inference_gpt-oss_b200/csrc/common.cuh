@@ -113,6 +113,42 @@ inline size_t dtype_size(gptoss_dtype_t d) { return d == GPTOSS_F32 ? 4 : 2; }
 // these kernels it is neutral.
 __device__ __forceinline__ void pdl_prologue() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
+// ---- the checked build (-DGPTOSS_BOUNDS) --------------------------------------------
+//
+// Stands in for a memory checker on machines where none can be run.  The library keeps a
+// table of the device allocations made through it (gptoss_device_alloc, the chain's
+// buffers); every entry point works out, from its shape arguments, how many bytes it will
+// touch behind each pointer and refuses the call (GPTOSS_ERR_BAD_ARG, nothing launched) when
+// a pointer that lies inside a known allocation would be walked past that allocation's end.
+// Pointers into memory the table does not know are let through and counted as unchecked.
+// Indices that come out of device data and have no extent in the call's arguments (the
+// combine's row map and expert renumbering) get their extent from the same table, and a
+// kernel that meets one outside it skips the access and counts it in a device word.  Nothing
+// traps.  gptoss_bounds_violations() adds both counts up.  In the ordinary build all of this
+// compiles to nothing.
+#ifdef GPTOSS_BOUNDS
+void bounds_register(const void *p, size_t bytes);
+void bounds_unregister(const void *p);
+bool bounds_span_ok(const void *p, size_t bytes, const char *what);
+size_t bounds_room(const void *p); // bytes from p to the end of its allocation; SIZE_MAX when unknown
+unsigned int *bounds_device_word();
+#define GPTOSS_SPAN(ptr, bytes)                                                                   \
+  do {                                                                                            \
+    if ((ptr) && !gptoss::bounds_span_ok((ptr), (size_t)(bytes), #ptr))                           \
+      return GPTOSS_ERR_BAD_ARG;                                                                  \
+  } while (0)
+#else
+inline void bounds_register(const void *, size_t) {}
+inline void bounds_unregister(const void *) {}
+#define GPTOSS_SPAN(ptr, bytes)                                                                   \
+  do {                                                                                            \
+  } while (0)
+#endif
+// Bytes behind the first element of T rows of `width` elements `stride` elements apart.
+inline size_t strided_bytes(long T, long stride, long width, size_t elem) {
+  return T <= 0 ? 0 : ((size_t)(T - 1) * (size_t)stride + (size_t)width) * elem;
+}
+
 // ---- 128-bit memory access ----------------------------------------------------
 
 // Read-once data (activations streamed through the kernel): do not keep the
@@ -172,6 +208,14 @@ __device__ __forceinline__ void st_stream8(void *p, uint2 v) {
 __device__ __forceinline__ void cp_async16(void *smem_dst, const void *gmem_src) {
   const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
+}
+// The same with the source optional: when `take` is false nothing is read and the 16 bytes
+// are filled with zeros (the instruction's source-size operand), so a caller can leave a
+// piece out without a branch.  gmem_src must still be a valid address.
+__device__ __forceinline__ void cp_async16_or_zeros(void *smem_dst, const void *gmem_src, bool take) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gmem_src), "r"(take ? 16 : 0)
+               : "memory");
 }
 // The same through L1 (.ca): for small read-only tables that many rows, warps and
 // blocks of an SM ask for again and again (a position's cos/sin row).  Kept in L1, the

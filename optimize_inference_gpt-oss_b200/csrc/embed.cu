@@ -106,6 +106,9 @@ extern "C" int gptoss_embed(gptoss_stream_t stream, int T, const void *table,
     return GPTOSS_OK;
   if (!table || !ids || !x)
     return GPTOSS_ERR_BAD_ARG;
+  GPTOSS_SPAN(table, (size_t)V * H * dtype_size(table_dtype));
+  GPTOSS_SPAN(ids, (size_t)T * 4);
+  GPTOSS_SPAN(x, (size_t)T * H * dtype_size(x_dtype));
   cudaStream_t s = as_stream(stream);
   if (table_dtype == GPTOSS_BF16 && x_dtype == GPTOSS_F32)
     return launch<uint16_t, float>(s, T, table, V, ids, x, H);
@@ -127,6 +130,9 @@ extern "C" int gptoss_moe_gather(gptoss_stream_t stream, int R, const void *t, g
     return GPTOSS_OK;
   if (!t || !row_pair || !Xg)
     return GPTOSS_ERR_BAD_ARG;
+  GPTOSS_SPAN(t, (size_t)n_tokens * H * dtype_size(dtype));
+  GPTOSS_SPAN(row_pair, (size_t)R * 4);
+  GPTOSS_SPAN(Xg, (size_t)R * H * dtype_size(dtype));
   cudaStream_t s = as_stream(stream);
   // the embedding gather with "ids" = pair indices divided by k
   return dtype == GPTOSS_BF16 ? launch<uint16_t, uint16_t>(s, R, t, n_tokens, row_pair, Xg, H, k)

@@ -178,6 +178,11 @@ extern "C" int gptoss_moe_group(gptoss_stream_t stream, const int *topk_e, int n
     return GPTOSS_ERR_BAD_ARG;
   if (n_pairs > 0 && (!topk_e || !row_pair || !own_row))
     return GPTOSS_ERR_BAD_ARG;
+  GPTOSS_SPAN(topk_e, (size_t)n_pairs * 4);
+  GPTOSS_SPAN(counts, (size_t)e_count * 4);
+  GPTOSS_SPAN(offsets, ((size_t)e_count + 1) * 4);
+  GPTOSS_SPAN(row_pair, (size_t)n_pairs * 4);
+  GPTOSS_SPAN(own_row, (size_t)n_pairs * 4);
   cudaStream_t s = as_stream(stream);
   const long per_thread = ((long)n_pairs + kWideThreads - 1) / kWideThreads; // pairs a thread of the wide form holds
   if (aligned16(topk_e) && per_thread <= 64) {

@@ -116,10 +116,16 @@ int gptoss_device_alloc(void **ptr, size_t bytes) {
   if (!ptr)
     return GPTOSS_ERR_BAD_ARG;
   *ptr = nullptr;
-  return cuda_status(cudaMalloc(ptr, bytes ? bytes : 1));
+  const int st = cuda_status(cudaMalloc(ptr, bytes ? bytes : 1));
+  if (st == GPTOSS_OK)
+    bounds_register(*ptr, bytes ? bytes : 1);
+  return st;
 }
 
-int gptoss_device_free(void *ptr) { return cuda_status(cudaFree(ptr)); }
+int gptoss_device_free(void *ptr) {
+  bounds_unregister(ptr);
+  return cuda_status(cudaFree(ptr));
+}
 
 int gptoss_device_memset(void *ptr, int byte, size_t bytes, gptoss_stream_t stream) {
   if (!ptr && bytes)

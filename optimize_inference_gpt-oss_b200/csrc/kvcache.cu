@@ -144,6 +144,14 @@ extern "C" int gptoss_kv_cache_write(gptoss_stream_t stream, int T, const void *
     return GPTOSS_OK;
   if (!qkv || !kc || !vq || !vs)
     return GPTOSS_ERR_BAD_ARG;
+  {
+    const size_t per_row = (size_t)slots * n_kv_heads * kHeadDim;
+    GPTOSS_SPAN(qkv, strided_bytes(T, row_stride, (long)(n_q_heads + 2 * n_kv_heads) * head_dim, dtype_size(qkv_dtype)));
+    GPTOSS_SPAN(kc, (size_t)T * per_row * 2);
+    GPTOSS_SPAN(vq, (size_t)T * per_row);
+    GPTOSS_SPAN(vs, (size_t)T * per_row / 64 * 4);
+    GPTOSS_SPAN(slot_of_row, (size_t)T * 4);
+  }
   const Prep none = {};
   return launch_cache_write(as_stream(stream), T, qkv, qkv_dtype, row_stride, n_q_heads, n_kv_heads, kc, vq, vs,
                             slots, slot_of_row, slot_scalar, none);

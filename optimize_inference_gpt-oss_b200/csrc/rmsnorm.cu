@@ -693,6 +693,10 @@ extern "C" int gptoss_add_rmsnorm(gptoss_stream_t stream, int T, float *x, const
   // In-place norm is only defined for an fp32 output of the same row layout.
   if (out == (void *)x && out_dtype != GPTOSS_F32)
     return GPTOSS_ERR_BAD_ARG;
+  GPTOSS_SPAN(x, (size_t)T * H * 4);
+  GPTOSS_SPAN(y, (size_t)T * H * dtype_size(y_dtype));
+  GPTOSS_SPAN(weight, (size_t)H * 4);
+  GPTOSS_SPAN(out, (size_t)T * H * dtype_size(out_dtype));
   cudaStream_t s = as_stream(stream);
   return (flags & GPTOSS_EXACT) ? launch_y<true>(s, T, x, y, y_dtype, weight, out, out_dtype, H)
                                 : launch_y<false>(s, T, x, y, y_dtype, weight, out, out_dtype, H);
@@ -708,6 +712,11 @@ extern "C" int gptoss_embed_rmsnorm(gptoss_stream_t stream, int T, const void *t
     return GPTOSS_OK;
   if (!table || !ids || !x || !weight || !out || out == (void *)x)
     return GPTOSS_ERR_BAD_ARG;
+  GPTOSS_SPAN(table, (size_t)V * H * dtype_size(table_dtype));
+  GPTOSS_SPAN(ids, (size_t)T * 4);
+  GPTOSS_SPAN(x, (size_t)T * H * 4);
+  GPTOSS_SPAN(weight, (size_t)H * 4);
+  GPTOSS_SPAN(out, (size_t)T * H * dtype_size(out_dtype));
   int st;
   {
     const PdlScope pdl(flags);

@@ -547,6 +547,19 @@ int run_bias_rope(gptoss_stream_t stream, int T, const void *qkv_in, gptoss_dtyp
   // In place only with identical layout: a thread overwrites exactly what it read.
   if (qkv_in == qkv_out && (in_dtype != out_dtype || in_row_stride != out_row_stride))
     return GPTOSS_ERR_BAD_ARG;
+  GPTOSS_SPAN(qkv_in, strided_bytes(T, in_row_stride, width, dtype_size(in_dtype)));
+  GPTOSS_SPAN(qkv_out, strided_bytes(T, out_row_stride, width, dtype_size(out_dtype)));
+  GPTOSS_SPAN(bias, (size_t)width * 4);
+  GPTOSS_SPAN(pos, (size_t)T * 4);
+  GPTOSS_SPAN(cos_tab, (size_t)n_pos * (head_dim / 2) * 4);
+  GPTOSS_SPAN(sin_tab, (size_t)n_pos * (head_dim / 2) * 4);
+  if (cache.kc) { // one cache of `slots` positions per row
+    const size_t per_row = (size_t)cache.slots * cache.n_kv_heads * 64;
+    GPTOSS_SPAN(cache.kc, (size_t)T * per_row * 2);
+    GPTOSS_SPAN(cache.vq, (size_t)T * per_row);
+    GPTOSS_SPAN(cache.vs, (size_t)T * per_row / 64 * 4);
+    GPTOSS_SPAN(cache.slot_of_row, (size_t)T * 4);
+  }
   const Args a{qkv_in, in_row_stride, bias,       pos,      pos_scalar, cos_tab,        sin_tab, n_pos,
                n_q_heads, n_kv_heads, head_dim, qkv_out,  out_row_stride, T,     cache};
   cudaStream_t s = as_stream(stream);

@@ -121,6 +121,11 @@ extern "C" int gptoss_router_topk(gptoss_stream_t stream, int T, const void *log
     return GPTOSS_OK;
   if (!logits || !topk_w || !topk_e)
     return GPTOSS_ERR_BAD_ARG;
+  GPTOSS_SPAN(logits, (size_t)T * E * dtype_size(logits_dtype));
+  GPTOSS_SPAN(topk_w, (size_t)T * k * 4);
+  GPTOSS_SPAN(topk_e, (size_t)T * k * 4);
+  GPTOSS_SPAN(done, (size_t)T * 4);
+  GPTOSS_SPAN(slot_of, (size_t)E * 4);
   const int grid = (T + kRowsPerBlock - 1) / kRowsPerBlock;
   cudaStream_t s = as_stream(stream);
   const int slots = (E + 31) / 32;

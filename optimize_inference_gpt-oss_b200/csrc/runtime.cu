@@ -1,5 +1,7 @@
 // Library-wide host helpers: version, status text, per-thread CUDA error memory,
 // cached device properties.
+#include <stdio.h>
+
 #include <atomic>
 #include <mutex>
 
@@ -48,6 +50,73 @@ unsigned int *wait_giveups_word() {
   }
   return p;
 }
+
+#ifdef GPTOSS_BOUNDS
+namespace {
+struct Span {
+  uintptr_t begin, end;
+};
+std::mutex g_bounds_mu;
+Span g_spans[4096];
+int g_n_spans = 0;
+std::atomic<long> g_host_violations{0}, g_unchecked{0}, g_checked{0};
+__device__ unsigned int g_bounds_device_word;
+} // namespace
+
+void bounds_register(const void *p, size_t bytes) {
+  if (!p)
+    return;
+  std::lock_guard<std::mutex> lock(g_bounds_mu);
+  if (g_n_spans < 4096)
+    g_spans[g_n_spans++] = Span{(uintptr_t)p, (uintptr_t)p + bytes};
+}
+void bounds_unregister(const void *p) {
+  std::lock_guard<std::mutex> lock(g_bounds_mu);
+  for (int i = 0; i < g_n_spans; i++)
+    if (g_spans[i].begin == (uintptr_t)p) {
+      g_spans[i] = g_spans[--g_n_spans];
+      return;
+    }
+}
+size_t bounds_room(const void *p) {
+  std::lock_guard<std::mutex> lock(g_bounds_mu);
+  const uintptr_t a = (uintptr_t)p;
+  for (int i = 0; i < g_n_spans; i++)
+    if (a >= g_spans[i].begin && a < g_spans[i].end)
+      return (size_t)(g_spans[i].end - a);
+  return SIZE_MAX;
+}
+bool bounds_span_ok(const void *p, size_t bytes, const char *what) {
+  const size_t room = bounds_room(p);
+  if (room == SIZE_MAX) {
+    g_unchecked++;
+    return true;
+  }
+  g_checked++;
+  if (bytes <= room)
+    return true;
+  g_host_violations++;
+  fprintf(stderr, "gptoss bounds: %s needs %zu bytes, its allocation has %zu left\n", what, bytes, room);
+  return false;
+}
+unsigned int *bounds_device_word() {
+  static std::atomic<unsigned int *> cached[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64)
+    return nullptr;
+  unsigned int *p = cached[dev].load(std::memory_order_acquire);
+  if (!p) {
+    void *q = nullptr;
+    if (cudaGetSymbolAddress(&q, g_bounds_device_word) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return nullptr;
+    }
+    p = static_cast<unsigned int *>(q);
+    cached[dev].store(p, std::memory_order_release);
+  }
+  return p;
+}
+#endif
 
 int occupancy_cached(const void *kernel, int threads, size_t smem) {
   struct Entry {
@@ -122,4 +191,31 @@ extern "C" long gptoss_wait_giveups(void) {
   if (!p || cudaMemcpy(&v, p, sizeof v, cudaMemcpyDeviceToHost) != cudaSuccess)
     return -1;
   return (long)v;
+}
+
+extern "C" int gptoss_bounds_enabled(void) {
+#ifdef GPTOSS_BOUNDS
+  return 1;
+#else
+  return 0;
+#endif
+}
+
+extern "C" long gptoss_bounds_violations(void) {
+#ifdef GPTOSS_BOUNDS
+  unsigned int *p = gptoss::bounds_device_word(), v = 0;
+  if (p && cudaMemcpy(&v, p, sizeof v, cudaMemcpyDeviceToHost) != cudaSuccess)
+    return -1;
+  return gptoss::g_host_violations.load() + (long)v;
+#else
+  return 0;
+#endif
+}
+
+extern "C" long gptoss_bounds_checked_spans(void) {
+#ifdef GPTOSS_BOUNDS
+  return gptoss::g_checked.load();
+#else
+  return 0;
+#endif
 }

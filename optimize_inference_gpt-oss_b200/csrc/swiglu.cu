@@ -146,6 +146,8 @@ extern "C" int gptoss_swiglu(gptoss_stream_t stream, const void *Y, gptoss_dtype
   if (R > ((size_t)1 << 40) / (size_t)I)
     return GPTOSS_ERR_UNSUPPORTED;
   const size_t n_out = R * (size_t)I;
+  GPTOSS_SPAN(Y, 2 * n_out * dtype_size(y_dtype));
+  GPTOSS_SPAN(G, n_out * dtype_size(g_dtype));
   cudaStream_t s = as_stream(stream);
   return (flags & GPTOSS_EXACT) ? launch_types<true>(s, Y, y_dtype, G, g_dtype, n_out, limit)
                                 : launch_types<false>(s, Y, y_dtype, G, g_dtype, n_out, limit);

@@ -33,6 +33,24 @@ def pkg():
     return mod
 
 
+@pytest.fixture(scope="session", autouse=True)
+def _checked_build_report(request):
+    """When the session runs on the checked build of the library (GPTOSS_B200_LIB pointing at
+    libgptoss_b200_bounds.so), its closing line says how many pointer arguments were held
+    against their allocations and how many violations were seen."""
+    yield
+    mod = sys.modules.get(PKG_NAME)
+    if mod is None or getattr(mod, "_lib", None) is None:
+        return
+    lib = mod._lib
+    if lib.gptoss_bounds_enabled():
+        import json
+        rec = {"enabled": 1, "violations": int(lib.gptoss_bounds_violations()),
+               "checked_spans": int(lib.gptoss_bounds_checked_spans())}
+        with request.config.pluginmanager.getplugin("capturemanager").global_and_fixture_disabled():
+            print("\n[bounds]" + json.dumps(rec))
+
+
 @pytest.fixture(scope="session")
 def orc():
     import oracle
