@@ -33,6 +33,7 @@ template <int KM> struct Routing { // weights and expert ids of one token
 template <int KM> struct RowIds { // where the token's expert rows are, and whether it is live
   int row[KM];
   bool live;
+  bool all_here; // every pair of the token has an expert row in Z (the usual case)
 };
 
 // MODE 0: fast (choice order, FMA).  MODE 1: exact (increasing expert, separate
@@ -71,8 +72,9 @@ __global__ void combine_rows(float *x, const ZT *__restrict__ Z, const int *__re
   //   "routing" word: L < k: topk_w[token*k + L];    k <= L < 2k: topk_e[token*k + L - k]
   // A pair whose own_row entry is negative has no expert row here (the grouping step writes
   // -1 for experts outside its range): nothing is read for it; its part of the stage is
-  // filled with zeros by the copy instruction itself, so it adds nothing and neither the
-  // copies nor the sum branch on it.
+  // filled with zeros by the copy instruction itself, so it adds nothing and the sum needs
+  // no test per pair.  Tokens with such a pair take a path of their own (one vote per token);
+  // the others run the plain copies.
   const int lane = threadIdx.x & 31;
   auto load_ids_word = [&](long row) -> uint32_t {
     if (lane < k)
@@ -91,9 +93,16 @@ __global__ void combine_rows(float *x, const ZT *__restrict__ Z, const int *__re
   auto spread_ids = [&](uint32_t word) {
     RowIds<KM> r;
     r.live = (int)__shfl_sync(0xffffffffu, word, k) >= 0;
+    int any = 0; // a negative entry anywhere sets the sign bit
 #pragma unroll
-    for (int j = 0; j < KM; j++)
+    for (int j = 0; j < KM; j++) {
       r.row[j] = (int)__shfl_sync(0xffffffffu, word, j < k ? j : 0);
+      any |= r.row[j];
+#ifdef GPTOSS_BOUNDS
+      any |= (uint32_t)r.row[j] >= (uint32_t)z_rows ? -1 : 0; // checked build: also past the end of Z
+#endif
+    }
+    r.all_here = any >= 0;
     return r;
   };
   auto spread_routing = [&](uint32_t word) {
@@ -114,12 +123,21 @@ __global__ void combine_rows(float *x, const ZT *__restrict__ Z, const int *__re
         const int chunk = threadIdx.x + c * blockDim.x;
         cp_async16(sx + (size_t)chunk * 32, xr + (size_t)chunk * 8);
         cp_async16(sx + (size_t)chunk * 32 + 16, xr + (size_t)chunk * 8 + 4);
-        if (ids.live) {
+        if (ids.live && ids.all_here) {
+#pragma unroll
+          for (int j = 0; j < KM; j++)
+            if (j < k) {
+              const ZT *zr = Z + (size_t)ids.row[j] * H + (size_t)chunk * 8;
+              unsigned char *sz = sx + x_bytes + (size_t)j * z_bytes + (size_t)chunk * 8 * SZ;
+              cp_async16(sz, zr);
+              if constexpr (SZ == 4)
+                cp_async16(sz + 16, zr + 4);
+            }
+        } else if (ids.live) { // some pair has no row here: that pair's part of the stage becomes zeros, unread
 #pragma unroll
           for (int j = 0; j < KM; j++)
             if (j < k) {
               unsigned char *sz = sx + x_bytes + (size_t)j * z_bytes + (size_t)chunk * 8 * SZ;
-              // no row here (a negative entry, or one past the end of Z): zeros, and no read
               const bool here = (unsigned)ids.row[j] < (unsigned)z_rows;
               const ZT *zr = Z + (size_t)(here ? ids.row[j] : 0) * H + (size_t)chunk * 8;
               cp_async16_or_zeros(sz, zr, here);

@@ -145,7 +145,7 @@ extern "C" int gptoss_kv_cache_write(gptoss_stream_t stream, int T, const void *
   if (!qkv || !kc || !vq || !vs)
     return GPTOSS_ERR_BAD_ARG;
   {
-    const size_t per_row = (size_t)slots * n_kv_heads * kHeadDim;
+    [[maybe_unused]] const size_t per_row = (size_t)slots * n_kv_heads * kHeadDim;
     GPTOSS_SPAN(qkv, strided_bytes(T, row_stride, (long)(n_q_heads + 2 * n_kv_heads) * head_dim, dtype_size(qkv_dtype)));
     GPTOSS_SPAN(kc, (size_t)T * per_row * 2);
     GPTOSS_SPAN(vq, (size_t)T * per_row);

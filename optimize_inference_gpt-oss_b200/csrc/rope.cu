@@ -78,8 +78,16 @@ __device__ __forceinline__ size_t chunk64_at(int b, int slot, int g, int i, int 
 // KV: the launch also writes the row's keys (bf16) and values (int8 codes + scale) into
 // the caches, from the fp32 values it holds in registers (head_dim is 64 then, so a head is
 // the 4 consecutive lanes of its 4 pieces and the value head's max |v| is two shuffles).
+#ifndef GPTOSS_ROPE_STAGES
+#define GPTOSS_ROPE_STAGES 2 // rows in the ring of the plain (no cache write) form
+#endif
+#ifdef GPTOSS_ROPE_BIAS_SMEM // experiment: the bias slice in shared memory, compiled for 4 blocks of 320 threads per SM
+#define GPTOSS_ROPE_BOUNDS __launch_bounds__(320, 4)
+#else
+#define GPTOSS_ROPE_BOUNDS
+#endif
 template <typename IT, typename OT, bool EXACT, bool FMA, int STAGES, bool KV>
-__global__ void bias_rope_rows(const IT *qkv_in, long in_stride, const float *__restrict__ bias,
+__global__ void GPTOSS_ROPE_BOUNDS bias_rope_rows(const IT *qkv_in, long in_stride, const float *__restrict__ bias,
                                const int *__restrict__ pos, int pos_scalar,
                                const float *__restrict__ cos_tab,
                                const float *__restrict__ sin_tab, int n_pos, int n_rot_heads,
@@ -98,6 +106,16 @@ __global__ void bias_rope_rows(const IT *qkv_in, long in_stride, const float *__
   const int head = active ? threadIdx.x / pieces : 0, piece = active ? threadIdx.x - head * pieces : 0;
   const size_t lo = (size_t)head * head_dim + piece * 8, hi = lo + half;
   const bool rotates = head < n_rot_heads;
+#ifdef GPTOSS_ROPE_BIAS_SMEM
+  uint4 *bias_s = reinterpret_cast<uint4 *>(ring + (size_t)STAGES * stage_bytes); // [4][blockDim.x]
+  if (bias && active) {
+#pragma unroll
+    for (int q = 0; q < 2; q++) {
+      bias_s[q * blockDim.x + threadIdx.x] = ld_table(bias + lo + 4 * q);
+      bias_s[(2 + q) * blockDim.x + threadIdx.x] = ld_table(bias + hi + 4 * q);
+    }
+  }
+#else
   Vec8 ba, bb;
 #pragma unroll
   for (int i = 0; i < 8; i++)
@@ -106,6 +124,7 @@ __global__ void bias_rope_rows(const IT *qkv_in, long in_stride, const float *__
     ba = load8<kTable>(bias, lo);
     bb = load8<kTable>(bias, hi);
   }
+#endif
 
   auto position = [&](long row) {
     int p = pos ? __ldg(pos + row) : pos_scalar;
@@ -167,6 +186,19 @@ __global__ void bias_rope_rows(const IT *qkv_in, long in_stride, const float *__
       const unsigned char *sr = ring + (size_t)stage * stage_bytes;
       a = smem_load8<IT>(sr + lo * SI), b = smem_load8<IT>(sr + hi * SI);
       if (bias) {
+#ifdef GPTOSS_ROPE_BIAS_SMEM
+        Vec8 ba, bb;
+        {
+          const uint4 p0 = bias_s[threadIdx.x], p1 = bias_s[blockDim.x + threadIdx.x];
+          const uint4 q0 = bias_s[2 * blockDim.x + threadIdx.x], q1 = bias_s[3 * blockDim.x + threadIdx.x];
+          ba.v[0] = __uint_as_float(p0.x), ba.v[1] = __uint_as_float(p0.y), ba.v[2] = __uint_as_float(p0.z),
+          ba.v[3] = __uint_as_float(p0.w), ba.v[4] = __uint_as_float(p1.x), ba.v[5] = __uint_as_float(p1.y),
+          ba.v[6] = __uint_as_float(p1.z), ba.v[7] = __uint_as_float(p1.w);
+          bb.v[0] = __uint_as_float(q0.x), bb.v[1] = __uint_as_float(q0.y), bb.v[2] = __uint_as_float(q0.z),
+          bb.v[3] = __uint_as_float(q0.w), bb.v[4] = __uint_as_float(q1.x), bb.v[5] = __uint_as_float(q1.y),
+          bb.v[6] = __uint_as_float(q1.z), bb.v[7] = __uint_as_float(q1.w);
+        }
+#endif
 #pragma unroll
         for (int i = 0; i < 8; i++) {
           a.v[i] = __fadd_rn(a.v[i], ba.v[i]);
@@ -495,10 +527,22 @@ template <typename IT, typename OT, bool EXACT, bool FMA> int launch(cudaStream_
     if (stage_bytes * 2 <= 220 * 1024) {
       if (a.cache.kc) { // with the cache write: 64-wide heads only, 16-byte key stores
         if (a.head_dim == 64 && aligned16(a.cache.kc))
+#ifdef GPTOSS_ROPE_BIAS_SMEM
+          st = threads <= 320 ? launch_pipe<IT, OT, EXACT, FMA, 2, true>(s, a, threads, stage_bytes * 2 + (size_t)threads * 64)
+                              : GPTOSS_ERR_UNSUPPORTED;
+#else
           st = launch_pipe<IT, OT, EXACT, FMA, 2, true>(s, a, threads, stage_bytes * 2);
+#endif
         return st;
       }
-      st = launch_pipe<IT, OT, EXACT, FMA, 2, false>(s, a, threads, stage_bytes * 2);
+#ifdef GPTOSS_ROPE_BIAS_SMEM
+      if (threads <= 320)
+        st = launch_pipe<IT, OT, EXACT, FMA, GPTOSS_ROPE_BIAS_SMEM, false>(
+            s, a, threads, stage_bytes * GPTOSS_ROPE_BIAS_SMEM + (size_t)threads * 64);
+      if (st != GPTOSS_ERR_UNSUPPORTED)
+        return st;
+#endif
+      st = launch_pipe<IT, OT, EXACT, FMA, GPTOSS_ROPE_STAGES, false>(s, a, threads, stage_bytes * GPTOSS_ROPE_STAGES);
       if (st != GPTOSS_ERR_UNSUPPORTED)
         return st;
     }
@@ -554,7 +598,7 @@ int run_bias_rope(gptoss_stream_t stream, int T, const void *qkv_in, gptoss_dtyp
   GPTOSS_SPAN(cos_tab, (size_t)n_pos * (head_dim / 2) * 4);
   GPTOSS_SPAN(sin_tab, (size_t)n_pos * (head_dim / 2) * 4);
   if (cache.kc) { // one cache of `slots` positions per row
-    const size_t per_row = (size_t)cache.slots * cache.n_kv_heads * 64;
+    [[maybe_unused]] const size_t per_row = (size_t)cache.slots * cache.n_kv_heads * 64;
     GPTOSS_SPAN(cache.kc, (size_t)T * per_row * 2);
     GPTOSS_SPAN(cache.vq, (size_t)T * per_row);
     GPTOSS_SPAN(cache.vs, (size_t)T * per_row / 64 * 4);
