@@ -5,7 +5,10 @@
 
 namespace gptoss {
 
-// bits(2^(i/32)) - (i << 47), i = 0..31; derived by derive_exp2_table.py.
+// T[i] = bits(2^(i/32) as a double) - (i << 47), i = 0..31: the table of the published
+// algorithm (Arm Optimized Routines / glibc exp2f_data, N = 32).  tests/test_abi_and_host.py
+// recomputes every entry from 2^(i/32) at 60 decimal digits; the GPU tests hold the function
+// built on it to the C library's expf on a dense sweep.
 __device__ static const unsigned long long kExp2Tab32[32] = {
     0x3ff0000000000000ull, 0x3fefd9b0d3158574ull, 0x3fefb5586cf9890full, 0x3fef9301d0125b51ull,
     0x3fef72b83c7d517bull, 0x3fef54873168b9aaull, 0x3fef387a6e756238ull, 0x3fef1e9df51fdee1ull,
@@ -46,11 +49,14 @@ __device__ __forceinline__ float glibc_expf(float x) {
   }
   const double z = __dmul_rn(kScale, (double)x);
   double kd = __dadd_rn(z, kRound);
-  const unsigned long long ki = (unsigned long long)__double_as_longlong(kd);
+  // k sits in the low bits of kd's mantissa.  Table entry + (k << 47) only ever changes the
+  // high word (the low 32 bits of k << 47 are zero, so nothing carries), and only k's low 17
+  // bits survive the shift: the 64-bit add is a 32-bit add of k << 15 to the high word.
+  const uint32_t k_lo = (uint32_t)__double2loint(kd);
   kd = __dsub_rn(kd, kRound);
   const double r = __dsub_rn(z, kd);
-  const unsigned long long tbits = kExp2Tab32[ki & 31u] + (ki << 47);
-  const double s = __longlong_as_double((long long)tbits);
+  const unsigned long long entry = kExp2Tab32[k_lo & 31u];
+  const double s = __hiloint2double((int)((uint32_t)(entry >> 32) + (k_lo << 15)), (int)(uint32_t)entry);
   const double hi = __fma_rn(c0, r, c1);
   double y = __fma_rn(c2, r, 1.0);
   y = __fma_rn(hi, __dmul_rn(r, r), y);

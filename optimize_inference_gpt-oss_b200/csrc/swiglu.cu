@@ -14,10 +14,24 @@
 namespace gptoss {
 namespace {
 
+// Groups per thread.  The fast form is a pure stream and wants bytes in flight: 2 groups
+// (1, 3 and 4 measured the same or slower on B200).  The exact form spends ~45 instructions per
+// output, nine of them in double precision: there the memory system is kept busy by other
+// blocks' loads while a block computes, so smaller pieces of work per block overlap better:
+// 1 group per thread 126 us per launch at 16,384 x 5760 fp32, 2 groups 139 us, 4 groups 175 us.
 #ifndef GPTOSS_SWIGLU_UNROLL
 #define GPTOSS_SWIGLU_UNROLL 2
 #endif
-constexpr int kUnroll = GPTOSS_SWIGLU_UNROLL;
+#ifndef GPTOSS_SWIGLU_UNROLL_EXACT
+#define GPTOSS_SWIGLU_UNROLL_EXACT 1
+#endif
+#ifndef GPTOSS_SWIGLU_THREADS_EXACT
+#define GPTOSS_SWIGLU_THREADS_EXACT 256
+#endif
+template <bool EXACT> struct Shape {
+  static constexpr int unroll = EXACT ? GPTOSS_SWIGLU_UNROLL_EXACT : GPTOSS_SWIGLU_UNROLL;
+  static constexpr int threads = EXACT ? GPTOSS_SWIGLU_THREADS_EXACT : 256;
+};
 
 template <bool EXACT> __device__ __forceinline__ float swiglu_one(float g, float u, float limit) {
   if (EXACT) { // run.cpp:709-722, every step rounded to fp32
@@ -27,7 +41,8 @@ template <bool EXACT> __device__ __forceinline__ float swiglu_one(float g, float
       u = limit;
     if (u < -limit)
       u = -limit;
-    const float sig = __fdiv_rn(1.0f, __fadd_rn(1.0f, glibc_expf(__fmul_rn(-1.702f, g))));
+    // 1.0f / (1.0f + e): the correctly rounded reciprocal is that quotient
+    const float sig = __frcp_rn(__fadd_rn(1.0f, glibc_expf(__fmul_rn(-1.702f, g))));
     g = __fmul_rn(g, sig);
     return __fmul_rn(g, __fadd_rn(u, 1.0f));
   }
@@ -45,17 +60,18 @@ template <bool EXACT> __device__ __forceinline__ float swiglu_one(float g, float
 // the hardware scheduler keeps every SM stocked with fresh blocks, which
 // measured ~10 % faster on B200 than a grid-stride loop over the same data.
 template <typename YT, typename GT, bool EXACT>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(Shape<EXACT>::threads)
     swiglu_flat(const YT *__restrict__ Y, GT *__restrict__ G, size_t n_groups, float limit) {
   pdl_prologue();
   constexpr int kIn = sizeof(YT);         // 16-byte loads per group
   constexpr int kPer = 16 / sizeof(YT);   // inputs per load
-  const size_t base = (size_t)blockIdx.x * (256 * kUnroll) + threadIdx.x;
+  constexpr int kUnroll = Shape<EXACT>::unroll, kThreads = Shape<EXACT>::threads;
+  const size_t base = (size_t)blockIdx.x * (kThreads * kUnroll) + threadIdx.x;
   uint4 raw[kUnroll][kIn];
 #pragma unroll
   for (int u = 0; u < kUnroll; u++) {
     // past the end: fetch the last group again; its result is not stored
-    const size_t g = base + u * 256 < n_groups ? base + u * 256 : n_groups - 1;
+    const size_t g = base + u * kThreads < n_groups ? base + u * kThreads : n_groups - 1;
 #pragma unroll
     for (int j = 0; j < kIn; j++)
       raw[u][j] = ld_stream(Y + g * 16 + j * kPer);
@@ -78,8 +94,8 @@ __global__ void __launch_bounds__(256)
         o.v[2 * j + 1] = swiglu_one<EXACT>(__uint_as_float(raw[u][j].z), __uint_as_float(raw[u][j].w), limit);
       }
     }
-    if (base + u * 256 < n_groups)
-      store8(G, (base + u * 256) * 8, o);
+    if (base + u * kThreads < n_groups)
+      store8(G, (base + u * kThreads) * 8, o);
   }
 }
 
@@ -97,7 +113,7 @@ template <typename YT, typename GT, bool EXACT>
 int launch(cudaStream_t s, const void *Y, void *G, size_t n_out, float limit) {
   const YT *yp = static_cast<const YT *>(Y);
   GT *gp = static_cast<GT *>(G);
-  constexpr int threads = 256;
+  constexpr int threads = Shape<EXACT>::threads, kUnroll = Shape<EXACT>::unroll;
   size_t n_groups = (aligned16(Y) && aligned16(G)) ? n_out / 8 : 0;
   if (n_groups > 0) {
     const size_t blocks = (n_groups + (size_t)threads * kUnroll - 1) / ((size_t)threads * kUnroll);

@@ -157,3 +157,21 @@ def test_reference_named_launchers_compile_as_plain_cxx(tmp_path):
                     os.path.join(ROOT, "tests", "cpp", "launcher_demo.cpp"), "-o", str(out), "-L", pkg_dir,
                     "-lgptoss_b200", f"-Wl,-rpath,{pkg_dir}"], check=True)
     assert out.exists()
+
+
+def test_exp2_table_of_the_device_expf():
+    """The 32-entry table in csrc/exact_math.cuh is bits(2^(i/32)) - (i << 47), with 2^(i/32)
+    correctly rounded to double: recomputed here at 60 decimal digits."""
+    import decimal
+    import re
+    import struct
+    src = open(os.path.join(ROOT, "optimize_inference_gpt-oss_b200", "csrc", "exact_math.cuh")).read()
+    body = src[src.index("kExp2Tab32[32]"):]
+    body = body[:body.index("};")]
+    table = [int(h, 16) for h in re.findall(r"0x([0-9a-f]{16})ull", body)]
+    assert len(table) == 32
+    decimal.getcontext().prec = 60
+    for i, t in enumerate(table):
+        exact = decimal.Decimal(2) ** (decimal.Decimal(i) / 32)
+        want = struct.unpack("<Q", struct.pack("<d", float(exact)))[0]   # float(Decimal) rounds correctly
+        assert (t + (i << 47)) & 0xFFFFFFFFFFFFFFFF == want, i
