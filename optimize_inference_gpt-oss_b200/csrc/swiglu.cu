@@ -18,7 +18,8 @@ namespace {
 // (1, 3 and 4 measured the same or slower on B200).  The exact form spends ~45 instructions per
 // output, nine of them in double precision: there the memory system is kept busy by other
 // blocks' loads while a block computes, so smaller pieces of work per block overlap better:
-// 1 group per thread 126 us per launch at 16,384 x 5760 fp32, 2 groups 139 us, 4 groups 175 us.
+// 1 group per thread 126 us per launch at 16,384 x 5760 fp32, 2 groups 139 us, 4 groups 175 us;
+// blocks of 128 threads another 3 % over 256 or 512.
 #ifndef GPTOSS_SWIGLU_UNROLL
 #define GPTOSS_SWIGLU_UNROLL 2
 #endif
@@ -26,7 +27,7 @@ namespace {
 #define GPTOSS_SWIGLU_UNROLL_EXACT 1
 #endif
 #ifndef GPTOSS_SWIGLU_THREADS_EXACT
-#define GPTOSS_SWIGLU_THREADS_EXACT 256
+#define GPTOSS_SWIGLU_THREADS_EXACT 128
 #endif
 template <bool EXACT> struct Shape {
   static constexpr int unroll = EXACT ? GPTOSS_SWIGLU_UNROLL_EXACT : GPTOSS_SWIGLU_UNROLL;
