@@ -98,6 +98,8 @@ def parse_args():
     ap.add_argument("--pdl", action="store_true",
                     help="launch the chain's kernels with programmatic stream serialization (GPTOSS_PDL); "
                          "measured neutral to slightly negative between these kernels, so off by default")
+    ap.add_argument("--bulk-stage", action="store_true",
+                    help="RoPE with its rows moved by the copy engine (GPTOSS_BULK_STAGE); measured slower, off by default")
     ap.add_argument("--fp32", action="store_true",
                     help="fp32 mode at the configuration's size: fp32 tensors everywhere and the "
                          "CPU program's rounding sequence (GPTOSS_EXACT); twice the bytes")
@@ -691,6 +693,8 @@ def main():
         c.flags |= pkg.PDL
     if args.split_embed_norm:
         c.flags |= pkg.CHAIN_SPLIT_EMBED_NORM
+    if args.bulk_stage:
+        c.flags |= pkg.BULK_STAGE
     sets = args.standin_sets or c.n_layers
     t_setup = time.perf_counter()
     chain = pkg.Chain(c, T, sets)

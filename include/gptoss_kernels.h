@@ -41,6 +41,11 @@
  *                 not even its tables, before the previous kernel has
  *                 completed.  These kernels do not signal early themselves, so
  *                 between two of them the flag is neutral.
+ *   GPTOSS_BULK_STAGE  gptoss_qkv_bias_rope only: rows are staged in shared memory by
+ *                 the copy engine (cp.async.bulk, one instruction per row, completion on
+ *                 an mbarrier, rows written back by a bulk store) instead of by 16-byte
+ *                 cp.async copies.  Same bits.  Slower than the default on B200 at every
+ *                 size measured, so off unless asked for; ignored by the other kernels.
  */
 #ifndef GPTOSS_KERNELS_H
 #define GPTOSS_KERNELS_H
@@ -77,6 +82,7 @@ enum {
   GPTOSS_EXACT = 1u,
   GPTOSS_FMA = 2u,
   GPTOSS_PDL = 4u,
+  GPTOSS_BULK_STAGE = 8u,
 };
 
 #define GPTOSS_MAX_TOPK 8      /* k of the router and of the combine */

@@ -23,7 +23,7 @@ INCLUDE_DIR = os.path.join(os.path.dirname(_HERE), "include")
 
 F32, BF16 = 0, 1
 OK, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_CUDA = 0, 1, 2, 3
-EXACT, FMA, PDL = 1, 2, 4
+EXACT, FMA, PDL, BULK_STAGE = 1, 2, 4, 8
 CHAIN_SPLIT_EMBED_NORM = 0x100  # chain only: gather and first norm as two launches
 MAX_TOPK, MAX_EXPERTS = 8, 256
 

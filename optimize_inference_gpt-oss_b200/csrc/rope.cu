@@ -78,16 +78,8 @@ __device__ __forceinline__ size_t chunk64_at(int b, int slot, int g, int i, int 
 // KV: the launch also writes the row's keys (bf16) and values (int8 codes + scale) into
 // the caches, from the fp32 values it holds in registers (head_dim is 64 then, so a head is
 // the 4 consecutive lanes of its 4 pieces and the value head's max |v| is two shuffles).
-#ifndef GPTOSS_ROPE_STAGES
-#define GPTOSS_ROPE_STAGES 2 // rows in the ring of the plain (no cache write) form
-#endif
-#ifdef GPTOSS_ROPE_BIAS_SMEM // experiment: the bias slice in shared memory, compiled for 4 blocks of 320 threads per SM
-#define GPTOSS_ROPE_BOUNDS __launch_bounds__(320, 4)
-#else
-#define GPTOSS_ROPE_BOUNDS
-#endif
 template <typename IT, typename OT, bool EXACT, bool FMA, int STAGES, bool KV>
-__global__ void GPTOSS_ROPE_BOUNDS bias_rope_rows(const IT *qkv_in, long in_stride, const float *__restrict__ bias,
+__global__ void bias_rope_rows(const IT *qkv_in, long in_stride, const float *__restrict__ bias,
                                const int *__restrict__ pos, int pos_scalar,
                                const float *__restrict__ cos_tab,
                                const float *__restrict__ sin_tab, int n_pos, int n_rot_heads,
@@ -106,16 +98,6 @@ __global__ void GPTOSS_ROPE_BOUNDS bias_rope_rows(const IT *qkv_in, long in_stri
   const int head = active ? threadIdx.x / pieces : 0, piece = active ? threadIdx.x - head * pieces : 0;
   const size_t lo = (size_t)head * head_dim + piece * 8, hi = lo + half;
   const bool rotates = head < n_rot_heads;
-#ifdef GPTOSS_ROPE_BIAS_SMEM
-  uint4 *bias_s = reinterpret_cast<uint4 *>(ring + (size_t)STAGES * stage_bytes); // [4][blockDim.x]
-  if (bias && active) {
-#pragma unroll
-    for (int q = 0; q < 2; q++) {
-      bias_s[q * blockDim.x + threadIdx.x] = ld_table(bias + lo + 4 * q);
-      bias_s[(2 + q) * blockDim.x + threadIdx.x] = ld_table(bias + hi + 4 * q);
-    }
-  }
-#else
   Vec8 ba, bb;
 #pragma unroll
   for (int i = 0; i < 8; i++)
@@ -124,7 +106,6 @@ __global__ void GPTOSS_ROPE_BOUNDS bias_rope_rows(const IT *qkv_in, long in_stri
     ba = load8<kTable>(bias, lo);
     bb = load8<kTable>(bias, hi);
   }
-#endif
 
   auto position = [&](long row) {
     int p = pos ? __ldg(pos + row) : pos_scalar;
@@ -186,19 +167,6 @@ __global__ void GPTOSS_ROPE_BOUNDS bias_rope_rows(const IT *qkv_in, long in_stri
       const unsigned char *sr = ring + (size_t)stage * stage_bytes;
       a = smem_load8<IT>(sr + lo * SI), b = smem_load8<IT>(sr + hi * SI);
       if (bias) {
-#ifdef GPTOSS_ROPE_BIAS_SMEM
-        Vec8 ba, bb;
-        {
-          const uint4 p0 = bias_s[threadIdx.x], p1 = bias_s[blockDim.x + threadIdx.x];
-          const uint4 q0 = bias_s[2 * blockDim.x + threadIdx.x], q1 = bias_s[3 * blockDim.x + threadIdx.x];
-          ba.v[0] = __uint_as_float(p0.x), ba.v[1] = __uint_as_float(p0.y), ba.v[2] = __uint_as_float(p0.z),
-          ba.v[3] = __uint_as_float(p0.w), ba.v[4] = __uint_as_float(p1.x), ba.v[5] = __uint_as_float(p1.y),
-          ba.v[6] = __uint_as_float(p1.z), ba.v[7] = __uint_as_float(p1.w);
-          bb.v[0] = __uint_as_float(q0.x), bb.v[1] = __uint_as_float(q0.y), bb.v[2] = __uint_as_float(q0.z),
-          bb.v[3] = __uint_as_float(q0.w), bb.v[4] = __uint_as_float(q1.x), bb.v[5] = __uint_as_float(q1.y),
-          bb.v[6] = __uint_as_float(q1.z), bb.v[7] = __uint_as_float(q1.w);
-        }
-#endif
 #pragma unroll
         for (int i = 0; i < 8; i++) {
           a.v[i] = __fadd_rn(a.v[i], ba.v[i]);
@@ -273,19 +241,18 @@ __global__ void GPTOSS_ROPE_BOUNDS bias_rope_rows(const IT *qkv_in, long in_stri
 // the bias slice stays in registers as above.  A stage is refilled right after the barrier
 // that ends its row's reads; an output buffer is reused only after the bulk store that read
 // it has finished reading (the issuing thread checks before the barrier of the row before).
+//
+// Asked for with GPTOSS_BULK_STAGE in flags; not the default, because on B200 it measured 5-10 %
+// slower than the 16-byte cp.async ring above at every ring depth tried (4096 rows: 17.7 us
+// against 16.8; that form needs no block barrier at all, this one needs one per row).
 #ifndef GPTOSS_ROPE_BULK_STAGES
 #define GPTOSS_ROPE_BULK_STAGES 3
 #endif
 #ifndef GPTOSS_ROPE_BULK_OUTS
 #define GPTOSS_ROPE_BULK_OUTS 2
 #endif
-#ifdef GPTOSS_ROPE_BULK_MINBLOCKS // blocks of up to 320 threads (the models' row) per SM to compile for
-#define GPTOSS_ROPE_BULK_BOUNDS __launch_bounds__(320, GPTOSS_ROPE_BULK_MINBLOCKS)
-#else
-#define GPTOSS_ROPE_BULK_BOUNDS
-#endif
 template <typename IT, typename OT, bool EXACT, bool FMA, int STAGES, int OUTS>
-__global__ void GPTOSS_ROPE_BULK_BOUNDS bias_rope_rows_bulk(const IT *qkv_in, long in_stride, const float *__restrict__ bias,
+__global__ void bias_rope_rows_bulk(const IT *qkv_in, long in_stride, const float *__restrict__ bias,
                                     const int *__restrict__ pos, int pos_scalar,
                                     const float *__restrict__ cos_tab, const float *__restrict__ sin_tab,
                                     int n_pos, int n_rot_heads, int n_heads, int head_dim, OT *qkv_out,
@@ -467,6 +434,7 @@ struct Args {
   long out_stride;
   int T;
   Cache cache; // cache.kc == nullptr: no cache write
+  bool bulk_stage; // GPTOSS_BULK_STAGE: rows moved by cp.async.bulk instead of 16-byte cp.async
 };
 
 template <typename IT, typename OT, bool EXACT, bool FMA, int STAGES, bool KV>
@@ -489,10 +457,6 @@ int launch_bulk(cudaStream_t s, const Args &a, int threads) {
   auto k = bias_rope_rows_bulk<IT, OT, EXACT, FMA, STAGES, OUTS>;
   const size_t width = (size_t)(a.n_q + 2 * a.n_kv) * a.head_dim;
   const size_t smem = STAGES * (width * sizeof(IT) + (size_t)a.head_dim * 4) + OUTS * width * sizeof(OT);
-#ifdef GPTOSS_ROPE_BULK_MINBLOCKS
-  if (threads > 320)
-    return GPTOSS_ERR_UNSUPPORTED;
-#endif
   const int per_sm = smem <= 200 * 1024 ? blocks_per_sm_smem(k, threads, smem) : 0;
   if (per_sm < 1)
     return GPTOSS_ERR_UNSUPPORTED;
@@ -517,32 +481,18 @@ template <typename IT, typename OT, bool EXACT, bool FMA> int launch(cudaStream_
     // rings (3 and 4 rows, which fit) measured slower on B200 -- 15.3 against 14.8 us per launch at
     // 4096 rows -- as did capping registers for a fourth resident block.
     int st = GPTOSS_ERR_UNSUPPORTED;
-#ifdef GPTOSS_ROPE_BULK
-    if (!a.cache.kc) {
+    if (a.bulk_stage && !a.cache.kc) { // the copy-engine form, on request (falls through if it does not fit)
       st = launch_bulk<IT, OT, EXACT, FMA>(s, a, threads);
       if (st != GPTOSS_ERR_UNSUPPORTED)
         return st;
     }
-#endif
     if (stage_bytes * 2 <= 220 * 1024) {
       if (a.cache.kc) { // with the cache write: 64-wide heads only, 16-byte key stores
         if (a.head_dim == 64 && aligned16(a.cache.kc))
-#ifdef GPTOSS_ROPE_BIAS_SMEM
-          st = threads <= 320 ? launch_pipe<IT, OT, EXACT, FMA, 2, true>(s, a, threads, stage_bytes * 2 + (size_t)threads * 64)
-                              : GPTOSS_ERR_UNSUPPORTED;
-#else
           st = launch_pipe<IT, OT, EXACT, FMA, 2, true>(s, a, threads, stage_bytes * 2);
-#endif
         return st;
       }
-#ifdef GPTOSS_ROPE_BIAS_SMEM
-      if (threads <= 320)
-        st = launch_pipe<IT, OT, EXACT, FMA, GPTOSS_ROPE_BIAS_SMEM, false>(
-            s, a, threads, stage_bytes * GPTOSS_ROPE_BIAS_SMEM + (size_t)threads * 64);
-      if (st != GPTOSS_ERR_UNSUPPORTED)
-        return st;
-#endif
-      st = launch_pipe<IT, OT, EXACT, FMA, GPTOSS_ROPE_STAGES, false>(s, a, threads, stage_bytes * GPTOSS_ROPE_STAGES);
+      st = launch_pipe<IT, OT, EXACT, FMA, 2, false>(s, a, threads, stage_bytes * 2);
       if (st != GPTOSS_ERR_UNSUPPORTED)
         return st;
     }
@@ -605,7 +555,8 @@ int run_bias_rope(gptoss_stream_t stream, int T, const void *qkv_in, gptoss_dtyp
     GPTOSS_SPAN(cache.slot_of_row, (size_t)T * 4);
   }
   const Args a{qkv_in, in_row_stride, bias,       pos,      pos_scalar, cos_tab,        sin_tab, n_pos,
-               n_q_heads, n_kv_heads, head_dim, qkv_out,  out_row_stride, T,     cache};
+               n_q_heads, n_kv_heads, head_dim, qkv_out,  out_row_stride, T,     cache,
+               (flags & GPTOSS_BULK_STAGE) != 0};
   cudaStream_t s = as_stream(stream);
   if (in_dtype == GPTOSS_F32)
     return out_dtype == GPTOSS_F32 ? launch_mode<float, float>(s, a, flags)

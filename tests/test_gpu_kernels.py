@@ -648,6 +648,45 @@ def test_bias_rope_with_cache_write_unaligned_cache_stores_the_same_bits(gpu, or
         assert np.array_equal(a.view(np.uint8), b.view(np.uint8)), what
 
 
+@pytest.mark.parametrize("T", [1, 5, 444, 1500])
+@pytest.mark.parametrize("idt,odt,mode", [("bf16", "bf16", "fast"), ("f32", "f32", "exact"), ("bf16", "f32", "fast"),
+                                          ("f32", "bf16", "exact_fma")])
+def test_bias_rope_bulk_stage_gives_the_same_bits(gpu, orc, T, idt, odt, mode):
+    """GPTOSS_BULK_STAGE moves the rows with the copy engine (cp.async.bulk + mbarrier in, bulk
+    store out) instead of 16-byte cp.async: every output word must equal the default kernel's,
+    with padded row strides, in place, with and without the bias, and no bounded wait may have
+    run out."""
+    pkg, d = gpu, Dev(gpu)
+    I, O = (pkg.BF16 if idt == "bf16" else pkg.F32), (pkg.BF16 if odt == "bf16" else pkg.F32)
+    flags = {"fast": 0, "exact": pkg.EXACT, "exact_fma": pkg.EXACT | pkg.FMA}[mode]
+    nq, nkv, row = 64, 8, 5120
+    r = rng_of("bulk", T, idt, odt)
+    qkv = widen(pkg, r.standard_normal((T, row)), I).reshape(T, row)
+    bias = (0.02 * r.standard_normal(row)).astype(np.float32)
+    pos = r.integers(-3, 4100, T).astype(np.int32)          # a few outside the table: clamped
+    ct, st = pkg.build_rope_tables(4096, 64)
+    dct, dst, dpos, dbias = d.put(ct), d.put(st), d.put(pos), d.put(bias)
+    before = pkg.load().gptoss_wait_giveups()
+    for in_stride, out_stride, with_bias in ((row, row, True), (row + 64, row + 8, True), (row, row, False)):
+        src = np.zeros((T, in_stride), np.float32)
+        src[:, :row] = qkv
+        outs = []
+        for extra in (0, pkg.BULK_STAGE):
+            o = d.out((T, out_stride), O)
+            pkg.qkv_bias_rope(T, d.put(src, I), I, in_stride, dbias if with_bias else None, dpos, 0, dct, dst, 4096,
+                              nq, nkv, 64, o, O, out_stride, flags=flags | extra)
+            outs.append(o.get(as_f32=False)[:, :row])
+        assert np.array_equal(outs[0].view(np.uint8), outs[1].view(np.uint8)), (in_stride, out_stride, with_bias)
+    if I == O:  # in place
+        res = []
+        for extra in (0, pkg.BULK_STAGE):
+            buf = d.put_inout(pkg.to_bf16_bits(qkv).reshape(T, row) if I == pkg.BF16 else qkv)
+            pkg.qkv_bias_rope(T, buf, I, row, dbias, dpos, 0, dct, dst, 4096, nq, nkv, 64, buf, O, row, flags=flags | extra)
+            res.append(buf.get(as_f32=False))
+        assert np.array_equal(res[0].view(np.uint8), res[1].view(np.uint8))
+    assert pkg.load().gptoss_wait_giveups() == before
+
+
 # ---- the argmax key as a public contract for logits producers --------------------------------
 
 def test_argmax_keys_finish_matches_argmax(gpu, orc):
