@@ -22,8 +22,10 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_SO = os.path.join(_HERE, "libgptoss_oracle.so")
 REF_SO = os.path.join(_HERE, "_ref", "libgptoss_ref.so")
-# where the reference project is checked out (only needed to build _ref/libgptoss_ref.so)
-REFERENCE_CHECKOUT = os.environ.get("GPTOSS_REFERENCE") or os.path.join(os.sep, "root", "reference")
+# where the reference project is checked out (only needed to build _ref/libgptoss_ref.so):
+# GPTOSS_REFERENCE, or a directory named "reference" beside this repository
+REFERENCE_CHECKOUT = os.environ.get("GPTOSS_REFERENCE") or os.path.abspath(
+    os.path.join(_HERE, os.pardir, os.pardir, "reference"))
 
 _f32p = np.ctypeslib.ndpointer(dtype=np.float32, flags="C_CONTIGUOUS")
 _i32p = np.ctypeslib.ndpointer(dtype=np.int32, flags="C_CONTIGUOUS")

@@ -59,7 +59,6 @@ def main():
     z = r.standard_normal((z_rows, H)).astype(np.float32)
     own = np.arange(T * k, dtype=np.int32)                    # the last 7 point past the end
     want_map = np.where(own < z_rows, own, -1).astype(np.int32).reshape(T, k)
-    want = orc.combine_rows(x, z, want_map, w, e, 32)
     for name, Hd in (("vector", H), ("scalar", 77)):
         zz, xx = np.ascontiguousarray(z[:, :Hd]), np.ascontiguousarray(x[:, :Hd])
         before = lib.gptoss_bounds_violations()
