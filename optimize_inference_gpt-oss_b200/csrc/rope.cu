@@ -233,6 +233,157 @@ __global__ void bias_rope_rows(const IT *qkv_in, long in_stride, const float *__
   cp_async_wait<0>();
 }
 
+// The ring above written out for 64-wide heads, the width of both models, so that everything
+// the general form computes per row from its arguments is a constant or a register here: a
+// head is 4 consecutive threads, byte offsets inside a stage are 32-bit and fixed per thread,
+// shared memory is addressed by 32-bit shared-space addresses, and the row, output and position
+// pointers advance by addition.  The general kernel executes 268 instructions per thread and
+// row at the models' shape and keeps the issue slots 72 % busy for 17 us (ncu); the
+// arithmetic itself -- 16 bias adds, 32 rotation operations, 24 conversions -- is a third of
+// that.  Same staging (ring of two rows, a cos/sin copy per warp through L1), same
+// arithmetic, same bits.
+__device__ __forceinline__ uint4 lds16(uint32_t a) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ void cp16_cg(uint32_t smem_dst, const void *gmem_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp16_ca(uint32_t smem_dst, const void *gmem_src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ Vec8 floats_of(uint4 a, uint4 b) {
+  Vec8 v;
+  v.v[0] = __uint_as_float(a.x), v.v[1] = __uint_as_float(a.y), v.v[2] = __uint_as_float(a.z),
+  v.v[3] = __uint_as_float(a.w), v.v[4] = __uint_as_float(b.x), v.v[5] = __uint_as_float(b.y),
+  v.v[6] = __uint_as_float(b.z), v.v[7] = __uint_as_float(b.w);
+  return v;
+}
+
+template <typename IT, typename OT, bool EXACT, bool FMA>
+__global__ void bias_rope_rows_hd64(const IT *qkv_in, long in_stride, const float *__restrict__ bias,
+                                    const int *__restrict__ pos, int pos_scalar,
+                                    const float *__restrict__ cos_tab, const float *__restrict__ sin_tab,
+                                    int n_pos, int n_rot_heads, int n_heads, OT *qkv_out, long out_stride, int T) {
+  pdl_prologue();
+  constexpr uint32_t SI = sizeof(IT), SO = sizeof(OT);
+  extern __shared__ __align__(16) unsigned char ring[];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, n_warps = blockDim.x >> 5;
+  const uint32_t row_bytes = (uint32_t)n_heads * 64u * SI, stage_bytes = row_bytes + (uint32_t)n_warps * 256u;
+  const int head = tid >> 2, piece = tid & 3;
+  const bool active = head < n_heads, rotates = head < n_rot_heads;
+  const uint32_t lo = (uint32_t)head * 64u + (uint32_t)piece * 8u; // first element of the thread's low run; the high run is 32 on
+
+  Vec8 ba, bb;
+#pragma unroll
+  for (int i = 0; i < 8; i++)
+    ba.v[i] = bb.v[i] = 0.0f;
+  if (bias && active) {
+    ba = load8<kTable>(bias, lo);
+    bb = load8<kTable>(bias, lo + 32);
+  }
+
+  // where things sit inside a stage, as byte offsets from the stage's shared-memory address
+  const uint32_t d_lo = lo * SI, d_hi = d_lo + 32u * SI;                        // this thread's two runs of the row
+  const uint32_t t_put = row_bytes + (uint32_t)warp * 256u + (uint32_t)lane * 16u; // lanes 0..15: the piece this lane copies
+  const uint32_t t_cos = row_bytes + (uint32_t)warp * 256u + (uint32_t)piece * 32u; // this thread's 8 cosines; sines 128 on
+  const float *trig_src = (lane < 8 ? cos_tab : sin_tab) + (lane & 7) * 4;      // + position * 32
+  uint32_t cur = smem_u32(ring), nxt = cur + stage_bytes;
+
+  const long step = gridDim.x;
+  long row = blockIdx.x;
+  if (row >= T)
+    return;
+  const unsigned char *in_row = reinterpret_cast<const unsigned char *>(qkv_in) + (size_t)row * in_stride * SI;
+  const size_t in_step = (size_t)step * in_stride * SI;
+  unsigned char *out_lo = reinterpret_cast<unsigned char *>(qkv_out) + (size_t)row * out_stride * SO + lo * SO;
+  const size_t out_step = (size_t)step * out_stride * SO;
+  const int *pos_at = pos ? pos + row : nullptr;
+
+  auto position = [&](const int *at) {
+    int p = at ? __ldg(at) : pos_scalar;
+    return p < 0 ? 0 : (p >= n_pos ? n_pos - 1 : p);
+  };
+  auto issue = [&](const unsigned char *src, uint32_t stage, int p) {
+    if (active) {
+      cp16_cg(stage + d_lo, src + d_lo);
+      cp16_cg(stage + d_hi, src + d_hi);
+      if constexpr (SI == 4) {
+        cp16_cg(stage + d_lo + 16, src + d_lo + 16);
+        cp16_cg(stage + d_hi + 16, src + d_hi + 16);
+      }
+    }
+    if (lane < 16)
+      cp16_ca(stage + t_put, trig_src + (size_t)p * 32);
+  };
+
+  issue(in_row, cur, position(pos_at));
+  cp_async_commit();
+  long ahead = row + step;
+  in_row += in_step;
+  if (pos_at)
+    pos_at += step;
+  int ahead_pos = ahead < T ? position(pos_at) : 0;
+  for (; row < T; row += step) {
+    if (ahead < T)
+      issue(in_row, nxt, ahead_pos);
+    cp_async_commit();
+    ahead += step;
+    in_row += in_step;
+    if (pos_at)
+      pos_at += step;
+    if (ahead < T)
+      ahead_pos = position(pos_at);
+    cp_async_wait<1>();
+    __syncwarp(); // the cos/sin pieces were copied by other lanes of this warp
+
+    if (active) {
+      Vec8 a, b;
+      if constexpr (SI == 2) {
+        a = widen8(lds16(cur + d_lo));
+        b = widen8(lds16(cur + d_hi));
+      } else {
+        a = floats_of(lds16(cur + d_lo), lds16(cur + d_lo + 16));
+        b = floats_of(lds16(cur + d_hi), lds16(cur + d_hi + 16));
+      }
+      if (bias) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          a.v[i] = __fadd_rn(a.v[i], ba.v[i]);
+          b.v[i] = __fadd_rn(b.v[i], bb.v[i]);
+        }
+      }
+      if (rotates) {
+        const Vec8 c = floats_of(lds16(cur + t_cos), lds16(cur + t_cos + 16));
+        const Vec8 sn = floats_of(lds16(cur + t_cos + 128), lds16(cur + t_cos + 144));
+        rotate8<EXACT, FMA>(a, b, c, sn);
+      }
+      if constexpr (SO == 2) {
+        st_stream(out_lo, make_uint4(pack_bf16(a.v[0], a.v[1]), pack_bf16(a.v[2], a.v[3]), pack_bf16(a.v[4], a.v[5]),
+                                     pack_bf16(a.v[6], a.v[7])));
+        st_stream(out_lo + 64, make_uint4(pack_bf16(b.v[0], b.v[1]), pack_bf16(b.v[2], b.v[3]),
+                                          pack_bf16(b.v[4], b.v[5]), pack_bf16(b.v[6], b.v[7])));
+      } else {
+        st_stream(out_lo, make_uint4(__float_as_uint(a.v[0]), __float_as_uint(a.v[1]), __float_as_uint(a.v[2]),
+                                     __float_as_uint(a.v[3])));
+        st_stream(out_lo + 16, make_uint4(__float_as_uint(a.v[4]), __float_as_uint(a.v[5]), __float_as_uint(a.v[6]),
+                                          __float_as_uint(a.v[7])));
+        st_stream(out_lo + 128, make_uint4(__float_as_uint(b.v[0]), __float_as_uint(b.v[1]), __float_as_uint(b.v[2]),
+                                           __float_as_uint(b.v[3])));
+        st_stream(out_lo + 144, make_uint4(__float_as_uint(b.v[4]), __float_as_uint(b.v[5]), __float_as_uint(b.v[6]),
+                                           __float_as_uint(b.v[7])));
+      }
+    }
+    out_lo += out_step;
+    __syncwarp(); // all lanes are done with this stage's cos/sin before it is refilled
+    const uint32_t t = cur;
+    cur = nxt;
+    nxt = t;
+  }
+  cp_async_wait<0>();
+}
+
 // The same operation with every row moved by the copy engine.  One thread asks for a whole
 // qkv row and the cos and sin rows of its position with three bulk copies that signal the
 // stage's mbarrier; the block rotates the row out of shared memory into one of OUTS output
@@ -481,6 +632,16 @@ template <typename IT, typename OT, bool EXACT, bool FMA> int launch(cudaStream_
     // rings (3 and 4 rows, which fit) measured slower on B200 -- 15.3 against 14.8 us per launch at
     // 4096 rows -- as did capping registers for a fourth resident block.
     int st = GPTOSS_ERR_UNSUPPORTED;
+    if (a.head_dim == 64 && !a.cache.kc && !a.bulk_stage && stage_bytes * 2 <= 220 * 1024) { // the models' head width
+      auto k = bias_rope_rows_hd64<IT, OT, EXACT, FMA>;
+      const int per_sm = blocks_per_sm_smem(k, threads, stage_bytes * 2);
+      if (per_sm >= 1) {
+        launch_kernel(k, dim3(row_grid(a.T, per_sm)), dim3(threads), stage_bytes * 2, s, static_cast<const IT *>(a.in),
+                      a.in_stride, a.bias, a.pos, a.pos_scalar, a.cos_tab, a.sin_tab, a.n_pos, n_rot, n_heads,
+                      static_cast<OT *>(a.out), a.out_stride, a.T);
+        return launch_status();
+      }
+    }
     if (a.bulk_stage && !a.cache.kc) { // the copy-engine form, on request (falls through if it does not fit)
       st = launch_bulk<IT, OT, EXACT, FMA>(s, a, threads);
       if (st != GPTOSS_ERR_UNSUPPORTED)
