@@ -17,15 +17,6 @@
 namespace gptoss {
 namespace {
 
-__device__ __forceinline__ Vec8 smem_chunk_f32(const unsigned char *p) {
-  const uint4 a = *reinterpret_cast<const uint4 *>(p), b = *reinterpret_cast<const uint4 *>(p + 16);
-  Vec8 v;
-  v.v[0] = __uint_as_float(a.x), v.v[1] = __uint_as_float(a.y), v.v[2] = __uint_as_float(a.z),
-  v.v[3] = __uint_as_float(a.w), v.v[4] = __uint_as_float(b.x), v.v[5] = __uint_as_float(b.y),
-  v.v[6] = __uint_as_float(b.z), v.v[7] = __uint_as_float(b.w);
-  return v;
-}
-
 template <int KM> struct Routing { // weights and expert ids of one token
   float w[KM];
   int e[KM];
@@ -37,33 +28,47 @@ template <int KM> struct RowIds { // where the token's expert rows are, and whet
 };
 
 // MODE 0: fast (choice order, FMA).  MODE 1: exact (increasing expert, separate
-// product and sum).  MODE 2: exact order with FMA.
-template <typename ZT, typename OT, int MODE, bool NORM, int KM, int NC, int STAGES>
+// product and sum).  MODE 2: exact order with FMA.  KEQ: k == KM is known at compile
+// time (the models' k = 4), which turns every "j < k" below into a constant.  Shared
+// memory is addressed by 32-bit shared-space addresses and per-thread byte offsets
+// that are fixed for the launch; a row's global addresses are one 64-bit
+// multiply-add each.  (The first form of this kernel, with generic pointers and a
+// run-time k throughout, executed 437 instructions per thread and token at the
+// models' shape and kept the issue slots 63 % busy at 36 % occupancy.)
+template <typename ZT, typename OT, int MODE, bool NORM, int KM, bool KEQ, int NC, int STAGES>
 __global__ void combine_rows(float *x, const ZT *__restrict__ Z, const int *__restrict__ own_row,
                              const float *__restrict__ topk_w, const int *__restrict__ topk_e,
-                             int k, int H, const int *__restrict__ phys_of,
+                             int k_arg, int H, const int *__restrict__ phys_of,
                              const float *__restrict__ norm_w, OT *__restrict__ out, int T, int z_rows,
                              int phys_n, unsigned int *oob) {
   pdl_prologue();
   constexpr bool EXACT = MODE != 0;
-  constexpr int SZ = sizeof(ZT);
+  constexpr uint32_t SZ = sizeof(ZT), SO = sizeof(OT);
   using Acc = typename std::conditional<EXACT, double, float>::type;
   extern __shared__ __align__(16) unsigned char ring[];
   __shared__ Acc scratch[2][32];
-  const size_t x_bytes = (size_t)H * 4, z_bytes = (size_t)H * SZ;
-  const size_t stage_bytes = x_bytes + (size_t)k * z_bytes;
+  const int k = KEQ ? KM : k_arg;
+  const uint32_t x_bytes = (uint32_t)H * 4u, z_bytes = (uint32_t)H * SZ;
+  const uint32_t stage_bytes = x_bytes + (uint32_t)k * z_bytes;
+  const uint32_t ring_a = smem_u32(ring);
   const int n_chunks = H >> 3;
 
+  // this thread's chunks: whether it has one, and its byte offset inside an fp32 row, an
+  // expert row and an output row
   bool has[NC];
+  uint32_t off_x[NC], off_z[NC], off_o[NC];
   [[maybe_unused]] Vec8 ws[NC];
 #pragma unroll
   for (int c = 0; c < NC; c++) {
     const int chunk = threadIdx.x + c * blockDim.x;
     has[c] = chunk < n_chunks;
+    off_x[c] = (uint32_t)chunk * 32u, off_z[c] = (uint32_t)chunk * 8u * SZ, off_o[c] = (uint32_t)chunk * 8u * SO;
     if constexpr (NORM)
       if (has[c])
         ws[c] = load8<kTable>(norm_w, (size_t)chunk * 8);
   }
+  unsigned char *const xb = reinterpret_cast<unsigned char *>(x);
+  const unsigned char *const zb = reinterpret_cast<const unsigned char *>(Z);
 
   // Routing data is tiny but every thread needs it.  Instead of every thread
   // loading every word, lane L of each warp loads one word of a token and the
@@ -73,8 +78,8 @@ __global__ void combine_rows(float *x, const ZT *__restrict__ Z, const int *__re
   // A pair whose own_row entry is negative has no expert row here (the grouping step writes
   // -1 for experts outside its range): nothing is read for it; its part of the stage is
   // filled with zeros by the copy instruction itself, so it adds nothing and the sum needs
-  // no test per pair.  Tokens with such a pair take a path of their own (one vote per token);
-  // the others run the plain copies.
+  // no test per pair.  Tokens with such a pair take a path of their own (one sign test per
+  // token on the broadcast row numbers); the others run the plain copies.
   const int lane = threadIdx.x & 31;
   auto load_ids_word = [&](long row) -> uint32_t {
     if (lane < k)
@@ -115,34 +120,33 @@ __global__ void combine_rows(float *x, const ZT *__restrict__ Z, const int *__re
     return r;
   };
   auto issue = [&](long row, int stage, const RowIds<KM> &ids) {
-    unsigned char *sx = ring + (size_t)stage * stage_bytes;
-    const float *xr = x + (size_t)row * H;
+    const uint32_t sx = ring_a + (uint32_t)stage * stage_bytes;
+    const unsigned char *xr = xb + (size_t)row * x_bytes;
 #pragma unroll
     for (int c = 0; c < NC; c++)
       if (has[c]) {
-        const int chunk = threadIdx.x + c * blockDim.x;
-        cp_async16(sx + (size_t)chunk * 32, xr + (size_t)chunk * 8);
-        cp_async16(sx + (size_t)chunk * 32 + 16, xr + (size_t)chunk * 8 + 4);
+        cp16_cg(sx + off_x[c], xr + off_x[c]);
+        cp16_cg(sx + off_x[c] + 16, xr + off_x[c] + 16);
         if (ids.live && ids.all_here) {
 #pragma unroll
           for (int j = 0; j < KM; j++)
             if (j < k) {
-              const ZT *zr = Z + (size_t)ids.row[j] * H + (size_t)chunk * 8;
-              unsigned char *sz = sx + x_bytes + (size_t)j * z_bytes + (size_t)chunk * 8 * SZ;
-              cp_async16(sz, zr);
+              const unsigned char *zr = zb + (size_t)(uint32_t)ids.row[j] * z_bytes + off_z[c];
+              const uint32_t sz = sx + x_bytes + (uint32_t)j * z_bytes + off_z[c];
+              cp16_cg(sz, zr);
               if constexpr (SZ == 4)
-                cp_async16(sz + 16, zr + 4);
+                cp16_cg(sz + 16, zr + 16);
             }
         } else if (ids.live) { // some pair has no row here: that pair's part of the stage becomes zeros, unread
 #pragma unroll
           for (int j = 0; j < KM; j++)
             if (j < k) {
-              unsigned char *sz = sx + x_bytes + (size_t)j * z_bytes + (size_t)chunk * 8 * SZ;
+              const uint32_t sz = sx + x_bytes + (uint32_t)j * z_bytes + off_z[c];
               const bool here = (unsigned)ids.row[j] < (unsigned)z_rows;
-              const ZT *zr = Z + (size_t)(here ? ids.row[j] : 0) * H + (size_t)chunk * 8;
-              cp_async16_or_zeros(sz, zr, here);
+              const unsigned char *zr = zb + (size_t)(here ? (uint32_t)ids.row[j] : 0u) * z_bytes + off_z[c];
+              cp16_cg_or_zeros(sz, zr, here);
               if constexpr (SZ == 4)
-                cp_async16_or_zeros(sz + 16, zr + 4, here);
+                cp16_cg_or_zeros(sz + 16, zr + 16, here);
 #ifdef GPTOSS_BOUNDS
               if (!here && ids.row[j] >= 0 && threadIdx.x == 0 && c == 0)
                 atomicAdd(oob, 1u); // a row number past the end of Z's allocation
@@ -208,16 +212,15 @@ __global__ void combine_rows(float *x, const ZT *__restrict__ Z, const int *__re
           }
     }
 
-    const unsigned char *sx = ring + (size_t)stage * stage_bytes;
-    float *xr = x + (size_t)row * H;
+    const uint32_t sx = ring_a + (uint32_t)stage * stage_bytes;
+    unsigned char *xr = xb + (size_t)row * x_bytes;
     Vec8 xs[NC];
     Acc ss = 0;
 #pragma unroll
     for (int c = 0; c < NC; c++) {
       if (!has[c])
         continue;
-      const int chunk = threadIdx.x + c * blockDim.x;
-      xs[c] = smem_chunk_f32(sx + (size_t)chunk * 32);
+      xs[c] = floats_of(lds16(sx + off_x[c]), lds16(sx + off_x[c] + 16));
       if (live) {
         Vec8 acc;
 #pragma unroll
@@ -236,12 +239,12 @@ __global__ void combine_rows(float *x, const ZT *__restrict__ Z, const int *__re
                 if (q == j)
                   wj = cur.w[q];
             }
-            const unsigned char *sz = sx + x_bytes + (size_t)j * z_bytes + (size_t)chunk * 8 * SZ;
+            const uint32_t sz = sx + x_bytes + (uint32_t)j * z_bytes + off_z[c];
             Vec8 z;
             if constexpr (SZ == 2)
-              z = widen8(*reinterpret_cast<const uint4 *>(sz));
+              z = widen8(lds16(sz));
             else
-              z = smem_chunk_f32(sz);
+              z = floats_of(lds16(sz), lds16(sz + 16));
 #pragma unroll
             for (int i = 0; i < 8; i++)
               acc.v[i] = MODE == 1 ? __fadd_rn(acc.v[i], __fmul_rn(z.v[i], wj)) : __fmaf_rn(z.v[i], wj, acc.v[i]);
@@ -249,7 +252,7 @@ __global__ void combine_rows(float *x, const ZT *__restrict__ Z, const int *__re
 #pragma unroll
         for (int i = 0; i < 8; i++)
           xs[c].v[i] = __fadd_rn(xs[c].v[i], acc.v[i]);
-        store8(xr, (size_t)chunk * 8, xs[c], false);
+        store8(reinterpret_cast<float *>(xr + off_x[c]), 0, xs[c], false);
       }
       if constexpr (NORM) {
 #pragma unroll
@@ -263,14 +266,14 @@ __global__ void combine_rows(float *x, const ZT *__restrict__ Z, const int *__re
     }
     if constexpr (NORM) {
       ss = block_sum<Acc>(ss, scratch[flip]);
-      OT *orow = out + (size_t)row * H;
+      unsigned char *orow = reinterpret_cast<unsigned char *>(out) + (size_t)row * ((size_t)H * SO);
       [[maybe_unused]] double inv_d = 0.0;
       [[maybe_unused]] float inv_f = 0.0f;
       if constexpr (EXACT) {
         const double m = __dadd_rn(__ddiv_rn(ss, (double)H), (double)GPTOSS_RMS_EPS);
         inv_d = (double)__fdiv_rn(1.0f, __fsqrt_rn((float)m));
       } else {
-        inv_f = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)H), GPTOSS_RMS_EPS)));
+        inv_f = fast_inv_rms(ss, H);
       }
 #pragma unroll
       for (int c = 0; c < NC; c++)
@@ -283,7 +286,7 @@ __global__ void combine_rows(float *x, const ZT *__restrict__ Z, const int *__re
             else
               o.v[i] = __fmul_rn(ws[c].v[i], __fmul_rn(inv_f, xs[c].v[i]));
           }
-          store8(orow, (size_t)(threadIdx.x + c * blockDim.x) * 8, o);
+          store8(reinterpret_cast<OT *>(orow + off_o[c]), 0, o);
         }
     }
     stage = stage + 1 == STAGES ? 0 : stage + 1;
@@ -360,7 +363,7 @@ __global__ void combine_rows_generic(float *x, const ZT *__restrict__ Z,
         for (int i = threadIdx.x; i < H; i += blockDim.x)
           store1(orow + i, (float)__dmul_rn((double)norm_w[i], __dmul_rn(inv, (double)xr[i])));
       } else {
-        const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)H), GPTOSS_RMS_EPS)));
+        const float inv = fast_inv_rms(ss, H);
         for (int i = threadIdx.x; i < H; i += blockDim.x)
           store1(orow + i, __fmul_rn(norm_w[i], __fmul_rn(inv, xr[i])));
       }
@@ -383,9 +386,9 @@ struct Args {
   unsigned int *oob;  // the checked build's device counter
 };
 
-template <typename ZT, typename OT, int MODE, bool NORM, int KM, int NC, int STAGES>
+template <typename ZT, typename OT, int MODE, bool NORM, int KM, bool KEQ, int NC, int STAGES>
 int launch_variant(cudaStream_t s, const Args &a, int threads, size_t smem) {
-  auto kern = combine_rows<ZT, OT, MODE, NORM, KM, NC, STAGES>;
+  auto kern = combine_rows<ZT, OT, MODE, NORM, KM, KEQ, NC, STAGES>;
   const int per_sm = blocks_per_sm_smem(kern, threads, smem);
   if (per_sm < 1)
     return GPTOSS_ERR_UNSUPPORTED;
@@ -395,15 +398,15 @@ int launch_variant(cudaStream_t s, const Args &a, int threads, size_t smem) {
   return launch_status();
 }
 
-template <typename ZT, typename OT, int MODE, bool NORM, int KM, int NC>
+template <typename ZT, typename OT, int MODE, bool NORM, int KM, bool KEQ, int NC>
 int launch_stages(cudaStream_t s, const Args &a, int threads, size_t stage_bytes, int stages) {
   if constexpr (NC > 1) // wide rows: a stage is tens of KB, two is what fits anyway
-    return launch_variant<ZT, OT, MODE, NORM, KM, NC, 2>(s, a, threads, stage_bytes * 2);
+    return launch_variant<ZT, OT, MODE, NORM, KM, KEQ, NC, 2>(s, a, threads, stage_bytes * 2);
   if (stages == 4)
-    return launch_variant<ZT, OT, MODE, NORM, KM, NC, 4>(s, a, threads, stage_bytes * 4);
+    return launch_variant<ZT, OT, MODE, NORM, KM, KEQ, NC, 4>(s, a, threads, stage_bytes * 4);
   if (stages == 3)
-    return launch_variant<ZT, OT, MODE, NORM, KM, NC, 3>(s, a, threads, stage_bytes * 3);
-  return launch_variant<ZT, OT, MODE, NORM, KM, NC, 2>(s, a, threads, stage_bytes * 2);
+    return launch_variant<ZT, OT, MODE, NORM, KM, KEQ, NC, 3>(s, a, threads, stage_bytes * 3);
+  return launch_variant<ZT, OT, MODE, NORM, KM, KEQ, NC, 2>(s, a, threads, stage_bytes * 2);
 }
 
 template <typename ZT, typename OT, int MODE, bool NORM> int launch(cudaStream_t s, const Args &a) {
@@ -421,12 +424,14 @@ template <typename ZT, typename OT, int MODE, bool NORM> int launch(cudaStream_t
     const int nc = n_chunks <= 512 ? 1 : 4;
     const int threads = ((n_chunks + nc - 1) / nc + 31) / 32 * 32;
     int st;
-    if (a.k <= 4)
-      st = nc == 1 ? launch_stages<ZT, OT, MODE, NORM, 4, 1>(s, a, threads, stage_bytes, stages)
-                   : launch_stages<ZT, OT, MODE, NORM, 4, 4>(s, a, threads, stage_bytes, stages);
+    if (a.k == 4 && nc == 1) // the models' shape: k known at compile time
+      st = launch_stages<ZT, OT, MODE, NORM, 4, true, 1>(s, a, threads, stage_bytes, stages);
+    else if (a.k <= 4)
+      st = nc == 1 ? launch_stages<ZT, OT, MODE, NORM, 4, false, 1>(s, a, threads, stage_bytes, stages)
+                   : launch_stages<ZT, OT, MODE, NORM, 4, false, 4>(s, a, threads, stage_bytes, stages);
     else
-      st = nc == 1 ? launch_stages<ZT, OT, MODE, NORM, 8, 1>(s, a, threads, stage_bytes, stages)
-                   : launch_stages<ZT, OT, MODE, NORM, 8, 4>(s, a, threads, stage_bytes, stages);
+      st = nc == 1 ? launch_stages<ZT, OT, MODE, NORM, 8, false, 1>(s, a, threads, stage_bytes, stages)
+                   : launch_stages<ZT, OT, MODE, NORM, 8, false, 4>(s, a, threads, stage_bytes, stages);
     if (st != GPTOSS_ERR_UNSUPPORTED)
       return st;
   }

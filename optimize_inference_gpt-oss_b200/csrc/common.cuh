@@ -300,6 +300,24 @@ __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.a
 // Device word counting bounded waits that ran out (current device); nullptr if unavailable.
 unsigned int *wait_giveups_word();
 
+// The same copies and the read-back by 32-bit shared-space address (smem_u32 of the buffer plus
+// a byte offset kept in a register): no generic-pointer arithmetic in a kernel's inner loop.
+__device__ __forceinline__ void cp16_cg(uint32_t smem_dst, const void *gmem_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp16_ca(uint32_t smem_dst, const void *gmem_src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp16_cg_or_zeros(uint32_t smem_dst, const void *gmem_src, bool take) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_dst), "l"(gmem_src), "r"(take ? 16 : 0)
+               : "memory");
+}
+__device__ __forceinline__ uint4 lds16(uint32_t a) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+  return v;
+}
+
 // Ring depth for a row kernel whose stage takes stage_bytes of shared memory:
 // deep enough to keep >= ~100 KB per SM in flight, shallow enough that two or
 // more blocks still fit on an SM (227 KB); 0 if even two stages do not fit.
@@ -353,6 +371,24 @@ __device__ __forceinline__ float fast_rcp(float x) {
 struct Vec8 {
   float v[8];
 };
+__device__ __forceinline__ Vec8 floats_of(uint4 a, uint4 b) {
+  Vec8 v;
+  v.v[0] = __uint_as_float(a.x), v.v[1] = __uint_as_float(a.y), v.v[2] = __uint_as_float(a.z),
+  v.v[3] = __uint_as_float(a.w), v.v[4] = __uint_as_float(b.x), v.v[5] = __uint_as_float(b.y),
+  v.v[6] = __uint_as_float(b.z), v.v[7] = __uint_as_float(b.w);
+  return v;
+}
+
+// 1 / sqrt(ss / H + eps) of the bf16-activation mode: one reciprocal, one fused multiply-add, one
+// reciprocal square root on the special-function unit (about 2 ulp).  The IEEE division, root
+// and division of the fp32 mode cost some 30 instructions per thread and row, a tenth of a row
+// kernel's whole instruction count.
+__device__ __forceinline__ float fast_inv_rms(float ss, int H) {
+  const float m = fmaf(ss, fast_rcp((float)H), GPTOSS_RMS_EPS);
+  float r;
+  asm("rsqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(m));
+  return r;
+}
 
 enum { kStream = 0, kPlain = 1, kTable = 2 };
 

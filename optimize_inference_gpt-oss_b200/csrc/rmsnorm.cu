@@ -25,14 +25,12 @@ template <> struct YSize<NoY> {
 };
 
 // fp32 mode scale: run.cpp:326-331 -- mean and eps in double, reciprocal root
-// in float.  bf16 mode: kernels/fast_misc.hpp:29 in fp32.
+// in float.  bf16 mode: kernels/fast_misc.hpp:29 in fp32, with the approximate reciprocal root
+// (fast_inv_rms in common.cuh).
 __device__ __forceinline__ double exact_inv_rms(double ss, int H) {
   double m = __ddiv_rn(ss, (double)H);
   m = __dadd_rn(m, (double)GPTOSS_RMS_EPS);
   return (double)__fdiv_rn(1.0f, __fsqrt_rn((float)m));
-}
-__device__ __forceinline__ float fast_inv_rms(float ss, int H) {
-  return __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)H), GPTOSS_RMS_EPS)));
 }
 
 template <typename YT, typename OT, bool EXACT, int NC, int STAGES>

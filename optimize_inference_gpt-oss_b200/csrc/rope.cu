@@ -242,25 +242,6 @@ __global__ void bias_rope_rows(const IT *qkv_in, long in_stride, const float *__
 // arithmetic itself -- 16 bias adds, 32 rotation operations, 24 conversions -- is a third of
 // that.  Same staging (ring of two rows, a cos/sin copy per warp through L1), same
 // arithmetic, same bits.
-__device__ __forceinline__ uint4 lds16(uint32_t a) {
-  uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
-  return v;
-}
-__device__ __forceinline__ void cp16_cg(uint32_t smem_dst, const void *gmem_src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(gmem_src) : "memory");
-}
-__device__ __forceinline__ void cp16_ca(uint32_t smem_dst, const void *gmem_src) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(gmem_src) : "memory");
-}
-__device__ __forceinline__ Vec8 floats_of(uint4 a, uint4 b) {
-  Vec8 v;
-  v.v[0] = __uint_as_float(a.x), v.v[1] = __uint_as_float(a.y), v.v[2] = __uint_as_float(a.z),
-  v.v[3] = __uint_as_float(a.w), v.v[4] = __uint_as_float(b.x), v.v[5] = __uint_as_float(b.y),
-  v.v[6] = __uint_as_float(b.z), v.v[7] = __uint_as_float(b.w);
-  return v;
-}
-
 template <typename IT, typename OT, bool EXACT, bool FMA>
 __global__ void bias_rope_rows_hd64(const IT *qkv_in, long in_stride, const float *__restrict__ bias,
                                     const int *__restrict__ pos, int pos_scalar,
