@@ -585,7 +585,8 @@ def vocab_ops(pkg, args, work: Work, world, rank, local_rank, dist, sharding, ba
         us = 1e3 * max(0.0, timed(g) - flush_ms)
         g.close()
         gbs = nbytes / (us * 1e-6) / 1e9 if us > 0 else 0.0
-        kernels[name] = {"launches_per_step": launches, "us_per_launch": round(us, 3), "bytes_per_launch": nbytes,
+        kernels[name] = {"launches_per_step": launches, "us_per_launch": round(us, 3), "flush_us": round(1e3 * flush_ms, 2),
+                         "bytes_per_launch": nbytes,
                          "achieved_gbs": round(gbs, 1), "frac": round(gbs / peak, 4),
                          "pct_of_nominal_8tbs": round(gbs / 80.0, 1)}
     step_bytes = sum(k["bytes_per_launch"] for k in kernels.values())

@@ -179,19 +179,19 @@ __global__ void add_rmsnorm_tile(float *x, const YT *__restrict__ y, const float
   const long row0 = (long)blockIdx.x * R;
   const size_t row_bytes = (size_t)H * (4 + SY);
 
+  const uint32_t rows_a = smem_u32(rows), my_x = (uint32_t)chunk * 32u, my_y = (uint32_t)H * 4u + (uint32_t)chunk * 8u * SY;
 #pragma unroll
   for (int r = 0; r < R; r++)
     if (has && row0 + r < T) {
-      unsigned char *sx = rows + r * row_bytes;
+      const uint32_t sx = rows_a + (uint32_t)r * (uint32_t)row_bytes;
       const float *xr = x + (size_t)(row0 + r) * H + (size_t)chunk * 8;
-      cp_async16(sx + (size_t)chunk * 32, xr);
-      cp_async16(sx + (size_t)chunk * 32 + 16, xr + 4);
+      cp16_cg(sx + my_x, xr);
+      cp16_cg(sx + my_x + 16, xr + 4);
       if constexpr (HAS_Y) {
-        unsigned char *sy = sx + (size_t)H * 4 + (size_t)chunk * 8 * SY;
         const YT *yr = y + (size_t)(row0 + r) * H + (size_t)chunk * 8;
-        cp_async16(sy, yr);
+        cp16_cg(sx + my_y, yr);
         if constexpr (SY == 4)
-          cp_async16(sy + 16, yr + 4);
+          cp16_cg(sx + my_y + 16, yr + 4);
       }
     }
   cp_async_commit();
@@ -206,23 +206,14 @@ __global__ void add_rmsnorm_tile(float *x, const YT *__restrict__ y, const float
   for (int r = 0; r < R; r++) {
     Acc ss = 0;
     if (has && row0 + r < T) {
-      const unsigned char *sx = rows + r * row_bytes;
-      const uint4 a = *reinterpret_cast<const uint4 *>(sx + (size_t)chunk * 32);
-      const uint4 b = *reinterpret_cast<const uint4 *>(sx + (size_t)chunk * 32 + 16);
-      xs[r].v[0] = __uint_as_float(a.x), xs[r].v[1] = __uint_as_float(a.y), xs[r].v[2] = __uint_as_float(a.z),
-      xs[r].v[3] = __uint_as_float(a.w), xs[r].v[4] = __uint_as_float(b.x), xs[r].v[5] = __uint_as_float(b.y),
-      xs[r].v[6] = __uint_as_float(b.z), xs[r].v[7] = __uint_as_float(b.w);
+      const uint32_t sx = rows_a + (uint32_t)r * (uint32_t)row_bytes;
+      xs[r] = floats_of(lds16(sx + my_x), lds16(sx + my_x + 16));
       if constexpr (HAS_Y) {
-        const unsigned char *sy = sx + (size_t)H * 4 + (size_t)chunk * 8 * SY;
         Vec8 ys;
-        if constexpr (SY == 2) {
-          ys = widen8(*reinterpret_cast<const uint4 *>(sy));
-        } else {
-          const uint4 p = *reinterpret_cast<const uint4 *>(sy), q = *reinterpret_cast<const uint4 *>(sy + 16);
-          ys.v[0] = __uint_as_float(p.x), ys.v[1] = __uint_as_float(p.y), ys.v[2] = __uint_as_float(p.z),
-          ys.v[3] = __uint_as_float(p.w), ys.v[4] = __uint_as_float(q.x), ys.v[5] = __uint_as_float(q.y),
-          ys.v[6] = __uint_as_float(q.z), ys.v[7] = __uint_as_float(q.w);
-        }
+        if constexpr (SY == 2)
+          ys = widen8(lds16(sx + my_y));
+        else
+          ys = floats_of(lds16(sx + my_y), lds16(sx + my_y + 16));
 #pragma unroll
         for (int i = 0; i < 8; i++)
           xs[r].v[i] = __fadd_rn(xs[r].v[i], ys.v[i]);
