@@ -165,95 +165,102 @@ __global__ void add_rmsnorm_rows(float *x, const YT *__restrict__ y, const float
 // with one barrier and exits; the hardware scheduler keeps the SMs stocked with fresh
 // blocks.  Same chunk-to-thread mapping and summation order as the ring with one chunk
 // per thread, hence the same bits.
-template <typename YT, typename OT, bool EXACT, int R>
+#ifndef GPTOSS_NORM_TILE_NC
+#define GPTOSS_NORM_TILE_NC 1 // chunks of 8 elements per thread in the one-row form
+#endif
+template <typename YT, typename OT, bool EXACT, int NC>
 __global__ void add_rmsnorm_tile(float *x, const YT *__restrict__ y, const float *__restrict__ w, OT *out,
                                  int T, int H) {
   pdl_prologue();
   constexpr bool HAS_Y = !std::is_same<YT, NoY>::value;
-  constexpr int SY = YSize<YT>::value;
+  constexpr uint32_t SY = YSize<YT>::value;
   using Acc = typename std::conditional<EXACT, double, float>::type;
-  extern __shared__ __align__(16) unsigned char rows[]; // R x (x row, delta row)
-  __shared__ Acc scratch[R][32];
-  const int chunk = threadIdx.x;
-  const bool has = chunk < (H >> 3);
-  const long row0 = (long)blockIdx.x * R;
-  const size_t row_bytes = (size_t)H * (4 + SY);
-
-  const uint32_t rows_a = smem_u32(rows), my_x = (uint32_t)chunk * 32u, my_y = (uint32_t)H * 4u + (uint32_t)chunk * 8u * SY;
+  extern __shared__ __align__(16) unsigned char rows[]; // the x row, then the delta row
+  __shared__ Acc scratch[32];
+  const long row = blockIdx.x;
+  const uint32_t rows_a = smem_u32(rows);
+  bool has[NC];
+  uint32_t my_x[NC], my_y[NC];
 #pragma unroll
-  for (int r = 0; r < R; r++)
-    if (has && row0 + r < T) {
-      const uint32_t sx = rows_a + (uint32_t)r * (uint32_t)row_bytes;
-      const float *xr = x + (size_t)(row0 + r) * H + (size_t)chunk * 8;
-      cp16_cg(sx + my_x, xr);
-      cp16_cg(sx + my_x + 16, xr + 4);
+  for (int c = 0; c < NC; c++) {
+    const int chunk = threadIdx.x + c * blockDim.x;
+    has[c] = chunk < (H >> 3);
+    my_x[c] = (uint32_t)chunk * 32u, my_y[c] = (uint32_t)H * 4u + (uint32_t)chunk * 8u * SY;
+  }
+#pragma unroll
+  for (int c = 0; c < NC; c++)
+    if (has[c]) {
+      const unsigned char *xr = reinterpret_cast<const unsigned char *>(x + (size_t)row * H) + my_x[c];
+      cp16_cg(rows_a + my_x[c], xr);
+      cp16_cg(rows_a + my_x[c] + 16, xr + 16);
       if constexpr (HAS_Y) {
-        const YT *yr = y + (size_t)(row0 + r) * H + (size_t)chunk * 8;
-        cp16_cg(sx + my_y, yr);
+        const unsigned char *yr = reinterpret_cast<const unsigned char *>(y + (size_t)row * H) + (my_y[c] - (uint32_t)H * 4u);
+        cp16_cg(rows_a + my_y[c], yr);
         if constexpr (SY == 4)
-          cp16_cg(sx + my_y + 16, yr + 4);
+          cp16_cg(rows_a + my_y[c] + 16, yr + 16);
       }
     }
   cp_async_commit();
-  Vec8 ws;
-  if (has)
-    ws = load8<kTable>(w, (size_t)chunk * 8);
+  Vec8 ws[NC];
+#pragma unroll
+  for (int c = 0; c < NC; c++)
+    if (has[c])
+      ws[c] = load8<kTable>(w, (size_t)(threadIdx.x + c * blockDim.x) * 8);
   cp_async_wait<0>(); // a thread reads back only what it copied itself: no barrier needed
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = (blockDim.x + 31) >> 5;
-  Vec8 xs[R];
+  Vec8 xs[NC];
+  Acc ss = 0;
 #pragma unroll
-  for (int r = 0; r < R; r++) {
-    Acc ss = 0;
-    if (has && row0 + r < T) {
-      const uint32_t sx = rows_a + (uint32_t)r * (uint32_t)row_bytes;
-      xs[r] = floats_of(lds16(sx + my_x), lds16(sx + my_x + 16));
+  for (int c = 0; c < NC; c++)
+    if (has[c]) {
+      xs[c] = floats_of(lds16(rows_a + my_x[c]), lds16(rows_a + my_x[c] + 16));
       if constexpr (HAS_Y) {
         Vec8 ys;
         if constexpr (SY == 2)
-          ys = widen8(lds16(sx + my_y));
+          ys = widen8(lds16(rows_a + my_y[c]));
         else
-          ys = floats_of(lds16(sx + my_y), lds16(sx + my_y + 16));
+          ys = floats_of(lds16(rows_a + my_y[c]), lds16(rows_a + my_y[c] + 16));
 #pragma unroll
         for (int i = 0; i < 8; i++)
-          xs[r].v[i] = __fadd_rn(xs[r].v[i], ys.v[i]);
+          xs[c].v[i] = __fadd_rn(xs[c].v[i], ys.v[i]);
       }
 #pragma unroll
       for (int i = 0; i < 8; i++) {
         if constexpr (EXACT)
-          ss = __dadd_rn(ss, (double)__fmul_rn(xs[r].v[i], xs[r].v[i]));
+          ss = __dadd_rn(ss, (double)__fmul_rn(xs[c].v[i], xs[c].v[i]));
         else
-          ss = fmaf(xs[r].v[i], xs[r].v[i], ss);
+          ss = fmaf(xs[c].v[i], xs[c].v[i], ss);
       }
     }
-    ss = warp_sum(ss);
-    if (lane == 0)
-      scratch[r][warp] = ss;
-  }
+  ss = warp_sum(ss);
+  if (lane == 0)
+    scratch[warp] = ss;
   __syncthreads();
+  Acc t = lane < n_warps ? scratch[lane] : Acc(0);
+  t = warp_sum(t); // every lane takes part, also those without a chunk
+  [[maybe_unused]] double inv_d = 0.0;
+  [[maybe_unused]] float inv_f = 0.0f;
+  if constexpr (EXACT)
+    inv_d = exact_inv_rms(t, H);
+  else
+    inv_f = fast_inv_rms(t, H);
 #pragma unroll
-  for (int r = 0; r < R; r++) {
-    Acc t = lane < n_warps ? scratch[r][lane] : Acc(0);
-    t = warp_sum(t); // every lane takes part, also those without a chunk
-    if (!has || row0 + r >= T)
-      continue;
-    const size_t e = (size_t)chunk * 8;
-    if constexpr (HAS_Y)
-      store8(x + (size_t)(row0 + r) * H, e, xs[r], false);
-    Vec8 o;
-    if constexpr (EXACT) {
-      const double inv = exact_inv_rms(t, H);
+  for (int c = 0; c < NC; c++)
+    if (has[c]) {
+      const size_t e = (size_t)(threadIdx.x + c * blockDim.x) * 8;
+      if constexpr (HAS_Y)
+        store8(x + (size_t)row * H, e, xs[c], false);
+      Vec8 o;
 #pragma unroll
-      for (int i = 0; i < 8; i++)
-        o.v[i] = (float)__dmul_rn((double)ws.v[i], __dmul_rn(inv, (double)xs[r].v[i]));
-    } else {
-      const float inv = fast_inv_rms(t, H);
-#pragma unroll
-      for (int i = 0; i < 8; i++)
-        o.v[i] = __fmul_rn(ws.v[i], __fmul_rn(inv, xs[r].v[i]));
+      for (int i = 0; i < 8; i++) {
+        if constexpr (EXACT)
+          o.v[i] = (float)__dmul_rn((double)ws[c].v[i], __dmul_rn(inv_d, (double)xs[c].v[i]));
+        else
+          o.v[i] = __fmul_rn(ws[c].v[i], __fmul_rn(inv_f, xs[c].v[i]));
+      }
+      store8(out + (size_t)row * H, e, o);
     }
-    store8(out + (size_t)(row0 + r) * H, e, o);
-  }
 }
 
 // Embedding gather fused with the norm that follows it (gptoss_embed_rmsnorm): the same
@@ -558,9 +565,10 @@ int launch(cudaStream_t s, int T, float *x, const void *y, const float *w, void 
     const size_t smem = stage_bytes * stages;
     int st = GPTOSS_ERR_UNSUPPORTED;
     if (nc == 1) { // H <= 4096: one row per block, no loop (measured against 2 and 4 rows per block and the ring)
-      auto k = add_rmsnorm_tile<YT, OT, EXACT, 1>;
-      if (blocks_per_sm_smem(k, threads, stage_bytes) >= 1) {
-        launch_kernel(k, dim3((unsigned)T), dim3(threads), stage_bytes, s, x, yp, w, op, T, H);
+      auto k = add_rmsnorm_tile<YT, OT, EXACT, GPTOSS_NORM_TILE_NC>;
+      const int tile_threads = ((n_chunks + GPTOSS_NORM_TILE_NC - 1) / GPTOSS_NORM_TILE_NC + 31) / 32 * 32;
+      if (blocks_per_sm_smem(k, tile_threads, stage_bytes) >= 1) {
+        launch_kernel(k, dim3((unsigned)T), dim3(tile_threads), stage_bytes, s, x, yp, w, op, T, H);
         return launch_status();
       }
     }
