@@ -209,14 +209,6 @@ __device__ __forceinline__ void cp_async16(void *smem_dst, const void *gmem_src)
   const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
 }
-// The same with the source optional: when `take` is false nothing is read and the 16 bytes
-// are filled with zeros (the instruction's source-size operand), so a caller can leave a
-// piece out without a branch.  gmem_src must still be a valid address.
-__device__ __forceinline__ void cp_async16_or_zeros(void *smem_dst, const void *gmem_src, bool take) {
-  const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gmem_src), "r"(take ? 16 : 0)
-               : "memory");
-}
 // The same through L1 (.ca): for small read-only tables that many rows, warps and
 // blocks of an SM ask for again and again (a position's cos/sin row).  Kept in L1, the
 // repeats never reach L2 -- when a whole batch sits at one position every block wants
@@ -224,10 +216,6 @@ __device__ __forceinline__ void cp_async16_or_zeros(void *smem_dst, const void *
 __device__ __forceinline__ void cp_async16_cached(void *smem_dst, const void *gmem_src) {
   const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
   asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
-}
-__device__ __forceinline__ void cp_async4(void *smem_dst, const void *gmem_src) {
-  const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(gmem_src) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() {
@@ -308,6 +296,9 @@ __device__ __forceinline__ void cp16_cg(uint32_t smem_dst, const void *gmem_src)
 __device__ __forceinline__ void cp16_ca(uint32_t smem_dst, const void *gmem_src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(gmem_src) : "memory");
 }
+// With the source optional: when `take` is false nothing is read and the 16 bytes are filled
+// with zeros (the instruction's source-size operand), so a caller can leave a piece out
+// without a branch.  gmem_src must still be a valid address.
 __device__ __forceinline__ void cp16_cg_or_zeros(uint32_t smem_dst, const void *gmem_src, bool take) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_dst), "l"(gmem_src), "r"(take ? 16 : 0)
                : "memory");
