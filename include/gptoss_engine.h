@@ -125,7 +125,7 @@ typedef struct {
 
 /* gpt-oss-20b (24 layers, 32 experts) or gpt-oss-120b (36 layers, 128 experts)
  * shapes (export_model_bin/gpt-oss-20b/config.json and gpt-oss-120b/config.json).
- * which: 20 or 120. */
+ * which: 20 or 120.  flags come back as GPTOSS_PDL, plus GPTOSS_EXACT for fp32 tensors. */
 GPTOSS_API int gptoss_chain_config_gpt_oss(int which, gptoss_dtype_t act_dtype, int max_pos,
                                            gptoss_chain_config_t *cfg);
 

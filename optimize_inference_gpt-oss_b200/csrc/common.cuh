@@ -102,15 +102,15 @@ inline size_t dtype_size(gptoss_dtype_t d) { return d == GPTOSS_F32 ? 4 : 2; }
 //
 // No kernel here signals its dependents early (griddepcontrol.launch_dependents): the
 // next kernel's blocks become schedulable only when this grid's blocks have exited.
-// Signalling at block start, before or after the wait, was measured on B200 and made the
-// 24-layer chain 15 % slower (and no faster at 64 or 512 tokens): blocks of kernels ahead
-// in the stream became resident, sat in their wait, and took the SM slots that the
-// persistent grids of the kernels actually running count on having all at once.  The flag
-// Signalling late instead (a row kernel's block when it starts its last row, a one-shot
-// grid's blocks after their wait, so that at most two kernels are ever resident) was also
-// measured: 1 % slower than not signalling.  The flag therefore pays off only behind a
-// producer that signals early itself (a GEMM with a programmatic-launch epilogue); between
-// these kernels it is neutral.
+// Signalling at block start was measured on B200 more than once: with the first round's
+// kernels it made the 24-layer chain 15 % slower (blocks of kernels ahead in the stream
+// became resident, sat in their wait, and took the SM slots that the persistent grids of
+// the kernels actually running count on having all at once); with the current kernels
+// 0.5 % slower at 4096 tokens and 8 % slower at 512 than the attribute alone.  Signalling
+// late (a row kernel's block when it starts its last row) was 1 % slower than not
+// signalling.  The attribute alone -- the launch may be set up while the previous kernel
+// drains, and its completion need not be flushed to the host's view first -- is what pays:
+// 3.14 -> 3.08 ms per step at 4096 tokens, 0.606 -> 0.541 ms at 512.
 __device__ __forceinline__ void pdl_prologue() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // ---- the checked build (-DGPTOSS_BOUNDS) --------------------------------------------

@@ -139,14 +139,15 @@ def test_chain_with_programmatic_dependent_launch(gpu, orc):
     bits as without it (graph replay and plain launches alike)."""
     pkg = gpu
     outs = []
-    for flags in (0, pkg.PDL):
+    assert _small_config(pkg, pkg.BF16).flags & pkg.PDL, "the chain's default"
+    for with_pdl in (False, True):
         c = _small_config(pkg, pkg.BF16)
-        c.flags |= flags
+        c.flags = (c.flags | pkg.PDL) if with_pdl else (c.flags & ~pkg.PDL)
         got_x, _ = _run_and_compare(pkg, orc, c, 200, 3, TOL_BF16, seed=15)
         outs.append(got_x)
     assert n_bit_diff(outs[0], outs[1]) == 0
     c = _small_config(pkg, pkg.F32)
-    c.flags |= pkg.PDL
+    c.flags &= ~pkg.PDL
     _run_and_compare(pkg, orc, c, 64, 3, TOL_F32, seed=11)
 
 
