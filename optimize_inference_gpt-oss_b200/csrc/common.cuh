@@ -102,11 +102,12 @@ inline size_t dtype_size(gptoss_dtype_t d) { return d == GPTOSS_F32 ? 4 : 2; }
 //
 // No kernel here signals its dependents early (griddepcontrol.launch_dependents): the
 // next kernel's blocks become schedulable only when this grid's blocks have exited.
-// Signalling at block start was measured on B200 more than once: with the first round's
+// Signalling at block start was measured on B200 more than once: with an earlier form of the
 // kernels it made the 24-layer chain 15 % slower (blocks of kernels ahead in the stream
 // became resident, sat in their wait, and took the SM slots that the persistent grids of
 // the kernels actually running count on having all at once); with the current kernels
-// 0.5 % slower at 4096 tokens and 8 % slower at 512 than the attribute alone.  Signalling
+// 0.5 % slower at 4096 tokens and 8 % slower at 512 than the attribute alone (2 % slower at 512
+// when only the one-shot grids signal).  Signalling
 // late (a row kernel's block when it starts its last row) was 1 % slower than not
 // signalling.  The attribute alone -- the launch may be set up while the previous kernel
 // drains, and its completion need not be flushed to the host's view first -- is what pays:
