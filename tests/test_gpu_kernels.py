@@ -687,6 +687,49 @@ def test_bias_rope_bulk_stage_gives_the_same_bits(gpu, orc, T, idt, odt, mode):
     assert pkg.load().gptoss_wait_giveups() == before
 
 
+def test_graph_capture_replays_the_recorded_launches(gpu, orc):
+    """gptoss_graph_begin / _end / _launch: three kernels recorded on a stream of the library
+    and replayed twice give what the same three direct calls give."""
+    pkg, d = gpu, Dev(gpu)
+    T, Hd, k, E = 50, 2880, 4, 32
+    r = rng_of("graph")
+    x = r.standard_normal((T, Hd)).astype(np.float32)
+    delta = widen(pkg, r.standard_normal((T, Hd)), pkg.BF16).reshape(T, Hd)
+    gain = (1 + 0.1 * r.standard_normal(Hd)).astype(np.float32)
+    y = widen(pkg, 2 * r.standard_normal((T * k, 2 * Hd)), pkg.BF16).reshape(T * k, 2 * Hd)
+    scores = r.standard_normal((T, E)).astype(np.float32)
+    dd, dg, dy, dsc = d.put(delta, pkg.BF16), d.put(gain), d.put(y, pkg.BF16), d.put(scores)
+    st = pkg.Stream()
+
+    def run(xb, o, g_out, w, e, stream):
+        pkg.add_rmsnorm(T, xb, dd, pkg.BF16, dg, o, pkg.BF16, Hd, stream=stream)
+        pkg.swiglu(dy, pkg.BF16, g_out, pkg.BF16, T * k, Hd, stream=stream)
+        pkg.router_topk(T, dsc, pkg.F32, E, k, w, e, stream=stream)
+
+    direct = (d.put_inout(x), d.out((T, Hd), pkg.BF16), d.out((T * k, Hd), pkg.BF16), d.out((T, k), np.float32),
+              d.out((T, k), np.int32))
+    run(*direct, None)
+    pkg.synchronize()
+    run(*direct, None)  # x is updated in place: two direct calls = two replays
+    pkg.synchronize()
+    replay = (d.put_inout(x), d.out((T, Hd), pkg.BF16), d.out((T * k, Hd), pkg.BF16), d.out((T, k), np.float32),
+              d.out((T, k), np.int32))
+    warm = (d.put_inout(x), d.out((T, Hd), pkg.BF16), d.out((T * k, Hd), pkg.BF16), d.out((T, k), np.float32),
+            d.out((T, k), np.int32))
+    run(*warm, st.h)  # every kernel once outside capture
+    st.synchronize()
+    g = pkg.Graph(st.h)
+    with g:
+        run(*replay, st.h)
+    g.launch()
+    g.launch()
+    st.synchronize()
+    for a, b, what in zip(direct, replay, ("x", "normed", "swiglu", "weights", "experts")):
+        assert np.array_equal(a.get(as_f32=False).view(np.uint8), b.get(as_f32=False).view(np.uint8)), what
+    g.close()
+    st.close()
+
+
 # ---- the argmax key as a public contract for logits producers --------------------------------
 
 def test_argmax_keys_finish_matches_argmax(gpu, orc):
