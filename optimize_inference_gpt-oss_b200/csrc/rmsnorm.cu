@@ -435,6 +435,9 @@ __global__ void embed_rmsnorm_tile(const TT *__restrict__ table, const int *__re
         cp_async16(dst + 16, src + 4);
     }
   cp_async_commit();
+  Vec8 ws; // the gain: asked for now, so that its latency passes under the rows'
+  if (has)
+    ws = load8<kTable>(w, (size_t)chunk * 8);
   cp_async_wait<0>(); // a thread reads back only what it copied itself: no barrier needed
   auto values = [&](int r) {
     Vec8 v;
@@ -473,9 +476,6 @@ __global__ void embed_rmsnorm_tile(const TT *__restrict__ table, const int *__re
       scratch[r][warp] = ss;
   }
   __syncthreads();
-  Vec8 ws;
-  if (has)
-    ws = load8<kTable>(w, (size_t)chunk * 8);
 #pragma unroll
   for (int r = 0; r < R; r++) {
     Acc t = lane < n_warps ? scratch[r][lane] : Acc(0);
