@@ -358,6 +358,30 @@ class Reference(_Lib):
     def __init__(self):
         super().__init__(REF_SO, "ref_")
         assert self.lib.ref_config_size() == C.sizeof(OrcConfig)
+        L = self.lib
+        self.has_group = hasattr(L, "ref_has_group") and bool(L.ref_has_group())
+        if self.has_group:
+            L.ref_moe_group.restype = None
+            L.ref_moe_group.argtypes = [_i32p, C.c_int, C.c_int, _i32p, _i32p, _i32p]
+            L.ref_moe_gather.restype = None
+            L.ref_moe_gather.argtypes = [_f32p, _i32p, C.c_int, C.c_int, _f32p, C.c_int]
+
+    def moe_group(self, topk_e, n_experts):
+        """moe_group_kernel over all experts: (offsets[E+1], row_pair[n_routed], pair_row[n_pairs], -1 where
+        the kernel writes nothing: pairs of finished tokens)."""
+        te = np.ascontiguousarray(topk_e, np.int32).ravel()
+        offsets = np.full(n_experts + 1, -7, np.int32)
+        row_pair = np.full(te.size, -7, np.int32)
+        pair_row = np.full(te.size, -1, np.int32)
+        self.lib.ref_moe_group(te, te.size, n_experts, offsets, row_pair, pair_row)
+        return offsets, row_pair[:offsets[-1]], pair_row
+
+    def moe_gather(self, t, row_pair, k):
+        t = np.ascontiguousarray(t, np.float32)
+        rp = np.ascontiguousarray(row_pair, np.int32)
+        out = np.full((rp.size, t.shape[1]), np.nan, np.float32)
+        self.lib.ref_moe_gather(t, rp, rp.size, k, out, t.shape[1])
+        return out
 
 
 def have_reference() -> bool:

@@ -377,9 +377,11 @@ ORC_API void orc_argmax_rows(int *out, const float *logits, int T, long V, int t
  * rows offsets[e] .. offsets[e+1] belong to local expert e_begin + e, in pair
  * order; row_pair[row] is the pair (token * k + choice) in that row and
  * own_row[pair] its inverse, -1 for a pair whose expert is not local (or -1,
- * a finished token).  The reference has no CPU form of this step (forward()
- * loops over experts instead), so this function restates the GPU kernel's
- * documented result and is NOT pinned against a run of the reference. */
+ * a finished token).  The reference's forward() loops over experts instead, so
+ * the pin is its GPU kernel: moe_group_kernel is plain C per thread, and the
+ * reference library runs its body on host threads; tests/test_oracle_pins.py
+ * holds this function to that run over all experts, and a grouping for part
+ * of the experts to the same run restricted to the range. */
 ORC_API void orc_moe_group(const int *topk_e, int n_pairs, int e_begin, int e_count, int *counts,
                            int *offsets, int *row_pair, int *own_row) {
   int row = 0;
@@ -410,12 +412,11 @@ ORC_API void orc_moe_gather(float *Xg, const float *t, const int *row_pair, int 
  * functions of kernels/fast_attention.hpp:558-600.  qkv rows are already biased
  * and rotated.  Keys: bf16 round-to-nearest-even.  Values: amax = max|v| over
  * the head's 64 numbers, inv = amax > 0 ? 127/amax : 0, code =
- * clamp(rintf(v*inv), +-127), scale = amax/127, all in fp32.  Like the grouping
- * step this restates a GPU kernel that has no CPU form in the reference, so the
- * value arithmetic is NOT pinned against a run of the reference; the layout (the
- * three index functions) and the bf16 rounding rule are: the reference defines
- * them in host-callable form and tests/test_oracle_pins.py holds these against
- * them. */
+ * clamp(rintf(v*inv), +-127), scale = amax/127, all in fp32.  The kernel itself
+ * has no CPU form in the reference, but its three parts do, and
+ * tests/test_oracle_pins.py holds each against them: the layout (the three index
+ * functions) and the bf16 rounding rule are host-callable in the reference's
+ * headers, the value rule is quantize_v of its attention test. */
 static size_t orc_chunk64(int b, int slot, int g, int i, int slots, int kv_dim) {
   return ((size_t)b * slots + (size_t)(slot & ~63)) * kv_dim + (size_t)g * 64 * 64 +
          (size_t)(slot & 63) * 64 + i;

@@ -227,3 +227,65 @@ REF_API long long ref_wave_bookkeeping(int n_rows, const int *prompt_tokens, con
 #else
 REF_API int ref_has_wave(void) { return 0; }
 #endif
+
+// ---- the grouping of (token, choice) pairs by expert, and the row gather --------------------
+// moe_group_kernel and moe_gather_kernel (kernels/moe.hpp:142-171, 175-182) as they stand.
+// Their bodies are plain C per GPU thread -- a loop over the pairs, a __shared__ array, two
+// __syncthreads() -- so a block is run here as host threads: threadIdx is a thread-local, the
+// shared array a function-local static, the barrier a pthread barrier.  One block at a time
+// (a mutex), as the shared array is one per process.
+#ifdef REF_GROUP_PART
+#include <pthread.h>
+
+#include <mutex>
+#include <thread>
+#include <vector>
+namespace ref_group {
+struct Index {
+  int x;
+};
+static thread_local Index threadIdx, blockIdx;
+static Index blockDim;
+static pthread_barrier_t block_barrier;
+static std::mutex one_block_at_a_time;
+#define __global__
+#define __shared__ static
+#define __syncthreads() pthread_barrier_wait(&ref_group::block_barrier)
+#include REF_GROUP_PART
+#undef __syncthreads
+#undef __shared__
+#undef __global__
+} // namespace ref_group
+
+REF_API int ref_has_group(void) { return 1; }
+// One block of E threads, as the reference launches it (E <= 1024).  pair_row keeps the
+// caller's fill for pairs of finished tokens (expert -1), which no thread owns.
+REF_API void ref_moe_group(const int *topk_e, int n_pairs, int E, int *offsets, int *row_pair, int *pair_row) {
+  std::lock_guard<std::mutex> lock(ref_group::one_block_at_a_time);
+  pthread_barrier_init(&ref_group::block_barrier, nullptr, (unsigned)E);
+  ref_group::blockDim.x = E;
+  std::vector<std::thread> block;
+  for (int e = 0; e < E; e++)
+    block.emplace_back([=] {
+      ref_group::threadIdx.x = e;
+      ref_group::blockIdx.x = 0;
+      ref_group::moe_group_kernel(topk_e, n_pairs, E, offsets, row_pair, pair_row);
+    });
+  for (auto &t : block)
+    t.join();
+  pthread_barrier_destroy(&ref_group::block_barrier);
+}
+// One block per row, 256 threads each; no barrier inside, so the threads of a block are a loop.
+REF_API void ref_moe_gather(const float *x, const int *row_pair, int R, int k, float *Xg, int H) {
+  std::lock_guard<std::mutex> lock(ref_group::one_block_at_a_time);
+  ref_group::blockDim.x = 256;
+  for (int row = 0; row < R; row++)
+    for (int t = 0; t < 256; t++) {
+      ref_group::blockIdx.x = row;
+      ref_group::threadIdx.x = t;
+      ref_group::moe_gather_kernel(x, row_pair, k, Xg, H);
+    }
+}
+#else
+REF_API int ref_has_group(void) { return 0; }
+#endif

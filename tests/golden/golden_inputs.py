@@ -198,3 +198,21 @@ def case_wave():
     out.append((prompts, small_ints(501, (1, n), 0, 199000), 1))
     out.append((prompts, np.zeros((0, n), np.int32), 0))
     return out
+
+
+def case_group():
+    """Routings (topk_e [T, k], n_experts) for the grouping step: 32 and 128 experts with four
+    distinct choices per token, finished tokens (all four -1) scattered and in a run, an expert
+    nobody picks, an expert everybody picks, one token, and a batch with every token finished."""
+    out = []
+    for j, (T, E, k) in enumerate(((257, 32, 4), (300, 128, 4), (1, 32, 4), (64, 32, 2))):
+        order = np.argsort(hashed(600 + j, T * E).reshape(T, E), axis=1, kind="stable").astype(np.int32)
+        e = np.ascontiguousarray(order[:, :k])
+        if T > 1:
+            e[e == 5] = 6 + (np.nonzero(e == 5)[0] % 3 == 0) * 20   # expert 5 is never picked ...
+            e[:, 0] = np.where((e[:, 1:] == 7).any(axis=1), e[:, 0], 7)  # ... and 7 by everybody
+            e[::9] = -1
+            e[40:52] = -1
+        out.append((e, E))
+    out.append((np.full((16, 4), -1, np.int32), 32))
+    return out

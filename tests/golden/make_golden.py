@@ -19,6 +19,9 @@ stores the expected outputs:
   * the wave bookkeeping (output rows, counts, finished mask, tokens fed and mask seen per
     step): the REFERENCE's statements of gpu_run_wave (engine/gpu_engine.hpp) around recorded
     picks;
+  * the grouping of pairs by expert (offsets, row of each pair, pair of each row) and the
+    gathered rows: the REFERENCE's moe_group_kernel / moe_gather_kernel (kernels/moe.hpp), their
+    bodies run on host threads;
   * SwiGLU rows and combine rows: produced by the restated oracle (the reference has no
     callable form of those loops); they are regression vectors for the oracle, whose
     agreement with forward() is checked separately.
@@ -84,6 +87,12 @@ def main():
         rows, total, ran, done, fed, mask = ref.wave_bookkeeping(prompts, picked, steps)
         out[f"wave{j}_rows"], out[f"wave{j}_counts"] = rows, np.array([total, ran], np.int64)
         out[f"wave{j}_done"], out[f"wave{j}_fed"], out[f"wave{j}_mask"] = done, fed, mask.astype(np.int8)
+
+    for j, (e, E) in enumerate(gi.case_group()):
+        off, rp, pr = ref.moe_group(e, E)
+        out[f"group{j}_offsets"], out[f"group{j}_row_pair"], out[f"group{j}_pair_row"] = off, rp, pr
+        if j == 0:
+            out["group0_rows"] = ref.moe_gather(gi.uniform(610, (e.shape[0], 64)), rp, e.shape[1])
 
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden.npz")
     np.savez_compressed(path, **out)

@@ -281,6 +281,66 @@ def test_ref_wave_bookkeeping(orc, ref):
         _assert_same_wave(orc.wave_bookkeeping(prompts, picked, steps), ref.wave_bookkeeping(prompts, picked, steps))
 
 
+def _group_of_a_range(full, e, e_begin, e_count):
+    """What grouping for experts e_begin .. e_begin+e_count-1 alone must give, derived from a
+    grouping over all experts: that range's rows, renumbered from zero, and -1 for every pair
+    whose expert lies outside it (kernels/moe_ep.hpp:44-49, :118-127)."""
+    off, rp, pr = full
+    lo, hi = off[e_begin], off[e_begin + e_count]
+    inside = (e.ravel() >= e_begin) & (e.ravel() < e_begin + e_count)
+    return off[e_begin:e_begin + e_count + 1] - lo, rp[lo:hi], np.where(inside, pr - lo, -1).astype(np.int32)
+
+
+def test_golden_group_and_gather(orc, golden):
+    for j, (e, E) in enumerate(gi.case_group()):
+        counts, off, rp, own = orc.moe_group(e, 0, E)
+        assert np.array_equal(off, golden[f"group{j}_offsets"]), j
+        assert np.array_equal(rp, golden[f"group{j}_row_pair"]), j
+        assert np.array_equal(own, golden[f"group{j}_pair_row"]), j
+        assert np.array_equal(counts, np.diff(off)), j
+        full = (golden[f"group{j}_offsets"], golden[f"group{j}_row_pair"], golden[f"group{j}_pair_row"])
+        for e_begin, e_count in ((0, E // 2), (E // 2, E // 2), (5, 3), (E - 1, 1)):
+            _, off2, rp2, own2 = orc.moe_group(e, e_begin, e_count)
+            w_off, w_rp, w_own = _group_of_a_range(full, e, e_begin, e_count)
+            assert np.array_equal(off2, w_off) and np.array_equal(rp2, w_rp) and np.array_equal(own2, w_own), (j, e_begin)
+    e, E = gi.case_group()[0]
+    rows = orc.moe_gather(gi.uniform(610, (e.shape[0], 64)), golden["group0_row_pair"], e.shape[1])
+    assert_bit_equal(rows, golden["group0_rows"], "gathered rows")
+
+
+def test_ref_group_and_gather(orc, ref):
+    """The grouping step against the reference's moe_group_kernel and the row gather against its
+    moe_gather_kernel (kernels/moe.hpp:142-171, 175-182), whose bodies the reference library
+    runs on host threads (one per GPU thread, a barrier for __syncthreads): offsets, the pair in
+    each row and the row of each pair, bit for bit; pairs of finished tokens keep the caller's
+    -1.  A grouping for part of the experts is held to the same run, restricted to that range."""
+    if not ref.has_group:
+        pytest.skip("reference library built without kernels/moe.hpp")
+    r = np.random.default_rng(29)
+    cases = list(gi.case_group())
+    for trial in range(40):
+        E, k = ((32, 4), (128, 4), (16, 8), (1024, 4), (7, 2))[trial % 5]
+        T = int(r.integers(1, 400)) if E < 1024 else 33
+        e = np.stack([r.permutation(E)[:k] for _ in range(T)]).astype(np.int32)
+        if trial % 2:
+            e[r.random(T) < 0.2] = -1
+        if trial % 7 == 3:
+            e[:] = e[0]   # every token picks the same experts
+        cases.append((e, E))
+    for e, E in cases:
+        full = ref.moe_group(e, E)
+        counts, off, rp, own = orc.moe_group(e, 0, E)
+        assert np.array_equal(off, full[0]) and np.array_equal(rp, full[1]) and np.array_equal(own, full[2])
+        if E >= 8:
+            for e_begin, e_count in ((0, E // 2), (E // 2, E - E // 2), (3, 4)):
+                got = orc.moe_group(e, e_begin, e_count)[1:]
+                for g, w in zip(got, _group_of_a_range(full, e, e_begin, e_count)):
+                    assert np.array_equal(g, w)
+        H = 24
+        t = r.standard_normal((e.shape[0], H)).astype(np.float32)
+        assert_bit_equal(orc.moe_gather(t, full[1], e.shape[1]), ref.moe_gather(t, full[1], e.shape[1]), "rows")
+
+
 @pytest.mark.parametrize("seed", [1, 2, 3])
 def test_ref_forward_pins_the_inline_loops(orc, ref, seed):
     """forward() of a tiny model: bias adds, SwiGLU (with clamping hit by the large
