@@ -28,25 +28,48 @@ __device__ static const unsigned long long kExp2Tab32[32] = {
 //   2^(r/N) ~ 1 + c2 r + (c1 + c0 r) r^2   (cubic, coefficients pre-divided by N^j);
 // all in double, rounded to float once.  The reference's GPU engine relies on
 // the same restatement (kernels/exact_math.hpp:8-52) for its bit-exact path.
-__device__ __forceinline__ float glibc_expf(float x) {
+//
+// The inputs with a result of their own: |x| >= 88, infinities, NaN.
+__device__ __forceinline__ bool glibc_expf_special(float x, float *result) {
+  const uint32_t bits = __float_as_uint(x);
+  const uint32_t top = (bits >> 20) & 0x7ffu;
+  if (top < (0x42b00000u >> 20))
+    return false;
+  if (bits == 0xff800000u) {
+    *result = 0.0f; // exp(-inf)
+    return true;
+  }
+  if (top >= (0x7f800000u >> 20)) {
+    *result = x + x; // +inf or NaN
+    return true;
+  }
+  if (x > 0x1.62e42ep6f) {
+    *result = __int_as_float(0x7f800000); // overflow
+    return true;
+  }
+  if (x < -0x1.9fe368p6f) {
+    *result = 0.0f; // underflow
+    return true;
+  }
+  return false;
+}
+
+// entry_of(i) returns table entry i (0..31).  With kSpecialsLast it is called exactly once by
+// every thread, before any branch on x, so it may be a warp shuffle of entries that the lanes
+// hold; the special inputs then replace the polynomial's result afterwards.  Otherwise they
+// leave early, as in the C library.
+template <bool kSpecialsLast, class Lookup>
+__device__ __forceinline__ float glibc_expf_with(float x, Lookup entry_of) {
   const double kScale = 0x1.71547652b82fep+0 * 32.0; // N / ln 2
   const double kRound = 0x1.8p+52;                   // adding it rounds to an integer
   const double c0 = 0x1.c6af84b912394p-5 / 32768.0;
   const double c1 = 0x1.ebfce50fac4f3p-3 / 1024.0;
   const double c2 = 0x1.62e42ff0c52d6p-1 / 32.0;
 
-  const uint32_t bits = __float_as_uint(x);
-  const uint32_t top = (bits >> 20) & 0x7ffu;
-  if (top >= (0x42b00000u >> 20)) { // |x| >= 88, infinities, NaN
-    if (bits == 0xff800000u)
-      return 0.0f; // exp(-inf)
-    if (top >= (0x7f800000u >> 20))
-      return x + x; // +inf or NaN
-    if (x > 0x1.62e42ep6f)
-      return __int_as_float(0x7f800000); // overflow
-    if (x < -0x1.9fe368p6f)
-      return 0.0f; // underflow
-  }
+  float special;
+  if constexpr (!kSpecialsLast)
+    if (glibc_expf_special(x, &special))
+      return special;
   const double z = __dmul_rn(kScale, (double)x);
   double kd = __dadd_rn(z, kRound);
   // k sits in the low bits of kd's mantissa.  Table entry + (k << 47) only ever changes the
@@ -55,12 +78,20 @@ __device__ __forceinline__ float glibc_expf(float x) {
   const uint32_t k_lo = (uint32_t)__double2loint(kd);
   kd = __dsub_rn(kd, kRound);
   const double r = __dsub_rn(z, kd);
-  const unsigned long long entry = kExp2Tab32[k_lo & 31u];
+  const unsigned long long entry = entry_of(k_lo & 31u);
   const double s = __hiloint2double((int)((uint32_t)(entry >> 32) + (k_lo << 15)), (int)(uint32_t)entry);
   const double hi = __fma_rn(c0, r, c1);
   double y = __fma_rn(c2, r, 1.0);
   y = __fma_rn(hi, __dmul_rn(r, r), y);
-  return (float)__dmul_rn(y, s);
+  const float out = (float)__dmul_rn(y, s);
+  if constexpr (kSpecialsLast)
+    if (glibc_expf_special(x, &special))
+      return special;
+  return out;
+}
+
+__device__ __forceinline__ float glibc_expf(float x) {
+  return glibc_expf_with<false>(x, [](uint32_t i) { return kExp2Tab32[i]; });
 }
 
 } // namespace gptoss

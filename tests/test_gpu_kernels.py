@@ -264,7 +264,8 @@ def _router_scores(r, T, E):
 
 
 @pytest.mark.parametrize("T,E,k", [(512, 32, 4), (512, 128, 4), (512, 200, 4), (7, 32, 2), (7, 128, 2),
-                                   (33, 16, 8), (65, 256, 8), (1, 32, 4), (4096, 32, 4)])
+                                   (33, 16, 8), (65, 256, 8), (1, 32, 4), (4096, 32, 4), (13, 32, 4),
+                                   (13, 128, 4), (1, 128, 4), (4099, 128, 4), (64, 64, 4)])
 @pytest.mark.parametrize("dt", ["f32", "bf16"])
 def test_router_topk(gpu, orc, T, E, k, dt):
     pkg, d = gpu, Dev(gpu)
@@ -285,6 +286,37 @@ def test_router_topk(gpu, orc, T, E, k, dt):
     assert (ge[~live] == -1).all() and (gw[~live] == 0).all()
     assert np.array_equal(ge[live], slot[want_e[live]])
     assert n_bit_diff(gw[live], want_w[live]) == 0
+
+
+@pytest.mark.parametrize("E", [32, 128])
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+def test_router_top4_kernel_and_general_kernel_agree(gpu, orc, E, dt):
+    """The model family's shapes (k = 4, 32 or 128 experts) run a kernel of their own; scores that
+    start off the lane's vector boundary fall to the general one.  Both must give the oracle's
+    bits, on rows with minus infinity among the scores, scores differing in the last bit, a row
+    of one repeated value, and denormals."""
+    pkg, d = gpu, Dev(gpu)
+    dtc = pkg.F32 if dt == "f32" else pkg.BF16
+    T, k = 333, 4
+    r = rng_of("router-top4", E, dt)
+    s = _router_scores(r, T, E)
+    s[1, r.permutation(E)[:E - 5]] = -np.inf
+    s[2] = 0.75
+    s[4] = np.float32(1.0) + np.arange(E, dtype=np.float32)[::-1] * np.float32(2.0 ** -23 if dt == "f32" else 2.0 ** -7)
+    s[6] = (r.integers(-40, 40, E) * 1e-40).astype(np.float32)
+    s[8] = -60.0                      # differences from the top score beyond where expf underflows
+    s[8, 1], s[8, 3], s[8, 5] = 40.0, 88.0, -5.0
+    s = widen(pkg, s, dtc).reshape(T, E)
+    want_w, want_e = orc.router_rows(s, k)
+    size = 4 if dt == "f32" else 2
+    bits = s if dt == "f32" else pkg.to_bf16_bits(s)
+    shifted = np.concatenate([np.zeros(1, bits.dtype), bits.ravel()])    # scores start one element in
+    base = d.put(shifted)
+    for ptr in (d.put(bits).ptr, base.ptr + size):
+        wb, eb = d.out((T, k), pkg.F32), d.out((T, k), np.int32)
+        pkg.router_topk(T, ptr, dtc, E, k, wb, eb)
+        assert np.array_equal(eb.get(), want_e)
+        assert n_bit_diff(wb.get(), want_w) == 0
 
 
 # ---- a5: clamped SwiGLU -----------------------------------------------------------------
