@@ -98,41 +98,55 @@ __device__ __forceinline__ int decode_pick(unsigned long long key, const LT *row
 // the block of the last slice.
 template <typename LT>
 __global__ void __launch_bounds__(kThreads)
-    argmax_slices(const LT *__restrict__ logits, long V, long row_stride, long pieces_per_row,
-                  long pieces_per_slice, int splits, unsigned long long *keys, int *__restrict__ out) {
+    argmax_slices(const LT *__restrict__ logits, long V, long row_stride, unsigned pieces_per_row,
+                  unsigned pieces_per_slice, int splits, unsigned long long *keys, int *__restrict__ out) {
   pdl_prologue();
-  constexpr int kPer = 16 / sizeof(LT); // values per 16-byte piece
+  constexpr unsigned kPer = 16 / sizeof(LT); // values per 16-byte piece
   __shared__ unsigned long long scratch[kThreads / 32];
   const int row = blockIdx.x / splits, slice = blockIdx.x - row * splits;
   const LT *r = logits + (size_t)row * row_stride;
-  const long p0 = (long)slice * pieces_per_slice;
-  long p1 = p0 + pieces_per_slice;
-  if (p1 > pieces_per_row)
-    p1 = pieces_per_row;
+  // Pieces are counted in 32 bits (a row has fewer than 2^29 of them) and the pointer to the
+  // thread's next piece is carried along, so an iteration's index work is one add.
+  const unsigned p0 = (unsigned)slice * pieces_per_slice;
+  const unsigned p1 = min(p0 + pieces_per_slice, pieces_per_row);
 
   float best = __int_as_float(0xff800000); // -inf: only values above it are recorded
   long best_idx = -1;
-  for (long p = p0 + threadIdx.x; p < p1; p += (long)kThreads * kUnroll) {
+  unsigned p = p0 + threadIdx.x;
+  const uint4 *at = reinterpret_cast<const uint4 *>(r) + p; // dereferenced only where p < p1
+  // whole iterations: kUnroll pieces in flight per thread, none past the slice
+  for (; p + (kUnroll - 1) * kThreads < p1; p += kThreads * kUnroll, at += kThreads * kUnroll) {
     uint4 q[kUnroll];
 #pragma unroll
-    for (int u = 0; u < kUnroll; u++) {
-      const long pp = p + (long)u * kThreads;
-      // past the slice: re-read its first piece; the strict '>' below makes a repeat harmless
-      q[u] = ld_stream(r + (pp < p1 ? pp : p0) * kPer);
-    }
+    for (int u = 0; u < kUnroll; u++)
+      q[u] = ld_stream(at + u * kThreads);
 #pragma unroll
     for (int u = 0; u < kUnroll; u++) {
       const float m = piece_max<LT>(q[u]);
       if (m > best) { // rare after the first few pieces
-        const long pp = p + (long)u * kThreads;
         best = m;
-        best_idx = (pp < p1 ? pp : p0) * kPer + piece_first<LT>(q[u], m);
+        best_idx = (long)(p + u * kThreads) * kPer + piece_first<LT>(q[u], m);
+      }
+    }
+  }
+  // the slice's last, partly filled iteration
+  if (p < p1) {
+    uint4 q[kUnroll - 1];
+#pragma unroll
+    for (int u = 0; u < kUnroll - 1; u++) // past the slice: the thread's first piece again; the strict '>' makes a repeat harmless
+      q[u] = ld_stream(at + (p + u * kThreads < p1 ? u * kThreads : 0));
+#pragma unroll
+    for (int u = 0; u < kUnroll - 1; u++) {
+      const float m = piece_max<LT>(q[u]);
+      if (m > best) {
+        best = m;
+        best_idx = (long)(p + u * kThreads < p1 ? p + u * kThreads : p) * kPer + piece_first<LT>(q[u], m);
       }
     }
   }
   // scalar tail of the row, by the last slice's block
   if (slice == splits - 1)
-    for (long i = pieces_per_row * kPer + threadIdx.x; i < V; i += kThreads) {
+    for (long i = (long)pieces_per_row * kPer + threadIdx.x; i < V; i += kThreads) {
       const float v = load1(r + i);
       if (v > best) {
         best = v;
@@ -217,7 +231,7 @@ int launch(cudaStream_t s, int T, const void *logits, long V, long row_stride,
     return GPTOSS_ERR_UNSUPPORTED;
   unsigned long long *merge = splits > 1 ? keys : nullptr;
   launch_kernel(argmax_slices<LT>, dim3((unsigned)((long)T * splits)), dim3(kThreads), 0, s, lp, V, row_stride,
-                pieces, per_slice, splits, merge, out);
+                (unsigned)pieces, (unsigned)per_slice, splits, merge, out);
   int st = launch_status();
   if (st != GPTOSS_OK || !merge)
     return st;
