@@ -366,6 +366,23 @@ class Reference(_Lib):
             L.ref_moe_gather.restype = None
             L.ref_moe_gather.argtypes = [_f32p, _i32p, C.c_int, C.c_int, _f32p, C.c_int]
 
+        self.has_group_ep = hasattr(L, "ref_has_group_ep") and bool(L.ref_has_group_ep())
+        if self.has_group_ep:
+            L.ref_moe_group_ep.restype = None
+            L.ref_moe_group_ep.argtypes = [_i32p, C.c_int, C.c_int, C.c_int, _i32p, _i32p, _i32p, _i32p]
+
+    def moe_group_ep(self, topk_e, e_begin, e_count):
+        """moe_count_ep_kernel + moe_place_ep_kernel for experts e_begin .. e_begin + e_count - 1 with no
+        partner: (counts[e_count], offsets[e_count + 1], row_pair[rows], own_row[n_pairs]); own_row starts
+        from a fill that the kernels must overwrite for every pair."""
+        te = np.ascontiguousarray(topk_e, np.int32).ravel()
+        counts = np.full(e_count, -7, np.int32)
+        offsets = np.full(e_count + 1, -7, np.int32)
+        row_pair = np.full(max(te.size, 1), -7, np.int32)
+        own_row = np.full(max(te.size, 1), -7, np.int32)
+        self.lib.ref_moe_group_ep(te, te.size, e_begin, e_count, counts, offsets, row_pair, own_row)
+        return counts, offsets, row_pair[:offsets[-1]], own_row[:te.size]
+
     def moe_group(self, topk_e, n_experts):
         """moe_group_kernel over all experts: (offsets[E+1], row_pair[n_routed], pair_row[n_pairs], -1 where
         the kernel writes nothing: pairs of finished tokens)."""

@@ -378,10 +378,12 @@ ORC_API void orc_argmax_rows(int *out, const float *logits, int T, long V, int t
  * order; row_pair[row] is the pair (token * k + choice) in that row and
  * own_row[pair] its inverse, -1 for a pair whose expert is not local (or -1,
  * a finished token).  The reference's forward() loops over experts instead, so
- * the pin is its GPU kernel: moe_group_kernel is plain C per thread, and the
- * reference library runs its body on host threads; tests/test_oracle_pins.py
- * holds this function to that run over all experts, and a grouping for part
- * of the experts to the same run restricted to the range. */
+ * the pins are its GPU kernels, run on host threads by the reference library
+ * (one per GPU thread, a barrier for __syncthreads, 64 threads to a wavefront
+ * for ballot and shuffle): moe_group_kernel over all experts, and
+ * moe_count_ep_kernel + moe_place_ep_kernel (kernels/moe_ep.hpp:55-127) with
+ * no partner for part of them; tests/test_oracle_pins.py holds this function
+ * to both. */
 ORC_API void orc_moe_group(const int *topk_e, int n_pairs, int e_begin, int e_count, int *counts,
                            int *offsets, int *row_pair, int *own_row) {
   int row = 0;

@@ -237,6 +237,7 @@ REF_API int ref_has_wave(void) { return 0; }
 #ifdef REF_GROUP_PART
 #include <pthread.h>
 
+#include <functional>
 #include <mutex>
 #include <thread>
 #include <vector>
@@ -248,13 +249,46 @@ static thread_local Index threadIdx, blockIdx;
 static Index blockDim;
 static pthread_barrier_t block_barrier;
 static std::mutex one_block_at_a_time;
+// A 64-wide wavefront's collectives, for the kernels that group for part of the experts
+// (kernels/moe_ep.hpp): every lane of the wave calls them together, as on the GPU.
+static pthread_barrier_t wave_barrier[16];
+static long long wave_slot[16][64];
+static inline long long wave_exchange(long long mine, int from_lane_offset) {
+  const int wave = threadIdx.x / 64, lane = threadIdx.x % 64;
+  wave_slot[wave][lane] = mine;
+  pthread_barrier_wait(&wave_barrier[wave]);
+  const long long got = lane + from_lane_offset < 64 ? wave_slot[wave][lane + from_lane_offset] : mine;
+  pthread_barrier_wait(&wave_barrier[wave]);
+  return got;
+}
+static inline int __shfl_down(int v, int offset) { return (int)wave_exchange(v, offset); }
+static inline unsigned long long __ballot(int pred) {
+  const int wave = threadIdx.x / 64, lane = threadIdx.x % 64;
+  wave_slot[wave][lane] = pred != 0;
+  pthread_barrier_wait(&wave_barrier[wave]);
+  unsigned long long mask = 0;
+  for (int i = 0; i < 64; i++)
+    mask |= (unsigned long long)(wave_slot[wave][i] != 0) << i;
+  pthread_barrier_wait(&wave_barrier[wave]);
+  (void)lane;
+  return mask;
+}
+#define __popcll __builtin_popcountll
+#define __launch_bounds__(...)
+#define __device__
 #define __global__
 #define __shared__ static
 #define __syncthreads() pthread_barrier_wait(&ref_group::block_barrier)
 #include REF_GROUP_PART
+#ifdef REF_GROUP_EP_PART
+#include REF_GROUP_EP_PART
+#endif
 #undef __syncthreads
 #undef __shared__
 #undef __global__
+#undef __device__
+#undef __launch_bounds__
+#undef __popcll
 } // namespace ref_group
 
 REF_API int ref_has_group(void) { return 1; }
@@ -286,6 +320,47 @@ REF_API void ref_moe_gather(const float *x, const int *row_pair, int R, int k, f
       ref_group::moe_gather_kernel(x, row_pair, k, Xg, H);
     }
 }
+
+#ifdef REF_GROUP_EP_PART
+REF_API int ref_has_group_ep(void) { return 1; }
+// moe_count_ep_kernel then moe_place_ep_kernel (kernels/moe_ep.hpp:55-127), the pair that
+// moe_group_ep launches for shapes its fused kernel does not take (:250-254), with no partner
+// (n_peer = 0): e_count blocks of MOE_GROUP_THREADS threads each, one block at a time, a host
+// thread per GPU thread, four 64-wide waves per block.
+static void run_block_ep(int block, const std::function<void()> &kernel) {
+  pthread_barrier_init(&ref_group::block_barrier, nullptr, MOE_GROUP_THREADS);
+  for (int w = 0; w < MOE_GROUP_THREADS / 64; w++)
+    pthread_barrier_init(&ref_group::wave_barrier[w], nullptr, 64);
+  ref_group::blockDim.x = MOE_GROUP_THREADS;
+  std::vector<std::thread> threads;
+  for (int t = 0; t < MOE_GROUP_THREADS; t++)
+    threads.emplace_back([=, &kernel] {
+      ref_group::threadIdx.x = t;
+      ref_group::blockIdx.x = block;
+      kernel();
+    });
+  for (auto &t : threads)
+    t.join();
+  for (int w = 0; w < MOE_GROUP_THREADS / 64; w++)
+    pthread_barrier_destroy(&ref_group::wave_barrier[w]);
+  pthread_barrier_destroy(&ref_group::block_barrier);
+}
+REF_API void ref_moe_group_ep(const int *topk_own, int n_own, int e_begin, int e_count, int *counts, int *offsets,
+                              int *row_pair, int *own_row) {
+  static_assert(MOE_GROUP_THREADS % 64 == 0 && MOE_GROUP_THREADS / 64 <= 16, "waves per block");
+  std::lock_guard<std::mutex> lock(ref_group::one_block_at_a_time);
+  for (int e = 0; e < e_count; e++)
+    run_block_ep(e, [=] { ref_group::moe_count_ep_kernel(topk_own, n_own, nullptr, 0, e_begin, counts); });
+  for (int e = 0; e < e_count; e++)
+    run_block_ep(e, [=] {
+      ref_group::moe_place_ep_kernel(topk_own, n_own, nullptr, 0, n_own, e_begin, e_count, counts, offsets, row_pair,
+                                     own_row, nullptr);
+    });
+}
+#else
+REF_API int ref_has_group_ep(void) { return 0; }
+#endif
 #else
 REF_API int ref_has_group(void) { return 0; }
+REF_API int ref_has_group_ep(void) { return 0; }
 #endif

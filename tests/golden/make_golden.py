@@ -21,7 +21,8 @@ stores the expected outputs:
     picks;
   * the grouping of pairs by expert (offsets, row of each pair, pair of each row) and the
     gathered rows: the REFERENCE's moe_group_kernel / moe_gather_kernel (kernels/moe.hpp), their
-    bodies run on host threads;
+    bodies run on host threads; for part of the experts its moe_count_ep_kernel +
+    moe_place_ep_kernel (kernels/moe_ep.hpp) the same way, 64 host threads to a wavefront;
   * SwiGLU rows and combine rows: produced by the restated oracle (the reference has no
     callable form of those loops); they are regression vectors for the oracle, whose
     agreement with forward() is checked separately.
@@ -93,6 +94,11 @@ def main():
         out[f"group{j}_offsets"], out[f"group{j}_row_pair"], out[f"group{j}_pair_row"] = off, rp, pr
         if j == 0:
             out["group0_rows"] = ref.moe_gather(gi.uniform(610, (e.shape[0], 64)), rp, e.shape[1])
+        if j < 2:   # for part of the experts: moe_count_ep_kernel + moe_place_ep_kernel, no partner
+            for i, (e_begin, e_count) in enumerate(gi.group_ranges(E)):
+                c, o, rp2, own = ref.moe_group_ep(e, e_begin, e_count)
+                out[f"group{j}_part{i}_counts"], out[f"group{j}_part{i}_offsets"] = c, o
+                out[f"group{j}_part{i}_row_pair"], out[f"group{j}_part{i}_own_row"] = rp2, own
 
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden.npz")
     np.savez_compressed(path, **out)

@@ -299,10 +299,13 @@ def test_golden_group_and_gather(orc, golden):
         assert np.array_equal(own, golden[f"group{j}_pair_row"]), j
         assert np.array_equal(counts, np.diff(off)), j
         full = (golden[f"group{j}_offsets"], golden[f"group{j}_row_pair"], golden[f"group{j}_pair_row"])
-        for e_begin, e_count in ((0, E // 2), (E // 2, E // 2), (5, 3), (E - 1, 1)):
-            _, off2, rp2, own2 = orc.moe_group(e, e_begin, e_count)
+        for i, (e_begin, e_count) in enumerate(gi.group_ranges(E)):
+            c2, off2, rp2, own2 = orc.moe_group(e, e_begin, e_count)
             w_off, w_rp, w_own = _group_of_a_range(full, e, e_begin, e_count)
             assert np.array_equal(off2, w_off) and np.array_equal(rp2, w_rp) and np.array_equal(own2, w_own), (j, e_begin)
+            if j < 2:   # the reference's own kernels for part of the experts
+                for got, name in ((c2, "counts"), (off2, "offsets"), (rp2, "row_pair"), (own2, "own_row")):
+                    assert np.array_equal(got, golden[f"group{j}_part{i}_{name}"]), (j, i, name)
     e, E = gi.case_group()[0]
     rows = orc.moe_gather(gi.uniform(610, (e.shape[0], 64)), golden["group0_row_pair"], e.shape[1])
     assert_bit_equal(rows, golden["group0_rows"], "gathered rows")
@@ -339,6 +342,28 @@ def test_ref_group_and_gather(orc, ref):
         H = 24
         t = r.standard_normal((e.shape[0], H)).astype(np.float32)
         assert_bit_equal(orc.moe_gather(t, full[1], e.shape[1]), ref.moe_gather(t, full[1], e.shape[1]), "rows")
+
+
+def test_ref_group_for_part_of_the_experts(orc, ref):
+    """Grouping for experts e_begin .. e_begin + e_count - 1 against the reference's
+    moe_count_ep_kernel + moe_place_ep_kernel (kernels/moe_ep.hpp:55-127; the pair moe_group_ep
+    launches at :250-254) with no partner, run on host threads with a 64-wide wavefront's ballot
+    and shuffle emulated: counts, offsets, the pair in each row, and the row of each pair with -1
+    for every pair whose expert lies outside the range or whose token has finished."""
+    if not ref.has_group_ep:
+        pytest.skip("reference library built without kernels/moe_ep.hpp")
+    r = np.random.default_rng(31)
+    cases = [(gi.case_group()[0][0], 32, (0, 16)), (gi.case_group()[0][0], 32, (16, 16)),
+             (gi.case_group()[1][0][:120], 128, (96, 32)), (gi.case_group()[4][0], 32, (8, 8))]
+    for E, k, T, rng in ((32, 4, 333, (5, 3)), (32, 4, 1, (0, 32)), (16, 8, 70, (8, 8)), (128, 4, 90, (31, 33))):
+        e = np.stack([r.permutation(E)[:k] for _ in range(T)]).astype(np.int32)
+        e[r.random(T) < 0.15] = -1
+        cases.append((e, E, rng))
+    for e, E, (e_begin, e_count) in cases:
+        want = ref.moe_group_ep(e, e_begin, e_count)
+        got = orc.moe_group(e, e_begin, e_count)
+        for g, w, name in zip(got, want, ("counts", "offsets", "row_pair", "own_row")):
+            assert np.array_equal(g, w), (name, E, e_begin, e_count)
 
 
 @pytest.mark.parametrize("seed", [1, 2, 3])
