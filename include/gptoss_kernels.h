@@ -199,7 +199,10 @@ GPTOSS_API int gptoss_qkv_bias_rope(gptoss_stream_t stream, int T, const void *q
  * rows with done[t] != 0 get expert -1 and weight 0 for all k choices.
  * slot_of (may be NULL): topk_e receives slot_of[e] instead of e.
  * E <= GPTOSS_MAX_EXPERTS, 1 <= k <= min(E, GPTOSS_MAX_TOPK).  A NaN logit is
- * never selected ahead of a number.
+ * never selected ahead of a number.  k = 4 with E = 32 or 128 (the model
+ * family's shapes) runs a kernel of its own with a shorter dependent chain;
+ * every other shape, and scores that do not start on a lane's vector boundary
+ * (E / 32 elements), the general one: same results.
  */
 GPTOSS_API int gptoss_router_topk(gptoss_stream_t stream, int T, const void *logits,
                                   gptoss_dtype_t logits_dtype, int E, int k, float *topk_w,
