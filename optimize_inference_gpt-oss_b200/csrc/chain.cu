@@ -64,66 +64,85 @@ struct WaveState {
   int active;          // rows not finished
   int steps_run;       // positions completed while any row was active
   int width;           // row pitch of `generated` (steps + 2)
-  int pad;
+  unsigned arrived;    // blocks of the running bookkeeping launch that are through; 0 between launches
   long long generated; // the reference's count over the rows that finished on an end token
   const int *prompts;  // device: the wave's prompts back to back
   int *out_rows;       // device: [n, width] generated tokens
   // (the two buffers are named here, not in the kernel's arguments, so that a captured
   // graph stays valid when a later wave needs larger ones)
+  int finished_now;    // rows that finished in the running launch, until its last block takes them off `active`
+  int pad;
 };
 
 namespace {
 
+constexpr int kWaveThreads = 256;
+
 // The per-step bookkeeping of gpu_run_wave (gpu_engine.hpp:800-826) as a kernel that
 // runs behind the step's argmax: the row takes its next prompt token while it has one
 // and the picked token afterwards, records generated tokens, and finishes on an end
-// token.  One block, so that "was anybody still active when this step began" is a
-// single read followed by a barrier; once nobody is, the kernel leaves everything as
-// it is, and the steps the host had already queued change nothing.
-__global__ void __launch_bounds__(1024)
+// token.  One thread per row, so the four dependent reads of a row (position, offsets,
+// token, output slot) are paid once for the batch and not once per 1024 rows.  "Was
+// anybody still active when this step began" must be the same answer in every block:
+// `active` is only written by the launch's last block (the one that finds every other
+// block through), after all of them have read it.  Once nobody is active the kernel
+// leaves everything as it is, and the steps the host had already queued change nothing.
+__global__ void __launch_bounds__(kWaveThreads)
     wave_advance(int n, const int *__restrict__ offsets, const int *__restrict__ next,
                  int *__restrict__ tokens, int *__restrict__ pos, int *__restrict__ done, WaveState *state) {
-  __shared__ int s_active, s_finished;
+  pdl_prologue();
+  __shared__ int s_active, s_finished, s_width;
   __shared__ long long s_count;
+  __shared__ const int *s_prompts;
+  __shared__ int *s_out_rows;
   if (threadIdx.x == 0) {
-    s_active = state->active;
+    s_active = *reinterpret_cast<volatile int *>(&state->active);
+    s_width = state->width;
+    s_prompts = state->prompts;
+    s_out_rows = state->out_rows;
     s_finished = 0;
     s_count = 0;
   }
   __syncthreads();
-  if (s_active <= 0)
-    return;
-  const int width = state->width;
-  const int *__restrict__ prompts = state->prompts;
-  int *__restrict__ generated = state->out_rows;
-  for (int b = threadIdx.x; b < n; b += blockDim.x) {
+  const int b = blockIdx.x * kWaveThreads + threadIdx.x;
+  if (s_active > 0 && b < n) {
     const int p = pos[b] + 1; // every row sits at the same position
     pos[b] = p;
-    if (done[b])
-      continue;
-    const int first = offsets[b], np = offsets[b + 1] - first;
-    int *out = generated + (size_t)b * width;
-    int token;
-    if (p < np) {
-      token = prompts[first + p];
-    } else {
-      token = next[b];
-      out[p - np] = token;
+    if (!done[b]) {
+      const int first = offsets[b], np = offsets[b + 1] - first;
+      int *out = s_out_rows + (size_t)b * s_width;
+      int token;
+      if (p < np) {
+        token = s_prompts[first + p];
+      } else {
+        token = next[b];
+        out[p - np] = token;
+      }
+      if (token == 199999 || token == 200002) {
+        done[b] = 1;
+        if (p - np + 1 >= 0)
+          out[p - np + 1] = -1;
+        atomicAdd(&s_finished, 1);
+        atomicAdd(reinterpret_cast<unsigned long long *>(&s_count), (unsigned long long)(long long)(p - np + 1));
+      }
+      tokens[b] = token;
     }
-    if (token == 199999 || token == 200002) {
-      done[b] = 1;
-      if (p - np + 1 >= 0)
-        out[p - np + 1] = -1;
-      atomicAdd(&s_finished, 1);
-      atomicAdd(reinterpret_cast<unsigned long long *>(&s_count), (unsigned long long)(long long)(p - np + 1));
-    }
-    tokens[b] = token;
   }
   __syncthreads();
   if (threadIdx.x == 0) {
-    state->active = s_active - s_finished;
-    state->steps_run += 1;
-    state->generated += s_count;
+    if (s_finished)
+      atomicAdd(&state->finished_now, s_finished);
+    if (s_count)
+      atomicAdd(reinterpret_cast<unsigned long long *>(&state->generated), (unsigned long long)s_count);
+    __threadfence();
+    if (atomicAdd(&state->arrived, 1u) == gridDim.x - 1) { // every other block is through
+      __threadfence();
+      if (s_active > 0) {
+        state->active = s_active - atomicExch(&state->finished_now, 0);
+        state->steps_run += 1;
+      }
+      state->arrived = 0u;
+    }
   }
 }
 
@@ -558,9 +577,11 @@ static int capture_step(gptoss_chain *c, int T, int only, cudaGraphExec_t *exec_
   if (with_io && issued == GPTOSS_OK)
     issued = cuda_status(cudaMemcpyAsync(c->io_host + 2 * io_stride, c->next, io_bytes, cudaMemcpyDeviceToHost, c->stream));
   if (with_wave_advance && issued == GPTOSS_OK) {
-    wave_advance<<<1, 1024, 0, c->stream>>>(T, c->wave_offsets, c->next, c->tokens, c->pos, c->row_done,
-                                            c->wave_state);
-    issued = cuda_status(cudaGetLastError());
+    const PdlScope pdl(c->cfg.flags);
+    launch_kernel(wave_advance, dim3((T + kWaveThreads - 1) / kWaveThreads), dim3(kWaveThreads), 0, c->stream, T,
+                  static_cast<const int *>(c->wave_offsets), static_cast<const int *>(c->next), c->tokens, c->pos,
+                  c->row_done, c->wave_state);
+    issued = launch_status();
   }
   cudaGraph_t graph = nullptr;
   st = cuda_status(cudaStreamEndCapture(c->stream, &graph));
@@ -712,7 +733,7 @@ static int wave_reserve(gptoss_chain *c, size_t prompt_ints, size_t generated_in
       st = cuda_status(cudaMemsetAsync(c->wave_state, 0, sizeof(WaveState), c->stream));
     if (st == GPTOSS_OK) {
       // first launch of the bookkeeping kernel outside any capture; with no active row it returns at once
-      wave_advance<<<1, 1024, 0, c->stream>>>(0, nullptr, nullptr, nullptr, nullptr, nullptr, c->wave_state);
+      wave_advance<<<1, kWaveThreads, 0, c->stream>>>(0, nullptr, nullptr, nullptr, nullptr, nullptr, c->wave_state);
       st = cuda_status(cudaGetLastError());
     }
     if (st == GPTOSS_OK)
@@ -789,6 +810,8 @@ int gptoss_chain_run_wave_on_device(gptoss_chain_t *c, const int *prompt_tokens,
   hs->active = n;
   hs->steps_run = 0;
   hs->width = width;
+  hs->arrived = 0u;
+  hs->finished_now = 0;
   hs->pad = 0;
   hs->generated = 0;
   hs->prompts = c->wave_prompts;
