@@ -333,6 +333,17 @@ def test_wave_of_4096_requests_host_loop_and_device_loop_agree(gpu):
         assert a[1:] == b[1:] and np.array_equal(a[0], b[0])
         assert np.array_equal(done_a, ch.download(pkg.BUF_ROW_DONE, 0, np.int32, (n,)))
         assert done_a[::5].all() and not done_a[1::5].any() and a[2] == steps
+        # 1000 requests: the bookkeeping kernel's last block is partly filled
+        a = ch.run_wave(prompts[:1000], steps)
+        b = ch.run_wave(prompts[:1000], steps, on_device=True)
+        assert a[1:] == b[1:] and np.array_equal(a[0], b[0])
+        # every request finishes at its second position: the count of active rows, taken down by
+        # sixteen blocks at once, reaches zero there, and the steps already queued change nothing
+        logits[:, 199999] = big
+        ch.upload(pkg.BUF_LOGITS, 0, logits)
+        for on_device in (False, True):
+            out, total, ran = ch.run_wave([[1, 2]] * n, 40, on_device=on_device)
+            assert ran == 2 and total == n and (out[:, 0] == 199999).all() and (out[:, 1:] == -1).all()
     finally:
         ch.close()
 
