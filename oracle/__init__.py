@@ -266,6 +266,10 @@ class Oracle(_Lib):
         L.orc_bias_rope_rows_table.restype = None
         L.orc_bias_rope_rows_table.argtypes = [_f32p, _opt, _i32p, C.c_int, C.c_int, C.c_int, C.c_int,
                                                _f32p, _f32p, C.c_int]
+        L.orc_bias_rope_rows_table_fma.restype = None
+        L.orc_bias_rope_rows_table_fma.argtypes = L.orc_bias_rope_rows_table.argtypes
+        L.orc_combine_rows_fma.restype = None
+        L.orc_combine_rows_fma.argtypes = [_f32p, _f32p, _i32p, _f32p, _i32p, C.c_int, C.c_int, C.c_int, C.c_int]
         L.orc_yarn_table.restype = None
         L.orc_yarn_table.argtypes = [_f32p, _f32p, C.c_int, C.c_float, C.c_int, C.c_float, C.c_float,
                                      C.c_float, C.c_float, C.c_int]
@@ -303,14 +307,23 @@ class Oracle(_Lib):
                                   np.ascontiguousarray(experts, np.int32), T, k, H, n_experts, threads)
         return x
 
+    def combine_rows_fma(self, x, Z, row_of, weights, experts, threads=1):
+        """The combine with the GPU exact path's rounding: fused multiply-adds in increasing expert order."""
+        x = np.array(x, np.float32, copy=True)
+        T, H = x.shape
+        k = weights.shape[1]
+        self.lib.orc_combine_rows_fma(x, np.ascontiguousarray(Z, np.float32), np.ascontiguousarray(row_of, np.int32),
+                                      np.ascontiguousarray(weights, np.float32),
+                                      np.ascontiguousarray(experts, np.int32), T, k, H, threads)
+        return x
+
     def bias_rope_rows_table(self, qkv, bias, pos, cos_tab, sin_tab, n_q=64, n_kv=8, head_dim=64,
-                             threads=1):
+                             threads=1, fma=False):
         qkv = np.array(qkv, np.float32, copy=True)
         b = None if bias is None else np.ascontiguousarray(bias, np.float32)
-        self.lib.orc_bias_rope_rows_table(qkv, _addr(b), np.ascontiguousarray(pos, np.int32),
-                                          qkv.shape[0], n_q, n_kv, head_dim,
-                                          np.ascontiguousarray(cos_tab, np.float32),
-                                          np.ascontiguousarray(sin_tab, np.float32), threads)
+        fn = self.lib.orc_bias_rope_rows_table_fma if fma else self.lib.orc_bias_rope_rows_table
+        fn(qkv, _addr(b), np.ascontiguousarray(pos, np.int32), qkv.shape[0], n_q, n_kv, head_dim,
+           np.ascontiguousarray(cos_tab, np.float32), np.ascontiguousarray(sin_tab, np.float32), threads)
         return qkv
 
     def yarn_table(self, n_pos, theta=150000.0, head_dim=64, factor=32.0, orig_ctx=4096.0,
@@ -366,10 +379,33 @@ class Reference(_Lib):
             L.ref_moe_gather.restype = None
             L.ref_moe_gather.argtypes = [_f32p, _i32p, C.c_int, C.c_int, _f32p, C.c_int]
 
+        self.has_exact_kernels = hasattr(L, "ref_has_exact_kernels") and bool(L.ref_has_exact_kernels())
+        if self.has_exact_kernels:
+            L.ref_rope_exact.restype = None
+            L.ref_rope_exact.argtypes = [_f32p, C.c_int, C.c_int, _f32p, _f32p, C.c_int, C.c_int]
+            L.ref_moe_combine_exact.restype = None
+            L.ref_moe_combine_exact.argtypes = [_f32p, C.c_int, _f32p, _i32p, _f32p, _i32p, C.c_int, C.c_int]
         self.has_group_ep = hasattr(L, "ref_has_group_ep") and bool(L.ref_has_group_ep())
         if self.has_group_ep:
             L.ref_moe_group_ep.restype = None
             L.ref_moe_group_ep.argtypes = [_i32p, C.c_int, C.c_int, C.c_int, _i32p, _i32p, _i32p, _i32p]
+
+    def rope_exact(self, rows, cos_row, sin_row, n_heads, head_dim):
+        """rope_exact (kernels/misc.hpp:55-70) on biased rows [B, row_stride]: the first n_heads heads of each
+        row rotated by one position's cos/sin, one block per row."""
+        rows = np.array(rows, np.float32, copy=True)
+        self.lib.ref_rope_exact(rows, rows.shape[0], rows.shape[1], np.ascontiguousarray(cos_row, np.float32),
+                                np.ascontiguousarray(sin_row, np.float32), n_heads, head_dim)
+        return rows
+
+    def moe_combine_exact(self, x, Z, pair_row, weights, experts):
+        """moe_combine_exact (kernels/moe.hpp:210-236): one block per token."""
+        x = np.array(x, np.float32, copy=True)
+        k = weights.shape[1]
+        self.lib.ref_moe_combine_exact(x, x.shape[0], np.ascontiguousarray(Z, np.float32),
+                                       np.ascontiguousarray(pair_row, np.int32), np.ascontiguousarray(weights, np.float32),
+                                       np.ascontiguousarray(experts, np.int32), k, x.shape[1])
+        return x
 
     def moe_group_ep(self, topk_e, e_begin, e_count):
         """moe_count_ep_kernel + moe_place_ep_kernel for experts e_begin .. e_begin + e_count - 1 with no

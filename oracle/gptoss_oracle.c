@@ -175,6 +175,25 @@ ORC_API void orc_rotate_heads(float *v, const float *cos_row, const float *sin_r
   }
 }
 
+/* The same rotation as the reference's GPU engine rounds it in its exact path (rope_exact,
+ * kernels/misc.hpp:55-70; rope_pair, kernels/fast_common.hpp:25-28), which is also what a CPU
+ * build with FMA contraction computes: the first product of each line is fused into the
+ * add, the second is rounded on its own. */
+ORC_API void orc_rotate_heads_fma(float *v, const float *cos_row, const float *sin_row, int n_heads,
+                                  int head_dim) {
+  const int half = head_dim / 2;
+  for (int h = 0; h < n_heads; h++) {
+    float *head = v + (size_t)h * head_dim;
+    for (int i = 0; i < half; i++) {
+      const float a = head[i], b = head[half + i];
+      const float c = cos_row[i], s = sin_row[i];
+      const float bs = b * s, as = a * s;
+      head[i] = fmaf(a, c, -bs);
+      head[half + i] = fmaf(b, c, as);
+    }
+  }
+}
+
 /* Clamped SwiGLU of one interleaved gate/up row (run.cpp:701-724). */
 ORC_API void orc_swiglu_row(float *out, const float *gate_up, int n_inter, float limit) {
   const float alpha = 1.702f;
@@ -290,6 +309,23 @@ ORC_API void orc_bias_rope_rows_table(float *qkv, const float *bias, const int *
   }
 }
 
+/* The same with the contracted rotation (orc_rotate_heads_fma). */
+ORC_API void orc_bias_rope_rows_table_fma(float *qkv, const float *bias, const int *pos, int T,
+                                          int n_q_heads, int n_kv_heads, int head_dim,
+                                          const float *cos_tab, const float *sin_tab, int threads) {
+  const int row = (n_q_heads + 2 * n_kv_heads) * head_dim, half = head_dim / 2;
+  const int nt = orc_threads(threads);
+#pragma omp parallel for num_threads(nt) schedule(static)
+  for (int t = 0; t < T; t++) {
+    float *r = qkv + (size_t)t * row;
+    if (bias)
+      for (int i = 0; i < row; i++)
+        r[i] += bias[i];
+    const float *cs = cos_tab + (size_t)pos[t] * half, *sn = sin_tab + (size_t)pos[t] * half;
+    orc_rotate_heads_fma(r, cs, sn, n_q_heads + n_kv_heads, head_dim);
+  }
+}
+
 /* Build the cos/sin table for positions 0..n_pos-1. */
 ORC_API void orc_yarn_table(float *cos_tab, float *sin_tab, int n_pos, float theta, int head_dim,
                             float factor, float orig_ctx, float beta_fast, float beta_slow,
@@ -370,6 +406,41 @@ ORC_API void orc_argmax_rows(int *out, const float *logits, int T, long V, int t
 #pragma omp parallel for num_threads(nt) schedule(static)
   for (int t = 0; t < T; t++)
     out[t] = orc_argmax(logits + (size_t)t * V, (int)V);
+}
+
+/* The combine as the reference's GPU engine rounds it in its exact path (moe_combine_exact,
+ * kernels/moe.hpp:210-236): the token's experts in increasing expert number, a chain of fused
+ * multiply-adds from zero, one add into x.  Equal expert numbers keep their choice order (the
+ * kernel's insertion sort is stable).  Finished tokens (expert -1) are left alone, as by
+ * orc_combine_rows. */
+ORC_API void orc_combine_rows_fma(float *x, const float *Z, const int *row_of, const float *weights,
+                                  const int *experts, int T, int k, int H, int threads) {
+  const int nt = orc_threads(threads);
+#pragma omp parallel for num_threads(nt) schedule(static)
+  for (int t = 0; t < T; t++) {
+    const int *ex = experts + (size_t)t * k;
+    if (ex[0] < 0 || k > 64)
+      continue;
+    int order[64];
+    for (int j = 0; j < k; j++)
+      order[j] = j;
+    for (int i = 1; i < k; i++)
+      for (int j = i; j > 0 && ex[order[j]] < ex[order[j - 1]]; j--) {
+        const int tmp = order[j];
+        order[j] = order[j - 1];
+        order[j - 1] = tmp;
+      }
+    float *xr = x + (size_t)t * H;
+    for (int i = 0; i < H; i++) {
+      float acc = 0.0f;
+      for (int j = 0; j < k; j++) {
+        const size_t p = (size_t)t * k + order[j];
+        if (row_of[p] >= 0)
+          acc = fmaf(Z[(size_t)row_of[p] * H + i], weights[p], acc);
+      }
+      xr[i] += acc;
+    }
+  }
 }
 
 /* Grouping of (token, choice) pairs by expert, the contract of the reference's

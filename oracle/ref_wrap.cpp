@@ -280,6 +280,16 @@ static inline unsigned long long __ballot(int pred) {
 #define __shared__ static
 #define __syncthreads() pthread_barrier_wait(&ref_group::block_barrier)
 #include REF_GROUP_PART
+#ifdef REF_EXACT_PART
+// rope_exact and moe_combine_exact, the GPU engine's bit-exact rotation and combine: plain C per
+// thread with the rounding of every step spelled out (__fmaf_rn, __fmul_rn, __fadd_rn); here
+// fmaf() and the plain operators (the build targets baseline x86-64, which has no fused
+// instruction for the compiler to contract them into; ref_has_exact_kernels() checks it).
+static inline float __fmaf_rn(float a, float b, float c) { return fmaf(a, b, c); }
+static inline float __fmul_rn(float a, float b) { return a * b; }
+static inline float __fadd_rn(float a, float b) { return a + b; }
+#include REF_EXACT_PART
+#endif
 #ifdef REF_GROUP_EP_PART
 #include REF_GROUP_EP_PART
 #endif
@@ -320,6 +330,41 @@ REF_API void ref_moe_gather(const float *x, const int *row_pair, int R, int k, f
       ref_group::moe_gather_kernel(x, row_pair, k, Xg, H);
     }
 }
+
+#ifdef REF_EXACT_PART
+// 1 if a * b + c written with plain operators rounds twice in this build, as the kernels' spelled-out
+// steps require; 0 (and the pin is skipped) if the compiler fused it.
+REF_API int ref_has_exact_kernels(void) {
+  volatile float a = 1.0f + 0x1p-12f, b = 1.0f + 0x1p-12f, c = -1.0f;
+  const float twice = ref_group::__fadd_rn(ref_group::__fmul_rn(a, b), c);
+  return twice != fmaf(a, b, c);
+}
+// No barrier in either kernel: a block's threads are a loop.
+REF_API void ref_rope_exact(float *qkv, int B, int row_stride, const float *cosv, const float *sinv, int n_heads,
+                            int head_dim) {
+  std::lock_guard<std::mutex> lock(ref_group::one_block_at_a_time);
+  ref_group::blockDim.x = 256;
+  for (int b = 0; b < B; b++)
+    for (int t = 0; t < 256; t++) {
+      ref_group::blockIdx.x = b;
+      ref_group::threadIdx.x = t;
+      ref_group::rope_exact(qkv, row_stride, cosv, sinv, n_heads, head_dim);
+    }
+}
+REF_API void ref_moe_combine_exact(float *x, int B, const float *Z, const int *pair_row, const float *topk_w,
+                                   const int *topk_e, int k, int H) {
+  std::lock_guard<std::mutex> lock(ref_group::one_block_at_a_time);
+  ref_group::blockDim.x = 256;
+  for (int b = 0; b < B; b++)
+    for (int t = 0; t < 256; t++) {
+      ref_group::blockIdx.x = b;
+      ref_group::threadIdx.x = t;
+      ref_group::moe_combine_exact(x, Z, pair_row, topk_w, topk_e, k, H);
+    }
+}
+#else
+REF_API int ref_has_exact_kernels(void) { return 0; }
+#endif
 
 #ifdef REF_GROUP_EP_PART
 REF_API int ref_has_group_ep(void) { return 1; }
@@ -363,4 +408,5 @@ REF_API int ref_has_group_ep(void) { return 0; }
 #else
 REF_API int ref_has_group(void) { return 0; }
 REF_API int ref_has_group_ep(void) { return 0; }
+REF_API int ref_has_exact_kernels(void) { return 0; }
 #endif

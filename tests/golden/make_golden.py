@@ -23,6 +23,8 @@ stores the expected outputs:
     gathered rows: the REFERENCE's moe_group_kernel / moe_gather_kernel (kernels/moe.hpp), their
     bodies run on host threads; for part of the experts its moe_count_ep_kernel +
     moe_place_ep_kernel (kernels/moe_ep.hpp) the same way, 64 host threads to a wavefront;
+  * the rotation and the combine with the GPU exact path's rounding (fused multiply-adds): the
+    REFERENCE's rope_exact (kernels/misc.hpp) and moe_combine_exact (kernels/moe.hpp), run on the host;
   * SwiGLU rows and combine rows: produced by the restated oracle (the reference has no
     callable form of those loops); they are regression vectors for the oracle, whose
     agreement with forward() is checked separately.
@@ -88,6 +90,15 @@ def main():
         rows, total, ran, done, fed, mask = ref.wave_bookkeeping(prompts, picked, steps)
         out[f"wave{j}_rows"], out[f"wave{j}_counts"] = rows, np.array([total, ran], np.int64)
         out[f"wave{j}_done"], out[f"wave{j}_fed"], out[f"wave{j}_mask"] = done, fed, mask.astype(np.int8)
+
+    # the contracted (fused multiply-add) flavour of the rotation and the combine: the REFERENCE's GPU
+    # exact kernels rope_exact (kernels/misc.hpp) and moe_combine_exact (kernels/moe.hpp), bodies run on the host
+    qkv, bias, pos = gi.case_rope()
+    biased = (qkv + bias).astype(np.float32)
+    out["rope_fma_out"] = np.concatenate([ref.rope_exact(biased[t:t + 1], *ref.yarn_cos_sin(int(pos[t])), 64 + 8, 64)
+                                          for t in range(len(pos))])
+    xc, Z, row_of, wt, e = gi.case_combine()
+    out["combine_fma_x"] = ref.moe_combine_exact(xc, Z, row_of, wt, e)
 
     for j, (e, E) in enumerate(gi.case_group()):
         off, rp, pr = ref.moe_group(e, E)

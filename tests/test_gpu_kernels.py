@@ -205,6 +205,8 @@ def test_bias_rope_fp32_mode_is_bit_exact(gpu, orc, T, heads):
     emu[:, :nq + nkv, 0] = fma32(x1, c_, -(x2 * s_))
     emu[:, :nq + nkv, 1] = fma32(x2, c_, x1 * s_)
     assert rel_err(o3.get(), emu.reshape(T, row)) <= 1e-6
+    # and bit for bit against the oracle's contracted form, which is pinned to the reference's rope_exact
+    assert n_bit_diff(o3.get(), orc.bias_rope_rows_table(qkv, bias, pos, ct, st, nq, nkv, hd, fma=True)) == 0
 
 
 def test_bias_rope_strided_rows_and_position_clamp(gpu, orc):
@@ -425,6 +427,8 @@ def test_combine_fp32_mode_is_bit_exact(gpu, orc, T, k, Hd):
             acc = fma32(Z[row_of[t, j]], w[t, j], acc)
         emu[t] = x[t] + acc
     assert rel_err(xb5.get(), emu) <= 1e-6
+    # and bit for bit against the oracle's contracted form, which is pinned to the reference's moe_combine_exact
+    assert n_bit_diff(xb5.get(), orc.combine_rows_fma(x, Z, row_of, w, e)) == 0
 
 
 @pytest.mark.parametrize("T,k,Hd", [(1, 4, 2880), (9, 4, 2880), (512, 4, 2880), (33, 2, 1000), (33, 8, 4096), (5, 4, 77)])
@@ -523,6 +527,9 @@ def test_golden_vectors_through_the_gpu(gpu, golden):
     pkg.qkv_bias_rope(4, d.put(qkv), pkg.F32, gi.QKV, d.put(bias), d.put(pos), 0, d.put(ct), d.put(st), 4096,
                       64, 8, 64, o, pkg.F32, gi.QKV, flags=pkg.EXACT)
     assert n_bit_diff(o.get(), golden["rope_out"]) == 0
+    pkg.qkv_bias_rope(4, d.put(qkv), pkg.F32, gi.QKV, d.put(bias), d.put(pos), 0, d.put(ct), d.put(st), 4096,
+                      64, 8, 64, o, pkg.F32, gi.QKV, flags=pkg.EXACT | pkg.FMA)
+    assert n_bit_diff(o.get(), golden["rope_fma_out"]) == 0   # the reference's rope_exact
 
     for s, tag in zip(gi.case_router(), ("router20", "router120")):
         T, E = s.shape
@@ -540,6 +547,9 @@ def test_golden_vectors_through_the_gpu(gpu, golden):
     xb = d.put_inout(xc)
     pkg.moe_combine(6, xb, d.put(Z), pkg.F32, d.put(row_of), d.put(w), d.put(e), 4, gi.H, flags=pkg.EXACT)
     assert n_bit_diff(xb.get(), golden["combine_x"]) == 0
+    xb = d.put_inout(xc)
+    pkg.moe_combine(6, xb, d.put(Z), pkg.F32, d.put(row_of), d.put(w), d.put(e), 4, gi.H, flags=pkg.EXACT | pkg.FMA)
+    assert n_bit_diff(xb.get(), golden["combine_fma_x"]) == 0   # the reference's moe_combine_exact
 
     lg = gi.case_argmax()
     for dt in (pkg.F32, pkg.BF16):  # the coarse grid is exact in bf16

@@ -344,6 +344,43 @@ def test_ref_group_and_gather(orc, ref):
         assert_bit_equal(orc.moe_gather(t, full[1], e.shape[1]), ref.moe_gather(t, full[1], e.shape[1]), "rows")
 
 
+def test_golden_contracted_rotation_and_combine(orc, golden):
+    qkv, bias, pos = gi.case_rope()
+    ct, st = orc.yarn_table(4096)
+    assert_bit_equal(orc.bias_rope_rows_table(qkv, bias, pos, ct, st, fma=True), golden["rope_fma_out"], "rope, fma")
+    xc, Z, row_of, wt, e = gi.case_combine()
+    assert_bit_equal(orc.combine_rows_fma(xc, Z, row_of, wt, e), golden["combine_fma_x"], "combine, fma")
+    assert not np.array_equal(golden["rope_fma_out"], golden["rope_out"]), "the two flavours differ somewhere"
+
+
+def test_ref_exact_kernels_pin_the_contracted_forms(orc, ref):
+    """The fused-multiply-add flavour of the rotation and of the combine (GPTOSS_EXACT | GPTOSS_FMA)
+    against the reference's GPU exact kernels rope_exact (kernels/misc.hpp:55-70) and
+    moe_combine_exact (kernels/moe.hpp:210-236), whose bodies -- plain C per thread, every rounding
+    step named -- the reference library runs on the host: bit for bit."""
+    if not ref.has_exact_kernels:
+        pytest.skip("reference library built without its exact kernels, or with contraction on")
+    r = np.random.default_rng(37)
+    for nq, nkv, hd in ((64, 8, 64), (5, 2, 32), (1, 1, 128)):
+        B, row = 7, (nq + 2 * nkv) * hd
+        rows = (r.standard_normal((B, row)) * 10.0 ** r.integers(-3, 4, (B, 1))).astype(np.float32)
+        if hd == 64:
+            c, s_ = orc.yarn_table(128)
+        else:  # any table will do for the rounding sequence
+            c, s_ = (r.uniform(-1.4, 1.4, (128, hd // 2)).astype(np.float32) for _ in range(2))
+        for p in (0, 1, 77):
+            want = ref.rope_exact(rows, c[p], s_[p], nq + nkv, hd)
+            got = orc.bias_rope_rows_table(rows, None, np.full(B, p, np.int32), c, s_, nq, nkv, hd, fma=True)
+            assert_bit_equal(got, want, f"rope {nq}/{nkv}/{hd} at {p}")
+    for T, k, Hd, E in ((33, 4, 2880, 32), (9, 8, 100, 16), (5, 1, 64, 4), (12, 4, 77, 128)):
+        x = r.standard_normal((T, Hd)).astype(np.float32)
+        Z = (r.standard_normal((T * k, Hd)) * 3).astype(np.float32)
+        w = r.random((T, k)).astype(np.float32)
+        e = np.stack([r.permutation(E)[:k] for _ in range(T)]).astype(np.int32)
+        row_of = r.permutation(T * k).astype(np.int32).reshape(T, k)
+        assert_bit_equal(orc.combine_rows_fma(x, Z, row_of, w, e), ref.moe_combine_exact(x, Z, row_of, w, e), "combine")
+
+
 def test_ref_group_for_part_of_the_experts(orc, ref):
     """Grouping for experts e_begin .. e_begin + e_count - 1 against the reference's
     moe_count_ep_kernel + moe_place_ep_kernel (kernels/moe_ep.hpp:55-127; the pair moe_group_ep
