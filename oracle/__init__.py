@@ -385,10 +385,26 @@ class Reference(_Lib):
             L.ref_rope_exact.argtypes = [_f32p, C.c_int, C.c_int, _f32p, _f32p, C.c_int, C.c_int]
             L.ref_moe_combine_exact.restype = None
             L.ref_moe_combine_exact.argtypes = [_f32p, C.c_int, _f32p, _i32p, _f32p, _i32p, C.c_int, C.c_int]
+        self.has_router_wave = hasattr(L, "ref_has_router_wave") and bool(L.ref_has_router_wave())
+        if self.has_router_wave:
+            L.ref_router_topk_wave.restype = None
+            L.ref_router_topk_wave.argtypes = [_f32p, C.c_int, C.c_int, _f32p, _i32p, C.c_int, _opt, _opt]
         self.has_group_ep = hasattr(L, "ref_has_group_ep") and bool(L.ref_has_group_ep())
         if self.has_group_ep:
             L.ref_moe_group_ep.restype = None
             L.ref_moe_group_ep.argtypes = [_i32p, C.c_int, C.c_int, C.c_int, _i32p, _i32p, _i32p, _i32p]
+
+    def router_topk_wave(self, logits, k, done=None, slot_of=None):
+        """router_topk_wave_kernel (kernels/moe.hpp:64-136), the router the engine launches: (weights, experts);
+        outputs start from a fill so that anything the kernel leaves unwritten shows."""
+        lg = np.ascontiguousarray(logits, np.float32)
+        B, E = lg.shape
+        w = np.full((B, k), -7.0, np.float32)
+        e = np.full((B, k), -7, np.int32)
+        dn = None if done is None else np.ascontiguousarray(done, np.int32)
+        so = None if slot_of is None else np.ascontiguousarray(slot_of, np.int32)
+        self.lib.ref_router_topk_wave(lg, E, k, w, e, B, _addr(dn), _addr(so))
+        return w, e
 
     def rope_exact(self, rows, cos_row, sin_row, n_heads, head_dim):
         """rope_exact (kernels/misc.hpp:55-70) on biased rows [B, row_stride]: the first n_heads heads of each

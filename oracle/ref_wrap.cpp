@@ -253,15 +253,30 @@ static std::mutex one_block_at_a_time;
 // (kernels/moe_ep.hpp): every lane of the wave calls them together, as on the GPU.
 static pthread_barrier_t wave_barrier[16];
 static long long wave_slot[16][64];
-static inline long long wave_exchange(long long mine, int from_lane_offset) {
+static inline long long wave_read(long long mine, int src_lane) {
   const int wave = threadIdx.x / 64, lane = threadIdx.x % 64;
   wave_slot[wave][lane] = mine;
   pthread_barrier_wait(&wave_barrier[wave]);
-  const long long got = lane + from_lane_offset < 64 ? wave_slot[wave][lane + from_lane_offset] : mine;
+  const long long got = wave_slot[wave][src_lane >= 0 && src_lane < 64 ? src_lane : lane];
   pthread_barrier_wait(&wave_barrier[wave]);
   return got;
 }
-static inline int __shfl_down(int v, int offset) { return (int)wave_exchange(v, offset); }
+static inline long long bits_of(float v) {
+  int u;
+  memcpy(&u, &v, 4);
+  return u;
+}
+static inline float float_of(long long bits) {
+  const int u = (int)bits;
+  float v;
+  memcpy(&v, &u, 4);
+  return v;
+}
+static inline int __shfl_down(int v, int offset) { return (int)wave_read(v, threadIdx.x % 64 + offset); }
+static inline int __shfl_xor(int v, int mask) { return (int)wave_read(v, (threadIdx.x % 64) ^ mask); }
+static inline float __shfl_xor(float v, int mask) { return float_of(wave_read(bits_of(v), (threadIdx.x % 64) ^ mask)); }
+static inline int __shfl(int v, int lane) { return (int)wave_read(v, lane); }
+static inline float __shfl(float v, int lane) { return float_of(wave_read(bits_of(v), lane)); }
 static inline unsigned long long __ballot(int pred) {
   const int wave = threadIdx.x / 64, lane = threadIdx.x % 64;
   wave_slot[wave][lane] = pred != 0;
@@ -292,6 +307,29 @@ static inline float __fadd_rn(float a, float b) { return a + b; }
 #endif
 #ifdef REF_GROUP_EP_PART
 #include REF_GROUP_EP_PART
+#endif
+#ifdef REF_ROUTER_PART
+// router_topk_wave_kernel (kernels/moe.hpp:64-136) with the expf_cpu it calls
+// (kernels/exact_math.hpp:12-52): the device's correctly rounded double operations are the
+// host's plain ones.
+static inline uint32_t __float_as_uint(float v) { return (uint32_t)bits_of(v); }
+static inline long long __double_as_longlong(double v) {
+  long long u;
+  memcpy(&u, &v, 8);
+  return u;
+}
+static inline double __longlong_as_double(long long u) {
+  double v;
+  memcpy(&v, &u, 8);
+  return v;
+}
+static inline double __dmul_rn(double a, double b) { return a * b; }
+static inline double __dadd_rn(double a, double b) { return a + b; }
+static inline double __dsub_rn(double a, double b) { return a - b; }
+static inline double __ddiv_rn(double a, double b) { return a / b; }
+static inline double __fma_rn(double a, double b, double c) { return fma(a, b, c); }
+static inline int min(int a, int b) { return a < b ? a : b; }
+#include REF_ROUTER_PART
 #endif
 #undef __syncthreads
 #undef __shared__
@@ -366,6 +404,36 @@ REF_API void ref_moe_combine_exact(float *x, int B, const float *Z, const int *p
 REF_API int ref_has_exact_kernels(void) { return 0; }
 #endif
 
+#ifdef REF_ROUTER_PART
+REF_API int ref_has_router_wave(void) { return 1; }
+// One 64-lane wave per row, TOPK_WAVES rows per block, as the engine launches it
+// (engine/gpu_engine.hpp:524-527).  No block barrier in the kernel: a wave whose row is past the
+// end leaves at once, the others only meet inside their own wave.
+REF_API void ref_router_topk_wave(const float *logits, int E, int k, float *topk_w, int *topk_e, int B, const int *done,
+                                  const int *slot_of) {
+  std::lock_guard<std::mutex> lock(ref_group::one_block_at_a_time);
+  const int threads = 64 * TOPK_WAVES;
+  ref_group::blockDim.x = threads;
+  for (int block = 0; block < (B + TOPK_WAVES - 1) / TOPK_WAVES; block++) {
+    for (int w = 0; w < TOPK_WAVES; w++)
+      pthread_barrier_init(&ref_group::wave_barrier[w], nullptr, 64);
+    std::vector<std::thread> pool;
+    for (int t = 0; t < threads; t++)
+      pool.emplace_back([=] {
+        ref_group::threadIdx.x = t;
+        ref_group::blockIdx.x = block;
+        ref_group::router_topk_wave_kernel(logits, E, k, topk_w, topk_e, B, done, slot_of);
+      });
+    for (auto &t : pool)
+      t.join();
+    for (int w = 0; w < TOPK_WAVES; w++)
+      pthread_barrier_destroy(&ref_group::wave_barrier[w]);
+  }
+}
+#else
+REF_API int ref_has_router_wave(void) { return 0; }
+#endif
+
 #ifdef REF_GROUP_EP_PART
 REF_API int ref_has_group_ep(void) { return 1; }
 // moe_count_ep_kernel then moe_place_ep_kernel (kernels/moe_ep.hpp:55-127), the pair that
@@ -409,4 +477,5 @@ REF_API int ref_has_group_ep(void) { return 0; }
 REF_API int ref_has_group(void) { return 0; }
 REF_API int ref_has_group_ep(void) { return 0; }
 REF_API int ref_has_exact_kernels(void) { return 0; }
+REF_API int ref_has_router_wave(void) { return 0; }
 #endif

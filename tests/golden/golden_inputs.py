@@ -221,3 +221,10 @@ def case_group():
 def group_ranges(E):
     """(e_begin, e_count) of the groupings for part of the experts that the golden file holds."""
     return ((0, E // 2), (E // 2, E // 2), (5, 3), (E - 1, 1))
+
+
+def router_done_and_slots(T, E):
+    """The finished-row flags and the expert renumbering table of the golden router cases."""
+    done = (np.arange(T) % 5 == 0).astype(np.int32)
+    slot_of = ((np.arange(E) * 37 + 5) % E).astype(np.int32)
+    return done, slot_of

@@ -23,6 +23,8 @@ stores the expected outputs:
     gathered rows: the REFERENCE's moe_group_kernel / moe_gather_kernel (kernels/moe.hpp), their
     bodies run on host threads; for part of the experts its moe_count_ep_kernel +
     moe_place_ep_kernel (kernels/moe_ep.hpp) the same way, 64 host threads to a wavefront;
+  * the router's output for finished rows and with an expert renumbering table: the REFERENCE's
+    router_topk_wave_kernel (kernels/moe.hpp), run on host threads;
   * the rotation and the combine with the GPU exact path's rounding (fused multiply-adds): the
     REFERENCE's rope_exact (kernels/misc.hpp) and moe_combine_exact (kernels/moe.hpp), run on the host;
   * SwiGLU rows and combine rows: produced by the restated oracle (the reference has no
@@ -65,6 +67,12 @@ def main():
     a, b = gi.case_router()
     out["router20_w"], out["router20_e"] = ref.router_rows(a)
     out["router120_w"], out["router120_e"] = ref.router_rows(b)
+
+    # finished rows and renumbered experts: the REFERENCE's router_topk_wave_kernel (kernels/moe.hpp), the router
+    # its engine launches, run on host threads (64 to a wave)
+    for sc, tag in ((a, "router20"), (b, "router120")):
+        done, slot_of = gi.router_done_and_slots(*sc.shape)
+        out[tag + "_wave_w"], out[tag + "_wave_e"] = ref.router_topk_wave(sc, 4, done, slot_of)
 
     out["argmax"] = ref.argmax_rows(gi.case_argmax())
 

@@ -537,6 +537,10 @@ def test_golden_vectors_through_the_gpu(gpu, golden):
         pkg.router_topk(T, d.put(s), pkg.F32, E, 4, wb, eb)
         assert np.array_equal(eb.get(), golden[tag + "_e"])
         assert n_bit_diff(wb.get(), golden[tag + "_w"]) == 0
+        done, slot_of = gi.router_done_and_slots(T, E)   # the reference's router_topk_wave_kernel
+        pkg.router_topk(T, d.put(s), pkg.F32, E, 4, wb, eb, done=d.put(done), slot_of=d.put(slot_of))
+        assert np.array_equal(eb.get(), golden[tag + "_wave_e"])
+        assert n_bit_diff(wb.get(), golden[tag + "_wave_w"]) == 0
 
     y = gi.case_swiglu()
     g = d.out((4, gi.H), pkg.F32)

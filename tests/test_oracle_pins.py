@@ -344,6 +344,48 @@ def test_ref_group_and_gather(orc, ref):
         assert_bit_equal(orc.moe_gather(t, full[1], e.shape[1]), ref.moe_gather(t, full[1], e.shape[1]), "rows")
 
 
+def _with_done_and_slots(w, e, done, slot_of):
+    """What finished rows and a renumbering table do to a router result (kernels/moe.hpp:60-63): a
+    finished row gets expert -1 and weight 0 for every choice; the others the table's number for
+    each chosen expert, the choice and the weights unchanged."""
+    live = (np.asarray(done) == 0)[:, None]
+    return np.where(live, w, np.float32(0)).astype(np.float32), np.where(live, np.asarray(slot_of)[e], -1).astype(np.int32)
+
+
+def test_golden_router_finished_rows_and_slots(orc, golden):
+    for sc, tag in zip(gi.case_router(), ("router20", "router120")):
+        done, slot_of = gi.router_done_and_slots(*sc.shape)
+        w, e = _with_done_and_slots(*orc.router_rows(sc, 4), done, slot_of)
+        assert np.array_equal(e, golden[tag + "_wave_e"])
+        assert_bit_equal(w, golden[tag + "_wave_w"], tag)
+
+
+def test_ref_router_wave_kernel(orc, ref):
+    """The router the engine launches, router_topk_wave_kernel (kernels/moe.hpp:64-136, with
+    expf_cpu of kernels/exact_math.hpp), run on host threads with a 64-wide wave's shuffles
+    emulated: experts and weights equal the oracle's (that is, topk() + softmax() of run.cpp) bit
+    for bit, planted ties included, and finished rows and the renumbering table act as the GPU
+    tests assume."""
+    if not ref.has_router_wave:
+        pytest.skip("reference library built without kernels/moe.hpp's router")
+    r = np.random.default_rng(41)
+    for E, k, B in ((32, 4, 41), (128, 4, 22), (200, 2, 9), (16, 8, 6), (256, 8, 5)):
+        s = r.standard_normal((B, E)).astype(np.float32)
+        s[::3, E - 1] = s[::3, 2]
+        s[::5] = np.trunc(s[::5] * 2)
+        s[1, 1], s[1, E // 2] = 0.0, -0.0
+        w, e = orc.router_rows(s, k)
+        w_ref, e_ref = ref.router_topk_wave(s, k)
+        assert np.array_equal(e, e_ref), (E, k)
+        assert_bit_equal(w, w_ref, "weights")
+        done = (r.random(B) < 0.3).astype(np.int32)
+        slot_of = r.permutation(E).astype(np.int32)
+        w_ref, e_ref = ref.router_topk_wave(s, k, done, slot_of)
+        w_want, e_want = _with_done_and_slots(w, e, done, slot_of)
+        assert np.array_equal(e_want, e_ref), (E, k)
+        assert_bit_equal(w_want, w_ref, "weights of live rows, zeros of finished ones")
+
+
 def test_golden_contracted_rotation_and_combine(orc, golden):
     qkv, bias, pos = gi.case_rope()
     ct, st = orc.yarn_table(4096)
