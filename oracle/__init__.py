@@ -389,6 +389,11 @@ class Reference(_Lib):
         if self.has_router_wave:
             L.ref_router_topk_wave.restype = None
             L.ref_router_topk_wave.argtypes = [_f32p, C.c_int, C.c_int, _f32p, _i32p, C.c_int, _opt, _opt]
+        self.has_rope_kv = hasattr(L, "ref_has_rope_kv") and bool(L.ref_has_rope_kv())
+        if self.has_rope_kv:
+            L.ref_rope_kv_bf16.restype = None
+            L.ref_rope_kv_bf16.argtypes = [C.c_int, _f32p, C.c_int, _f32p, _f32p, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
+                                           C.c_void_p, C.c_int, C.c_int, C.c_int]
         self.has_group_ep = hasattr(L, "ref_has_group_ep") and bool(L.ref_has_group_ep())
         if self.has_group_ep:
             L.ref_moe_group_ep.restype = None
@@ -405,6 +410,16 @@ class Reference(_Lib):
         so = None if slot_of is None else np.ascontiguousarray(slot_of, np.int32)
         self.lib.ref_router_topk_wave(lg, E, k, w, e, B, _addr(dn), _addr(so))
         return w, e
+
+    def rope_kv_bf16(self, rows, cos_row, sin_row, n_q, n_kv, kc, vq, vs, slots, slot, rotate_q=True):
+        """rope_kv_bf16_kernel (kernels/fast_misc.hpp:48-108) as its launcher instantiates it: rotates the rows
+        in place (a copy is returned) and writes row b's keys and values into the caches at (b, slot)."""
+        rows = np.array(rows, np.float32, copy=True)
+        assert kc.dtype == np.uint16 and vq.dtype == np.int8 and vs.dtype == np.float32
+        self.lib.ref_rope_kv_bf16(rows.shape[0], rows, rows.shape[1], np.ascontiguousarray(cos_row, np.float32),
+                                  np.ascontiguousarray(sin_row, np.float32), n_q, n_kv, kc.ctypes.data, vq.ctypes.data,
+                                  vs.ctypes.data, slots, slot, int(rotate_q))
+        return rows
 
     def rope_exact(self, rows, cos_row, sin_row, n_heads, head_dim):
         """rope_exact (kernels/misc.hpp:55-70) on biased rows [B, row_stride]: the first n_heads heads of each

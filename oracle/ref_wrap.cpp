@@ -308,6 +308,14 @@ static inline float __fadd_rn(float a, float b) { return a + b; }
 #ifdef REF_GROUP_EP_PART
 #include REF_GROUP_EP_PART
 #endif
+static inline int min(int a, int b) { return a < b ? a : b; }
+#if defined(REF_ROPE_KV_PART) && defined(REF_EXACT_PART) && defined(REF_CACHE_PART)
+// rope_pair (kernels/fast_common.hpp:25-28) and rope_kv_bf16_kernel (kernels/fast_misc.hpp:48-108):
+// the engine's rotation + KV-cache write in one launch.  It calls the index functions and the
+// rounding rule included above, and one wave-wide maximum per value head.
+#include REF_ROPE_KV_PART
+#define REF_HAS_ROPE_KV 1
+#endif
 #ifdef REF_ROUTER_PART
 // router_topk_wave_kernel (kernels/moe.hpp:64-136) with the expf_cpu it calls
 // (kernels/exact_math.hpp:12-52): the device's correctly rounded double operations are the
@@ -328,7 +336,6 @@ static inline double __dadd_rn(double a, double b) { return a + b; }
 static inline double __dsub_rn(double a, double b) { return a - b; }
 static inline double __ddiv_rn(double a, double b) { return a / b; }
 static inline double __fma_rn(double a, double b, double c) { return fma(a, b, c); }
-static inline int min(int a, int b) { return a < b ? a : b; }
 #include REF_ROUTER_PART
 #endif
 #undef __syncthreads
@@ -402,6 +409,41 @@ REF_API void ref_moe_combine_exact(float *x, int B, const float *Z, const int *p
 }
 #else
 REF_API int ref_has_exact_kernels(void) { return 0; }
+#endif
+
+#ifdef REF_HAS_ROPE_KV
+REF_API int ref_has_rope_kv(void) { return 1; }
+// B blocks of 256 threads (four 64-wide waves, no block barrier), instantiated as the launcher
+// rope_kv_bf16 chooses (kernels/fast_misc.hpp:110-127): rotate_q = 0 starts at the first key head.
+REF_API void ref_rope_kv_bf16(int B, float *qkv, int row_stride, const float *cosv, const float *sinv, int n_q_heads,
+                              int n_kv_heads, uint16_t *kc, int8_t *vq, float *vs, int slots, int slot, int rotate_q) {
+  std::lock_guard<std::mutex> lock(ref_group::one_block_at_a_time);
+  const int h0 = rotate_q ? 0 : n_q_heads;
+  const int ns = (n_q_heads + n_kv_heads - h0 + 7) / 8, nv = (n_kv_heads * 64 + 255) / 256;
+  ref_group::blockDim.x = 256;
+  for (int block = 0; block < B; block++) {
+    for (int w = 0; w < 4; w++)
+      pthread_barrier_init(&ref_group::wave_barrier[w], nullptr, 64);
+    std::vector<std::thread> pool;
+    for (int t = 0; t < 256; t++)
+      pool.emplace_back([=] {
+        ref_group::threadIdx.x = t;
+        ref_group::blockIdx.x = block;
+        if (ns == 1 && nv == 2)
+          ref_group::rope_kv_bf16_kernel<1, 2>(qkv, row_stride, cosv, sinv, n_q_heads, n_kv_heads, h0, kc, vq, vs, slots, slot);
+        else if (ns == 9 && nv == 2)
+          ref_group::rope_kv_bf16_kernel<9, 2>(qkv, row_stride, cosv, sinv, n_q_heads, n_kv_heads, h0, kc, vq, vs, slots, slot);
+        else
+          ref_group::rope_kv_bf16_kernel<16, 4>(qkv, row_stride, cosv, sinv, n_q_heads, n_kv_heads, h0, kc, vq, vs, slots, slot);
+      });
+    for (auto &t : pool)
+      t.join();
+    for (int w = 0; w < 4; w++)
+      pthread_barrier_destroy(&ref_group::wave_barrier[w]);
+  }
+}
+#else
+REF_API int ref_has_rope_kv(void) { return 0; }
 #endif
 
 #ifdef REF_ROUTER_PART
@@ -478,4 +520,5 @@ REF_API int ref_has_group(void) { return 0; }
 REF_API int ref_has_group_ep(void) { return 0; }
 REF_API int ref_has_exact_kernels(void) { return 0; }
 REF_API int ref_has_router_wave(void) { return 0; }
+REF_API int ref_has_rope_kv(void) { return 0; }
 #endif

@@ -228,3 +228,10 @@ def router_done_and_slots(T, E):
     done = (np.arange(T) % 5 == 0).astype(np.int32)
     slot_of = ((np.arange(E) * 37 + 5) % E).astype(np.int32)
     return done, slot_of
+
+
+def case_rope_kv():
+    """The engine's rotation + KV-cache write call: rows [3, 5120] at one position, one cache slot."""
+    rows = uniform(81, (3, QKV), 2.5)
+    rows[1, (64 + 8) * 64:(64 + 8) * 64 + 64] = 0.0   # a value head of zeros
+    return rows, 37, 64, 21   # rows, position, slots, slot

@@ -23,6 +23,8 @@ stores the expected outputs:
     gathered rows: the REFERENCE's moe_group_kernel / moe_gather_kernel (kernels/moe.hpp), their
     bodies run on host threads; for part of the experts its moe_count_ep_kernel +
     moe_place_ep_kernel (kernels/moe_ep.hpp) the same way, 64 host threads to a wavefront;
+  * rotated rows, bf16 keys, int8 value codes and scales of the engine's rotation + cache write: the
+    REFERENCE's rope_kv_bf16_kernel (kernels/fast_misc.hpp), run on host threads;
   * the router's output for finished rows and with an expert renumbering table: the REFERENCE's
     router_topk_wave_kernel (kernels/moe.hpp), run on host threads;
   * the rotation and the combine with the GPU exact path's rounding (fused multiply-adds): the
@@ -107,6 +109,14 @@ def main():
                                           for t in range(len(pos))])
     xc, Z, row_of, wt, e = gi.case_combine()
     out["combine_fma_x"] = ref.moe_combine_exact(xc, Z, row_of, wt, e)
+
+    # the engine's rotation + KV-cache write in one launch: the REFERENCE's rope_kv_bf16_kernel
+    # (kernels/fast_misc.hpp), run on host threads
+    rows, p_, slots, slot = gi.case_rope_kv()
+    n_k = rows.shape[0] * slots * 512
+    kc, vq, vs = np.zeros(n_k, np.uint16), np.zeros(n_k, np.int8), np.zeros(n_k // 64, np.float32)
+    out["rope_kv_rows"] = ref.rope_kv_bf16(rows, *ref.yarn_cos_sin(p_), 64, 8, kc, vq, vs, slots, slot)
+    out["rope_kv_keys"], out["rope_kv_codes"], out["rope_kv_scales"] = kc, vq, vs
 
     for j, (e, E) in enumerate(gi.case_group()):
         off, rp, pr = ref.moe_group(e, E)

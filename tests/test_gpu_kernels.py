@@ -555,6 +555,18 @@ def test_golden_vectors_through_the_gpu(gpu, golden):
     pkg.moe_combine(6, xb, d.put(Z), pkg.F32, d.put(row_of), d.put(w), d.put(e), 4, gi.H, flags=pkg.EXACT | pkg.FMA)
     assert n_bit_diff(xb.get(), golden["combine_fma_x"]) == 0   # the reference's moe_combine_exact
 
+    # the engine's rotation + cache write in one launch (in place, one position, one slot): the bits of the
+    # reference's rope_kv_bf16_kernel -- queries in the rows, keys, codes and scales in the caches
+    rows, p_, slots, slot = gi.case_rope_kv()
+    n_k = rows.shape[0] * slots * 512
+    kc, vq, vs = d.put_inout(np.zeros(n_k, np.uint16)), d.put_inout(np.zeros(n_k, np.int8)), d.put_inout(np.zeros(n_k // 64, np.float32))
+    qb = d.put_inout(rows)
+    pkg.qkv_bias_rope_kv(rows.shape[0], qb, pkg.F32, gi.QKV, None, None, p_, d.put(ct), d.put(st), 4096, 64, 8, 64, qb,
+                         pkg.F32, gi.QKV, kc, vq, vs, slots, slot_scalar=slot, flags=pkg.EXACT | pkg.FMA)
+    assert n_bit_diff(qb.get()[:, :4096], golden["rope_kv_rows"][:, :4096]) == 0
+    assert np.array_equal(kc.get(as_f32=False), golden["rope_kv_keys"]) and np.array_equal(vq.get(), golden["rope_kv_codes"])
+    assert n_bit_diff(vs.get(), golden["rope_kv_scales"]) == 0
+
     lg = gi.case_argmax()
     for dt in (pkg.F32, pkg.BF16):  # the coarse grid is exact in bf16
         out = d.out((3,), np.int32)
@@ -654,8 +666,8 @@ def test_combine_behind_a_partial_expert_range(gpu, orc, Hd):
         pkg.moe_combine(T, xb, d.put(z), pkg.F32, d.put(own_row), d.put(w), d.put(e), k, Hd, flags=flags)
         if flags == pkg.EXACT:
             assert n_bit_diff(xb.get(), want) == 0
-        else:  # fused multiply-adds against the oracle's separate products: a last bit here and there
-            assert rel_err(xb.get(), want) <= TOL_F32 * 10
+        else:  # the contracted form, pinned to the reference's moe_combine_exact
+            assert n_bit_diff(xb.get(), orc.combine_rows_fma(x, z, own_row.reshape(T, k), w, e)) == 0
     zb = widen(pkg, z, pkg.BF16).reshape(R, Hd)
     want_b = orc.combine_rows(x, zb, own_row.reshape(T, k), w, e, E)
     xb, o = d.put_inout(x), d.out((T, Hd), pkg.BF16)
@@ -952,8 +964,9 @@ def test_bias_rope_with_cache_write_equals_the_two_launches(gpu, orc, T, nq, nkv
     assert np.array_equal(k1.get(as_f32=False), k2.get(as_f32=False))
     assert np.array_equal(q1.get(), q2.get())
     assert n_bit_diff(s1.get(), s2.get()) == 0
-    if mode == "exact":
-        rotated = orc.bias_rope_rows_table(qkv, bias, pos, ct, st, nq, nkv, 64)
+    if mode in ("exact", "exact_fma"):  # the second is the rounding of the reference's rope_kv_bf16_kernel
+        rotated = orc.bias_rope_rows_table(qkv, bias, pos, ct, st, nq, nkv, 64, fma=mode == "exact_fma")
+        assert n_bit_diff(o1.get(), rotated) == 0
         want = [a.copy() for a in fill]
         orc.kv_cache_write(rotated, nq, nkv, want[0], want[1], want[2], slots, slot)
         assert np.array_equal(k1.get(as_f32=False), want[0]) and np.array_equal(q1.get(), want[1])

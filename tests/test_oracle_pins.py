@@ -423,6 +423,53 @@ def test_ref_exact_kernels_pin_the_contracted_forms(orc, ref):
         assert_bit_equal(orc.combine_rows_fma(x, Z, row_of, w, e), ref.moe_combine_exact(x, Z, row_of, w, e), "combine")
 
 
+def _rope_kv_of_the_oracle(orc, rows, ct, st, p, nq, nkv, slots, slot, rotate_q=True):
+    """Rotation (contracted form) then cache write, as two oracle calls; the rows come back as
+    the reference's kernel leaves them: rotated queries, keys and values untouched."""
+    B, kv = rows.shape[0], nkv * 64
+    rotated = orc.bias_rope_rows_table(rows, None, np.full(B, p, np.int32), ct, st, nq, nkv, 64, fma=True)
+    kc, vq, vs = np.zeros(B * slots * kv, np.uint16), np.zeros(B * slots * kv, np.int8), np.zeros(B * slots * nkv, np.float32)
+    orc.kv_cache_write(rotated, nq, nkv, kc, vq, vs, slots, np.full(B, slot, np.int32))
+    after = rows.copy()
+    if rotate_q:
+        after[:, :nq * 64] = rotated[:, :nq * 64]
+    return after, kc, vq, vs
+
+
+def test_golden_rope_kv(orc, golden):
+    rows, p, slots, slot = gi.case_rope_kv()
+    ct, st = orc.yarn_table(64)
+    after, kc, vq, vs = _rope_kv_of_the_oracle(orc, rows, ct, st, p, 64, 8, slots, slot)
+    assert_bit_equal(after, golden["rope_kv_rows"], "rows")
+    assert np.array_equal(kc, golden["rope_kv_keys"]) and np.array_equal(vq, golden["rope_kv_codes"])
+    assert_bit_equal(vs, golden["rope_kv_scales"], "scales")
+
+
+def test_ref_rope_kv_kernel(orc, ref):
+    """The engine's rotation + KV-cache write in one launch, rope_kv_bf16_kernel
+    (kernels/fast_misc.hpp:48-108, instantiated as its launcher does at :110-127), run on host
+    threads: rotated queries, bf16 keys, int8 value codes, scales and where each lands equal the
+    oracle's contracted rotation followed by its cache write, bit for bit -- with the queries
+    rotated or left to the attention, for both models' head counts and the kernel's widest case."""
+    if not ref.has_rope_kv:
+        pytest.skip("reference library built without kernels/fast_misc.hpp's rope_kv_bf16_kernel")
+    r = np.random.default_rng(43)
+    ct, st = orc.yarn_table(300)
+    for nq, nkv, rotate_q, slots, slot in ((64, 8, True, 128, 77), (64, 8, False, 64, 63), (5, 2, True, 64, 0),
+                                           (100, 16, True, 128, 16)):
+        B, row = 4, (nq + 2 * nkv) * 64
+        rows = (r.standard_normal((B, row)) * 10.0 ** r.integers(-2, 3, (B, 1))).astype(np.float32)
+        rows[1, (nq + nkv) * 64:(nq + nkv) * 64 + 64] = 0.0
+        p = int(r.integers(0, 300))
+        kv = nkv * 64
+        kc, vq, vs = np.zeros(B * slots * kv, np.uint16), np.zeros(B * slots * kv, np.int8), np.zeros(B * slots * nkv, np.float32)
+        after = ref.rope_kv_bf16(rows, ct[p], st[p], nq, nkv, kc, vq, vs, slots, slot, rotate_q)
+        w_after, w_kc, w_vq, w_vs = _rope_kv_of_the_oracle(orc, rows, ct, st, p, nq, nkv, slots, slot, rotate_q)
+        assert_bit_equal(after, w_after, "rows")
+        assert np.array_equal(kc, w_kc) and np.array_equal(vq, w_vq), (nq, nkv)
+        assert_bit_equal(vs, w_vs, "scales")
+
+
 def test_ref_group_for_part_of_the_experts(orc, ref):
     """Grouping for experts e_begin .. e_begin + e_count - 1 against the reference's
     moe_count_ep_kernel + moe_place_ep_kernel (kernels/moe_ep.hpp:55-127; the pair moe_group_ep
