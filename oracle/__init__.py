@@ -394,6 +394,10 @@ class Reference(_Lib):
             L.ref_rope_kv_bf16.restype = None
             L.ref_rope_kv_bf16.argtypes = [C.c_int, _f32p, C.c_int, _f32p, _f32p, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
                                            C.c_void_p, C.c_int, C.c_int, C.c_int]
+        self.has_argmax_key = hasattr(L, "ref_has_argmax_key") and bool(L.ref_has_argmax_key())
+        if self.has_argmax_key:
+            L.ref_argmax_keys.restype = None
+            L.ref_argmax_keys.argtypes = [C.c_long, _f32p, _i32p, np.ctypeslib.ndpointer(np.uint64, flags="C")]
         self.has_group_ep = hasattr(L, "ref_has_group_ep") and bool(L.ref_has_group_ep())
         if self.has_group_ep:
             L.ref_moe_group_ep.restype = None
@@ -410,6 +414,14 @@ class Reference(_Lib):
         so = None if slot_of is None else np.ascontiguousarray(slot_of, np.int32)
         self.lib.ref_router_topk_wave(lg, E, k, w, e, B, _addr(dn), _addr(so))
         return w, e
+
+    def argmax_keys(self, x, col):
+        """argmax_key (kernels/fast_gemm.hpp:94-104) of each (value, column)."""
+        x = np.ascontiguousarray(x, np.float32).ravel()
+        col = np.ascontiguousarray(col, np.int32).ravel()
+        keys = np.empty(x.size, np.uint64)
+        self.lib.ref_argmax_keys(x.size, x, col, keys)
+        return keys
 
     def rope_kv_bf16(self, rows, cos_row, sin_row, n_q, n_kv, kc, vq, vs, slots, slot, rotate_q=True):
         """rope_kv_bf16_kernel (kernels/fast_misc.hpp:48-108) as its launcher instantiates it: rotates the rows

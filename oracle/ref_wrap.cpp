@@ -309,6 +309,10 @@ static inline float __fadd_rn(float a, float b) { return a + b; }
 #include REF_GROUP_EP_PART
 #endif
 static inline int min(int a, int b) { return a < b ? a : b; }
+#ifdef REF_ARGMAX_KEY_PART
+// argmax_key (kernels/fast_gemm.hpp:94-104): the 64-bit word the LM-head epilogue folds with atomicMax.
+#include REF_ARGMAX_KEY_PART
+#endif
 #if defined(REF_ROPE_KV_PART) && defined(REF_EXACT_PART) && defined(REF_CACHE_PART)
 // rope_pair (kernels/fast_common.hpp:25-28) and rope_kv_bf16_kernel (kernels/fast_misc.hpp:48-108):
 // the engine's rotation + KV-cache write in one launch.  It calls the index functions and the
@@ -409,6 +413,16 @@ REF_API void ref_moe_combine_exact(float *x, int B, const float *Z, const int *p
 }
 #else
 REF_API int ref_has_exact_kernels(void) { return 0; }
+#endif
+
+#ifdef REF_ARGMAX_KEY_PART
+REF_API int ref_has_argmax_key(void) { return 1; }
+REF_API void ref_argmax_keys(long n, const float *x, const int *col, unsigned long long *keys) {
+  for (long i = 0; i < n; i++)
+    keys[i] = ref_group::argmax_key(x[i], col[i]);
+}
+#else
+REF_API int ref_has_argmax_key(void) { return 0; }
 #endif
 
 #ifdef REF_HAS_ROPE_KV
@@ -521,4 +535,5 @@ REF_API int ref_has_group_ep(void) { return 0; }
 REF_API int ref_has_exact_kernels(void) { return 0; }
 REF_API int ref_has_router_wave(void) { return 0; }
 REF_API int ref_has_rope_kv(void) { return 0; }
+REF_API int ref_has_argmax_key(void) { return 0; }
 #endif

@@ -3,12 +3,14 @@ functions produced (always), (2) against the reference's functions themselves, b
 bit, on seeded inputs (where oracle/_ref/libgptoss_ref.so is present)."""
 from __future__ import annotations
 
+import os
+
 import numpy as np
 import pytest
 
 import golden_inputs as gi
 import oracle
-from conftest import assert_bit_equal
+from conftest import ROOT, assert_bit_equal
 
 
 # ---- (1) golden known answers -------------------------------------------------------
@@ -468,6 +470,35 @@ def test_ref_rope_kv_kernel(orc, ref):
         assert_bit_equal(after, w_after, "rows")
         assert np.array_equal(kc, w_kc) and np.array_equal(vq, w_vq), (nq, nkv)
         assert_bit_equal(vs, w_vs, "scales")
+
+
+def test_argmax_key_header_is_the_reference_key(ref, tmp_path):
+    """include/gptoss_argmax_key.cuh, compiled for the host (tests/cpp/argmax_key_host.cpp), against
+    the reference's argmax_key (kernels/fast_gemm.hpp:94-104): the same 64-bit word for every
+    (value, column) -- random bit patterns, both zeros, infinities, NaNs, denormals, columns up to
+    2^31 - 1 -- so a producer written against either folds into the same words; and the merged
+    word names its column."""
+    if not ref.has_argmax_key:
+        pytest.skip("reference library built without kernels/fast_gemm.hpp's argmax_key")
+    import ctypes as C
+    import subprocess
+    so = tmp_path / "argmax_key_host.so"
+    subprocess.run(["g++", "-O2", "-shared", "-fPIC", "-I", os.path.join(ROOT, "include"), "-x", "c++",
+                    os.path.join(ROOT, "tests", "cpp", "argmax_key_host.cpp"), "-o", str(so)], check=True)
+    host = C.CDLL(str(so))
+    r = np.random.default_rng(47)
+    x = r.integers(0, 2 ** 32, 400000, dtype=np.uint64).astype(np.uint32).view(np.float32).copy()
+    x[:12] = np.array([0.0, -0.0, np.inf, -np.inf, np.nan, -np.nan, 1e-45, -1e-45, 3.4e38, -3.4e38, 1.0, -1.0], np.float32)
+    col = r.integers(0, 2 ** 31, x.size).astype(np.int32)
+    col[:4] = 0, 1, 2 ** 31 - 1, 201087
+    got = np.empty(x.size, np.uint64)
+    host.host_argmax_keys(C.c_long(x.size), x.ctypes.data_as(C.c_void_p), col.ctypes.data_as(C.c_void_p),
+                          got.ctypes.data_as(C.c_void_p))
+    assert np.array_equal(got, ref.argmax_keys(x, col))
+    back = np.empty(x.size, np.int32)
+    host.host_argmax_columns(C.c_long(x.size), got.ctypes.data_as(C.c_void_p), back.ctypes.data_as(C.c_void_p))
+    number = ~np.isnan(x)
+    assert np.array_equal(back[number], col[number]) and (got[~number] == 0).all() and (back[~number] == 0).all()
 
 
 def test_ref_group_for_part_of_the_experts(orc, ref):
