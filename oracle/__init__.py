@@ -398,6 +398,15 @@ class Reference(_Lib):
         if self.has_argmax_key:
             L.ref_argmax_keys.restype = None
             L.ref_argmax_keys.argtypes = [C.c_long, _f32p, _i32p, np.ctypeslib.ndpointer(np.uint64, flags="C")]
+        self.has_fast_kernels = hasattr(L, "ref_has_fast_kernels") and bool(L.ref_has_fast_kernels())
+        if self.has_fast_kernels:
+            _u16p = np.ctypeslib.ndpointer(np.uint16, flags="C")
+            L.ref_rmsnorm_bf16.restype = None
+            L.ref_rmsnorm_bf16.argtypes = [C.c_int, _f32p, _f32p, _u16p, C.c_int]
+            L.ref_swiglu_bf16.restype = None
+            L.ref_swiglu_bf16.argtypes = [_f32p, _u16p, C.c_long, C.c_int, C.c_float]
+            L.ref_moe_combine_fast.restype = None
+            L.ref_moe_combine_fast.argtypes = [C.c_int, _f32p, _f32p, _i32p, _f32p, C.c_int, C.c_int]
         self.has_group_ep = hasattr(L, "ref_has_group_ep") and bool(L.ref_has_group_ep())
         if self.has_group_ep:
             L.ref_moe_group_ep.restype = None
@@ -414,6 +423,29 @@ class Reference(_Lib):
         so = None if slot_of is None else np.ascontiguousarray(slot_of, np.int32)
         self.lib.ref_router_topk_wave(lg, E, k, w, e, B, _addr(dn), _addr(so))
         return w, e
+
+    def rmsnorm_bf16(self, x, weight):
+        """rmsnorm_bf16_kernel (kernels/fast_misc.hpp:11-30): bf16 bits of the normalised rows."""
+        x = np.ascontiguousarray(x, np.float32)
+        out = np.zeros(x.shape, np.uint16)
+        self.lib.ref_rmsnorm_bf16(x.shape[0], x, np.ascontiguousarray(weight, np.float32), out, x.shape[1])
+        return out
+
+    def swiglu_bf16(self, y, limit=7.0):
+        """swiglu_bf16_kernel (kernels/fast_misc.hpp:130-141) with the C library's expf: bf16 bits."""
+        y = np.ascontiguousarray(y, np.float32)
+        R, I = y.shape[0], y.shape[1] // 2
+        out = np.zeros((R, I), np.uint16)
+        self.lib.ref_swiglu_bf16(y, out, R, I, limit)
+        return out
+
+    def moe_combine_fast(self, x, Z, pair_row, weights):
+        """moe_combine_kernel (kernels/fast_misc.hpp:154-166): fused multiply-adds in choice order."""
+        x = np.array(x, np.float32, copy=True)
+        self.lib.ref_moe_combine_fast(x.shape[0], x, np.ascontiguousarray(Z, np.float32),
+                                      np.ascontiguousarray(pair_row, np.int32), np.ascontiguousarray(weights, np.float32),
+                                      weights.shape[1], x.shape[1])
+        return x
 
     def argmax_keys(self, x, col):
         """argmax_key (kernels/fast_gemm.hpp:94-104) of each (value, column)."""

@@ -309,6 +309,15 @@ static inline float __fadd_rn(float a, float b) { return a + b; }
 #include REF_GROUP_EP_PART
 #endif
 static inline int min(int a, int b) { return a < b ? a : b; }
+#if defined(REF_FAST_PART) && defined(REF_CACHE_PART)
+// Three kernels of the engine's fast (bf16-activation) path: rmsnorm_bf16_kernel, swiglu_bf16_kernel,
+// moe_combine_kernel (kernels/fast_misc.hpp:11-30, 130-141, 154-166).  The device's approximate
+// __expf has no host twin; the C library's expf stands in (the two differ by a few units in the
+// last place of an fp32 value that is then rounded to bf16).
+static inline float __expf(float x) { return expf(x); }
+#include REF_FAST_PART
+#define REF_HAS_FAST 1
+#endif
 #ifdef REF_ARGMAX_KEY_PART
 // argmax_key (kernels/fast_gemm.hpp:94-104): the 64-bit word the LM-head epilogue folds with atomicMax.
 #include REF_ARGMAX_KEY_PART
@@ -413,6 +422,53 @@ REF_API void ref_moe_combine_exact(float *x, int B, const float *Z, const int *p
 }
 #else
 REF_API int ref_has_exact_kernels(void) { return 0; }
+#endif
+
+#ifdef REF_HAS_FAST
+REF_API int ref_has_fast_kernels(void) { return 1; }
+// One block of 256 threads per row; the halving tree has a block barrier per level.
+REF_API void ref_rmsnorm_bf16(int B, const float *x, const float *weight, uint16_t *out, int H) {
+  std::lock_guard<std::mutex> lock(ref_group::one_block_at_a_time);
+  ref_group::blockDim.x = 256;
+  for (int block = 0; block < B; block++) {
+    pthread_barrier_init(&ref_group::block_barrier, nullptr, 256);
+    std::vector<std::thread> pool;
+    for (int t = 0; t < 256; t++)
+      pool.emplace_back([=] {
+        ref_group::threadIdx.x = t;
+        ref_group::blockIdx.x = block;
+        ref_group::rmsnorm_bf16_kernel(x, weight, out, H);
+      });
+    for (auto &t : pool)
+      t.join();
+    pthread_barrier_destroy(&ref_group::block_barrier);
+  }
+}
+// No barrier in these two: a block's threads are a loop.
+REF_API void ref_swiglu_bf16(const float *Y, uint16_t *G, long R, int I, float limit) {
+  std::lock_guard<std::mutex> lock(ref_group::one_block_at_a_time);
+  ref_group::blockDim.x = 256;
+  const long blocks = (R * I + 255) / 256;
+  for (long block = 0; block < blocks; block++)
+    for (int t = 0; t < 256; t++) {
+      ref_group::blockIdx.x = (int)block;
+      ref_group::threadIdx.x = t;
+      ref_group::swiglu_bf16_kernel(Y, G, (size_t)R, I, limit);
+    }
+}
+REF_API void ref_moe_combine_fast(int B, float *x, const float *Z, const int *pair_row, const float *topk_w, int k,
+                                  int H) {
+  std::lock_guard<std::mutex> lock(ref_group::one_block_at_a_time);
+  ref_group::blockDim.x = 256;
+  for (int block = 0; block < B; block++)
+    for (int t = 0; t < 256; t++) {
+      ref_group::blockIdx.x = block;
+      ref_group::threadIdx.x = t;
+      ref_group::moe_combine_kernel(x, Z, pair_row, topk_w, k, H);
+    }
+}
+#else
+REF_API int ref_has_fast_kernels(void) { return 0; }
 #endif
 
 #ifdef REF_ARGMAX_KEY_PART
@@ -536,4 +592,5 @@ REF_API int ref_has_exact_kernels(void) { return 0; }
 REF_API int ref_has_router_wave(void) { return 0; }
 REF_API int ref_has_rope_kv(void) { return 0; }
 REF_API int ref_has_argmax_key(void) { return 0; }
+REF_API int ref_has_fast_kernels(void) { return 0; }
 #endif

@@ -25,6 +25,8 @@ stores the expected outputs:
     moe_place_ep_kernel (kernels/moe_ep.hpp) the same way, 64 host threads to a wavefront;
   * rotated rows, bf16 keys, int8 value codes and scales of the engine's rotation + cache write: the
     REFERENCE's rope_kv_bf16_kernel (kernels/fast_misc.hpp), run on host threads;
+  * the bf16 mode's norm, SwiGLU and combine as the REFERENCE's fast-path kernels compute them
+    (rmsnorm_bf16_kernel, swiglu_bf16_kernel, moe_combine_kernel of kernels/fast_misc.hpp), run on the host;
   * the router's output for finished rows and with an expert renumbering table: the REFERENCE's
     router_topk_wave_kernel (kernels/moe.hpp), run on host threads;
   * the rotation and the combine with the GPU exact path's rounding (fused multiply-adds): the
@@ -117,6 +119,15 @@ def main():
     kc, vq, vs = np.zeros(n_k, np.uint16), np.zeros(n_k, np.int8), np.zeros(n_k // 64, np.float32)
     out["rope_kv_rows"] = ref.rope_kv_bf16(rows, *ref.yarn_cos_sin(p_), 64, 8, kc, vq, vs, slots, slot)
     out["rope_kv_keys"], out["rope_kv_codes"], out["rope_kv_scales"] = kc, vq, vs
+
+    # the fast (bf16-activation) path's own answers: the REFERENCE's rmsnorm_bf16_kernel (behind the float
+    # add of add_inplace_kernel), swiglu_bf16_kernel and moe_combine_kernel (kernels/fast_misc.hpp), bodies
+    # run on the host; the device's approximate __expf is the C library's expf here
+    x, delta, gain = gi.case_rmsnorm()
+    out["fast_norm_bits"] = ref.rmsnorm_bf16((x + delta).astype(np.float32), gain)
+    out["fast_swiglu_bits"] = ref.swiglu_bf16(gi.case_swiglu())
+    xc, Z, row_of, wt, e = gi.case_combine()
+    out["fast_combine_x"] = ref.moe_combine_fast(xc, Z, row_of, wt)
 
     for j, (e, E) in enumerate(gi.case_group()):
         off, rp, pr = ref.moe_group(e, E)

@@ -38,6 +38,15 @@ def rel_err_unfloored(got, want) -> float:
     return float(np.max(np.abs(got[nz] - want[nz]) / np.abs(want[nz]))) if nz.any() else 0.0
 
 
+def bf16_ulps_apart(a_bits, b_bits) -> int:
+    """Largest distance, in representable bf16 values, between two arrays of bf16 bit patterns."""
+    def ordered(u):
+        u = np.asarray(u, np.uint16).astype(np.int32)
+        return np.where(u & 0x8000, -(u & 0x7fff), u & 0x7fff)
+    a, b = ordered(a_bits), ordered(b_bits)
+    return int(np.max(np.abs(a - b))) if a.size else 0
+
+
 def n_bit_diff(a, b) -> int:
     a, b = np.ascontiguousarray(a), np.ascontiguousarray(b)
     v = {4: np.uint32, 2: np.uint16}[a.dtype.itemsize]

@@ -13,7 +13,7 @@ import numpy as np
 import pytest
 
 import golden_inputs as gi
-from gpu_util import Dev, TOL_BF16, TOL_F32, n_bit_diff, rel_err, widen
+from gpu_util import Dev, TOL_BF16, TOL_F32, bf16_ulps_apart, n_bit_diff, rel_err, widen
 
 pytestmark = pytest.mark.gpu
 
@@ -554,6 +554,20 @@ def test_golden_vectors_through_the_gpu(gpu, golden):
     xb = d.put_inout(xc)
     pkg.moe_combine(6, xb, d.put(Z), pkg.F32, d.put(row_of), d.put(w), d.put(e), 4, gi.H, flags=pkg.EXACT | pkg.FMA)
     assert n_bit_diff(xb.get(), golden["combine_fma_x"]) == 0   # the reference's moe_combine_exact
+
+    # bf16 mode against the reference's own fast-path kernels (rmsnorm_bf16_kernel behind the float add,
+    # swiglu_bf16_kernel, moe_combine_kernel): bf16 outputs at most one representable value apart (summation
+    # order and the approximate exp / reciprocal / root differ by design), the fp32 combine within 1e-6
+    x, delta, gain = gi.case_rmsnorm()
+    xb, o16 = d.put_inout(x), d.out(x.shape, pkg.BF16)
+    pkg.add_rmsnorm(4, xb, d.put(delta), pkg.F32, d.put(gain), o16, pkg.BF16, gi.H)
+    assert bf16_ulps_apart(o16.get(as_f32=False), golden["fast_norm_bits"]) <= 1
+    g16 = d.out((4, gi.H), pkg.BF16)
+    pkg.swiglu(d.put(y), pkg.F32, g16, pkg.BF16, 4, gi.H, 7.0)
+    assert bf16_ulps_apart(g16.get(as_f32=False), golden["fast_swiglu_bits"]) <= 1
+    xb = d.put_inout(xc)
+    pkg.moe_combine(6, xb, d.put(Z), pkg.F32, d.put(row_of), d.put(w), d.put(e), 4, gi.H)
+    assert rel_err(xb.get(), golden["fast_combine_x"]) <= 1e-6
 
     # the engine's rotation + cache write in one launch (in place, one position, one slot): the bits of the
     # reference's rope_kv_bf16_kernel -- queries in the rows, keys, codes and scales in the caches

@@ -472,6 +472,30 @@ def test_ref_rope_kv_kernel(orc, ref):
         assert_bit_equal(vs, w_vs, "scales")
 
 
+def test_ref_fast_kernels_sit_inside_the_bf16_tolerance(orc, ref, golden):
+    """The reference's fast-path kernels (rmsnorm_bf16_kernel, swiglu_bf16_kernel,
+    moe_combine_kernel, kernels/fast_misc.hpp), run on the host, against the fp32 oracle: they
+    differ by the bf16 rounding of their outputs and their own summation order, inside the 2e-2
+    that the bf16 mode is held to.  Their outputs on the committed inputs are golden vectors for
+    the GPU's bf16 mode."""
+    if not ref.has_fast_kernels:
+        pytest.skip("reference library built without kernels/fast_misc.hpp's fast-path kernels")
+    widen = lambda bits: (np.asarray(bits, np.uint32) << 16).view(np.float32)
+    rel = lambda got, want: float(np.max(np.abs(got - want) / np.maximum(np.abs(want), 0.01 * np.sqrt(np.mean(want * want)))))
+    x, delta, gain = gi.case_rmsnorm()
+    bits = ref.rmsnorm_bf16((x + delta).astype(np.float32), gain)
+    assert np.array_equal(bits, golden["fast_norm_bits"])
+    assert rel(widen(bits), orc.add_rmsnorm_rows(x, delta, gain)[1]) <= 2e-2
+    y = gi.case_swiglu()
+    bits = ref.swiglu_bf16(y)
+    assert np.array_equal(bits, golden["fast_swiglu_bits"])
+    assert rel(widen(bits), orc.swiglu_rows(y)) <= 2e-2
+    xc, Z, row_of, wt, e = gi.case_combine()
+    got = ref.moe_combine_fast(xc, Z, row_of, wt)
+    assert_bit_equal(got, golden["fast_combine_x"], "fast combine")
+    assert rel(got, orc.combine_rows(xc, Z, row_of, wt, e, gi.E20)) <= 1e-5
+
+
 def test_argmax_key_header_is_the_reference_key(ref, tmp_path):
     """include/gptoss_argmax_key.cuh, compiled for the host (tests/cpp/argmax_key_host.cpp), against
     the reference's argmax_key (kernels/fast_gemm.hpp:94-104): the same 64-bit word for every
