@@ -13,8 +13,16 @@
  * compute_cos_sin, apply_rotary_emb, sample_argmax) and, for the loops that
  * only exist inline in forward() (bias add, SwiGLU, expert combine, residual),
  * through a whole tiny-model forward() run of the reference against
- * orc_forward_seq() here.  The golden vectors under tests/golden/ were produced
- * by the reference's functions and are checked against this file on every run.
+ * orc_forward_seq() here.  The steps on either side of the path, which the CPU
+ * program does not have, are held to the reference's GPU kernels, whose bodies
+ * the reference library compiles as host code and runs on host threads: pair
+ * grouping and the row gather (moe_group_kernel, moe_gather_kernel,
+ * moe_count_ep_kernel + moe_place_ep_kernel), the KV-cache write (the index
+ * functions, f32_to_bf16, quantize_v of the attention test, and
+ * rope_kv_bf16_kernel as a whole), the contracted rotation and combine
+ * (rope_exact, moe_combine_exact), and the wave bookkeeping (the host statements
+ * of gpu_run_wave).  The golden vectors under tests/golden/ were produced by the
+ * reference's code and are checked against this file on every run.
  *
  * Build: gcc -O3 -fopenmp -ffp-contract=off -fPIC -shared (no -ffast-math, no
  * -march=native: the reference baseline build is "-O3 -fopenmp", which on
