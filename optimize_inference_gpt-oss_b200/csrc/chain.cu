@@ -332,7 +332,7 @@ int gptoss_chain_config_gpt_oss(int which, gptoss_dtype_t act_dtype, int max_pos
   // Programmatic launch between the chain's kernels is on: every kernel waits for its predecessor
   // before it reads anything, so results do not change, and a step of 123 launches measured
   // 2 % shorter at 4096 tokens and 11 % shorter at 512.
-  cfg->flags = (act_dtype == GPTOSS_F32 ? GPTOSS_EXACT : 0u) | GPTOSS_PDL;
+  cfg->flags = (act_dtype == GPTOSS_F32 ? (unsigned)GPTOSS_EXACT : 0u) | (unsigned)GPTOSS_PDL;
   return GPTOSS_OK;
 }
 
