@@ -407,6 +407,16 @@ class Reference(_Lib):
             L.ref_swiglu_bf16.argtypes = [_f32p, _u16p, C.c_long, C.c_int, C.c_float]
             L.ref_moe_combine_fast.restype = None
             L.ref_moe_combine_fast.argtypes = [C.c_int, _f32p, _f32p, _i32p, _f32p, C.c_int, C.c_int]
+        self.has_exact_rows = hasattr(L, "ref_has_exact_rows") and bool(L.ref_has_exact_rows())
+        if self.has_exact_rows:
+            _u16 = np.ctypeslib.ndpointer(np.uint16, flags="C")
+            for name, args in (("ref_embed", [C.c_int, _u16, _i32p, _f32p, C.c_int]),
+                               ("ref_add_inplace", [_f32p, _f32p, C.c_long]),
+                               ("ref_router_topk_exact", [_f32p, C.c_int, C.c_int, _f32p, _i32p, C.c_int]),
+                               ("ref_swiglu_exact", [_f32p, _f32p, C.c_long, C.c_int, C.c_float]),
+                               ("ref_argmax_kernel", [C.c_int, _f32p, C.c_int, _i32p])):
+                getattr(L, name).restype = None
+                getattr(L, name).argtypes = args
         self.has_group_ep = hasattr(L, "ref_has_group_ep") and bool(L.ref_has_group_ep())
         if self.has_group_ep:
             L.ref_moe_group_ep.restype = None
@@ -423,6 +433,36 @@ class Reference(_Lib):
         so = None if slot_of is None else np.ascontiguousarray(slot_of, np.int32)
         self.lib.ref_router_topk_wave(lg, E, k, w, e, B, _addr(dn), _addr(so))
         return w, e
+
+    def exact_rows(self, op, *a):
+        """The GPU engine's bit-exact kernels, bodies run on the host: 'embed' (bf16 table bits, ids),
+        'add' (x, y), 'router' (logits, k), 'swiglu' (Y, limit), 'argmax' (logits)."""
+        L = self.lib
+        if op == "embed":
+            table, ids = np.ascontiguousarray(a[0], np.uint16), np.ascontiguousarray(a[1], np.int32)
+            x = np.zeros((ids.size, table.shape[1]), np.float32)
+            L.ref_embed(ids.size, table, ids, x, table.shape[1])
+            return x
+        if op == "add":
+            x = np.array(a[0], np.float32, copy=True)
+            L.ref_add_inplace(x, np.ascontiguousarray(a[1], np.float32), x.size)
+            return x
+        if op == "router":
+            lg, k = np.ascontiguousarray(a[0], np.float32), a[1]
+            w, e = np.zeros((lg.shape[0], k), np.float32), np.zeros((lg.shape[0], k), np.int32)
+            L.ref_router_topk_exact(lg, lg.shape[1], k, w, e, lg.shape[0])
+            return w, e
+        if op == "swiglu":
+            y = np.ascontiguousarray(a[0], np.float32)
+            g = np.zeros((y.shape[0], y.shape[1] // 2), np.float32)
+            L.ref_swiglu_exact(y, g, y.shape[0], y.shape[1] // 2, a[1])
+            return g
+        if op == "argmax":
+            lg = np.ascontiguousarray(a[0], np.float32)
+            out = np.full(lg.shape[0], -7, np.int32)
+            L.ref_argmax_kernel(lg.shape[0], lg, lg.shape[1], out)
+            return out
+        raise ValueError(op)
 
     def rmsnorm_bf16(self, x, weight):
         """rmsnorm_bf16_kernel (kernels/fast_misc.hpp:11-30): bf16 bits of the normalised rows."""

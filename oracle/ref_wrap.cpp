@@ -351,6 +351,15 @@ static inline double __ddiv_rn(double a, double b) { return a / b; }
 static inline double __fma_rn(double a, double b, double c) { return fma(a, b, c); }
 #include REF_ROUTER_PART
 #endif
+#if defined(REF_EXACT_ROWS_PART) && defined(REF_ROUTER_PART) && defined(REF_EXACT_PART)
+// The rest of the GPU engine's bit-exact path: embed_kernel, add_inplace_kernel, argmax_kernel
+// (kernels/misc.hpp:10-23, 86-93, 95-129), router_topk_exact and swiglu_exact
+// (kernels/moe.hpp:15-52, 186-205; expf_cpu is already in from the router's cut).
+static inline float __uint_as_float(uint32_t u) { return float_of((long long)u); }
+static inline float __fdiv_rn(float a, float b) { return a / b; }
+#include REF_EXACT_ROWS_PART
+#define REF_HAS_EXACT_ROWS 1
+#endif
 #undef __syncthreads
 #undef __shared__
 #undef __global__
@@ -422,6 +431,53 @@ REF_API void ref_moe_combine_exact(float *x, int B, const float *Z, const int *p
 }
 #else
 REF_API int ref_has_exact_kernels(void) { return 0; }
+#endif
+
+#ifdef REF_HAS_EXACT_ROWS
+REF_API int ref_has_exact_rows(void) { return 1; }
+// Runs `kernel` for every (block, thread) of a launch whose blocks have no barrier.
+template <class K> static void run_flat(long blocks, int threads, K kernel) {
+  std::lock_guard<std::mutex> lock(ref_group::one_block_at_a_time);
+  ref_group::blockDim.x = threads;
+  for (long b = 0; b < blocks; b++)
+    for (int t = 0; t < threads; t++) {
+      ref_group::blockIdx.x = (int)b;
+      ref_group::threadIdx.x = t;
+      kernel();
+    }
+}
+REF_API void ref_embed(int B, const uint16_t *emb, const int *tokens, float *x, int H) {
+  run_flat(B, 256, [=] { ref_group::embed_kernel(emb, tokens, x, H); });
+}
+REF_API void ref_add_inplace(float *x, const float *y, long n) {
+  run_flat((n + 255) / 256, 256, [=] { ref_group::add_inplace_kernel(x, y, (size_t)n); });
+}
+REF_API void ref_router_topk_exact(const float *logits, int E, int k, float *topk_w, int *topk_e, int B) {
+  run_flat((B + 63) / 64, 64, [=] { ref_group::router_topk_exact(logits, E, k, topk_w, topk_e, B); });
+}
+REF_API void ref_swiglu_exact(const float *Y, float *G, long R, int I, float limit) {
+  run_flat((R * I + 255) / 256, 256, [=] { ref_group::swiglu_exact(Y, G, (size_t)R, I, limit); });
+}
+// argmax_kernel merges through shared arrays with a block barrier per level: 256 host threads per row.
+REF_API void ref_argmax_kernel(int B, const float *logits, int V, int *out) {
+  std::lock_guard<std::mutex> lock(ref_group::one_block_at_a_time);
+  ref_group::blockDim.x = 256;
+  for (int block = 0; block < B; block++) {
+    pthread_barrier_init(&ref_group::block_barrier, nullptr, 256);
+    std::vector<std::thread> pool;
+    for (int t = 0; t < 256; t++)
+      pool.emplace_back([=] {
+        ref_group::threadIdx.x = t;
+        ref_group::blockIdx.x = block;
+        ref_group::argmax_kernel(logits, V, out);
+      });
+    for (auto &t : pool)
+      t.join();
+    pthread_barrier_destroy(&ref_group::block_barrier);
+  }
+}
+#else
+REF_API int ref_has_exact_rows(void) { return 0; }
 #endif
 
 #ifdef REF_HAS_FAST
@@ -593,4 +649,5 @@ REF_API int ref_has_router_wave(void) { return 0; }
 REF_API int ref_has_rope_kv(void) { return 0; }
 REF_API int ref_has_argmax_key(void) { return 0; }
 REF_API int ref_has_fast_kernels(void) { return 0; }
+REF_API int ref_has_exact_rows(void) { return 0; }
 #endif

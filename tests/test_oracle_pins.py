@@ -472,6 +472,41 @@ def test_ref_rope_kv_kernel(orc, ref):
         assert_bit_equal(vs, w_vs, "scales")
 
 
+def test_ref_exact_gpu_kernels_agree_with_the_oracle(orc, ref):
+    """The rest of the GPU engine's bit-exact path -- embed_kernel, add_inplace_kernel, argmax_kernel
+    (kernels/misc.hpp), router_topk_exact and swiglu_exact (kernels/moe.hpp) -- bodies run on the
+    host, against the oracle (which is run.cpp's arithmetic): bit for bit.  One corner differs by
+    the reference's own choice and is held as such: a NaN in a row's first logit makes
+    sample_argmax answer 0, while argmax_kernel skips it like any other NaN."""
+    if not ref.has_exact_rows:
+        pytest.skip("reference library built without the exact kernels of kernels/misc.hpp and kernels/moe.hpp")
+    r = np.random.default_rng(53)
+    table = r.integers(0, 2 ** 16, (300, 96), dtype=np.uint16)
+    ids = r.integers(0, 300, 41).astype(np.int32)
+    want = (table[ids].astype(np.uint32) << 16).view(np.float32)
+    assert_bit_equal(ref.exact_rows("embed", table, ids), want, "embedding rows")
+    x, y = (r.standard_normal(1000) * 10.0 ** r.integers(-5, 6, 1000)).astype(np.float32), r.standard_normal(1000).astype(np.float32)
+    assert_bit_equal(ref.exact_rows("add", x, y), (x + y).astype(np.float32), "residual add")
+    for E, k in ((32, 4), (128, 4), (200, 2), (16, 8)):
+        lg = r.standard_normal((37, E)).astype(np.float32)
+        lg[::3, E - 1] = lg[::3, 2]
+        lg[::5] = np.trunc(lg[::5] * 2)
+        w, e = ref.exact_rows("router", lg, k)
+        w2, e2 = orc.router_rows(lg, k)
+        assert np.array_equal(e, e2), (E, k)
+        assert_bit_equal(w, w2, "router weights")
+    yy = (r.standard_normal((9, 2 * 333)) * np.float32(4)).astype(np.float32)
+    yy[0, :8] = 100.0, -100.0, 7.0, -7.0, -60.0, 3.0, 0.0, -0.0
+    assert_bit_equal(ref.exact_rows("swiglu", yy, 7.0), orc.swiglu_rows(yy), "SwiGLU")
+    lg = np.trunc(r.standard_normal((6, 5001)) * 3).astype(np.float32)   # many equal maxima: the first one wins
+    lg[2, :] = -np.inf
+    lg[3, 17] = np.nan
+    lg[4, 4000] = lg[4].max() + 1
+    assert np.array_equal(ref.exact_rows("argmax", lg), orc.argmax_rows(lg))
+    lg[5, 0] = np.nan
+    assert orc.argmax_rows(lg)[5] == 0 and ref.exact_rows("argmax", lg)[5] == int(np.nanargmax(lg[5]))
+
+
 def test_ref_fast_kernels_sit_inside_the_bf16_tolerance(orc, ref, golden):
     """The reference's fast-path kernels (rmsnorm_bf16_kernel, swiglu_bf16_kernel,
     moe_combine_kernel, kernels/fast_misc.hpp), run on the host, against the fp32 oracle: they
