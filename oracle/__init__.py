@@ -417,6 +417,13 @@ class Reference(_Lib):
                                ("ref_argmax_kernel", [C.c_int, _f32p, C.c_int, _i32p])):
                 getattr(L, name).restype = None
                 getattr(L, name).argtypes = args
+        self.has_fused_kernels = hasattr(L, "ref_has_fused_kernels") and bool(L.ref_has_fused_kernels())
+        if self.has_fused_kernels:
+            _u16o = np.ctypeslib.ndpointer(np.uint16, flags="C")
+            L.ref_add_rmsnorm_bf16.restype = None
+            L.ref_add_rmsnorm_bf16.argtypes = [C.c_int, _f32p, _f32p, _f32p, _u16o, C.c_int]
+            L.ref_moe_combine_rmsnorm.restype = None
+            L.ref_moe_combine_rmsnorm.argtypes = [C.c_int, _f32p, _f32p, _i32p, _f32p, _i32p, C.c_int, C.c_int, _f32p, _u16o]
         self.has_group_ep = hasattr(L, "ref_has_group_ep") and bool(L.ref_has_group_ep())
         if self.has_group_ep:
             L.ref_moe_group_ep.restype = None
@@ -463,6 +470,26 @@ class Reference(_Lib):
             L.ref_argmax_kernel(lg.shape[0], lg, lg.shape[1], out)
             return out
         raise ValueError(op)
+
+    def add_rmsnorm_bf16(self, x, y, weight):
+        """add_rmsnorm_bf16_kernel (kernels/fast_misc.hpp:237-256) as its launcher instantiates it:
+        (x + y, bf16 bits of the normalised rows)."""
+        x = np.array(x, np.float32, copy=True)
+        out = np.zeros(x.shape, np.uint16)
+        self.lib.ref_add_rmsnorm_bf16(x.shape[0], x, np.ascontiguousarray(y, np.float32),
+                                      np.ascontiguousarray(weight, np.float32), out, x.shape[1])
+        return x, out
+
+    def moe_combine_rmsnorm(self, x, Z, own_row, weights, experts, norm_w):
+        """moe_combine_rmsnorm_kernel (kernels/moe_ep.hpp:479-515) as its launcher instantiates it:
+        (updated x, bf16 bits of the next norm's output)."""
+        x = np.array(x, np.float32, copy=True)
+        out = np.zeros(x.shape, np.uint16)
+        self.lib.ref_moe_combine_rmsnorm(x.shape[0], x, np.ascontiguousarray(Z, np.float32),
+                                         np.ascontiguousarray(own_row, np.int32), np.ascontiguousarray(weights, np.float32),
+                                         np.ascontiguousarray(experts, np.int32), weights.shape[1], x.shape[1],
+                                         np.ascontiguousarray(norm_w, np.float32), out)
+        return x, out
 
     def rmsnorm_bf16(self, x, weight):
         """rmsnorm_bf16_kernel (kernels/fast_misc.hpp:11-30): bf16 bits of the normalised rows."""

@@ -309,6 +309,15 @@ static inline float __fadd_rn(float a, float b) { return a + b; }
 #include REF_GROUP_EP_PART
 #endif
 static inline int min(int a, int b) { return a < b ? a : b; }
+#if defined(REF_FUSED_PART) && defined(REF_CACHE_PART) && defined(REF_EXACT_PART)
+// add_rmsnorm_bf16_kernel (kernels/fast_misc.hpp:237-256, with block_sum256, row_has, load_row256,
+// rms_inv_row and rmsnorm_store_bf16 before it) and moe_combine_rmsnorm_kernel
+// (kernels/moe_ep.hpp:479-515): the fast path's fused row kernels.  Their row sum meets at a block
+// barrier and finishes inside each 64-wide wave with shuffles.
+static inline float __shfl_down(float v, int offset) { return float_of(wave_read(bits_of(v), threadIdx.x % 64 + offset)); }
+#include REF_FUSED_PART
+#define REF_HAS_FUSED 1
+#endif
 #if defined(REF_FAST_PART) && defined(REF_CACHE_PART)
 // Three kernels of the engine's fast (bf16-activation) path: rmsnorm_bf16_kernel, swiglu_bf16_kernel,
 // moe_combine_kernel (kernels/fast_misc.hpp:11-30, 130-141, 154-166).  The device's approximate
@@ -478,6 +487,50 @@ REF_API void ref_argmax_kernel(int B, const float *logits, int V, int *out) {
 }
 #else
 REF_API int ref_has_exact_rows(void) { return 0; }
+#endif
+
+#ifdef REF_HAS_FUSED
+REF_API int ref_has_fused_kernels(void) { return 1; }
+// A block of 256 host threads with the block barrier and four wave barriers set up.
+template <class K> static void run_blocks_256(int blocks, K kernel) {
+  std::lock_guard<std::mutex> lock(ref_group::one_block_at_a_time);
+  ref_group::blockDim.x = 256;
+  for (int block = 0; block < blocks; block++) {
+    pthread_barrier_init(&ref_group::block_barrier, nullptr, 256);
+    for (int w = 0; w < 4; w++)
+      pthread_barrier_init(&ref_group::wave_barrier[w], nullptr, 64);
+    std::vector<std::thread> pool;
+    for (int t = 0; t < 256; t++)
+      pool.emplace_back([=] {
+        ref_group::threadIdx.x = t;
+        ref_group::blockIdx.x = block;
+        kernel();
+      });
+    for (auto &t : pool)
+      t.join();
+    for (int w = 0; w < 4; w++)
+      pthread_barrier_destroy(&ref_group::wave_barrier[w]);
+    pthread_barrier_destroy(&ref_group::block_barrier);
+  }
+}
+// Instantiated as the launchers do (kernels/fast_misc.hpp:259-267, kernels/moe_ep.hpp:563-573).
+REF_API void ref_add_rmsnorm_bf16(int B, float *x, const float *y, const float *weight, uint16_t *out, int H) {
+  if ((H + 255) / 256 == 12)
+    run_blocks_256(B, [=] { ref_group::add_rmsnorm_bf16_kernel<12>(x, y, weight, out, H, nullptr); });
+  else
+    run_blocks_256(B, [=] { ref_group::add_rmsnorm_bf16_kernel<FUSED_ROW_MAX>(x, y, weight, out, H, nullptr); });
+}
+REF_API void ref_moe_combine_rmsnorm(int B, float *x, const float *Z, const int *own_row, const float *topk_w,
+                                     const int *topk_e, int k, int H, const float *norm_w, uint16_t *out) {
+  if (k <= 4 && (H + 255) / 256 == 12)
+    run_blocks_256(B, [=] { ref_group::moe_combine_rmsnorm_kernel<4, 12>(x, Z, own_row, topk_w, topk_e, k, H, norm_w, out); });
+  else
+    run_blocks_256(B, [=] {
+      ref_group::moe_combine_rmsnorm_kernel<MOE_MAX_TOPK, FUSED_ROW_MAX>(x, Z, own_row, topk_w, topk_e, k, H, norm_w, out);
+    });
+}
+#else
+REF_API int ref_has_fused_kernels(void) { return 0; }
 #endif
 
 #ifdef REF_HAS_FAST
@@ -650,4 +703,5 @@ REF_API int ref_has_rope_kv(void) { return 0; }
 REF_API int ref_has_argmax_key(void) { return 0; }
 REF_API int ref_has_fast_kernels(void) { return 0; }
 REF_API int ref_has_exact_rows(void) { return 0; }
+REF_API int ref_has_fused_kernels(void) { return 0; }
 #endif

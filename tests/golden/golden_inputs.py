@@ -235,3 +235,12 @@ def case_rope_kv():
     rows = uniform(81, (3, QKV), 2.5)
     rows[1, (64 + 8) * 64:(64 + 8) * 64 + 64] = 0.0   # a value head of zeros
     return rows, 37, 64, 21   # rows, position, slots, slot
+
+
+def case_combine_norm():
+    """The combine case with token 2 finished (expert -1 for every choice) and the gain of the norm case:
+    inputs of the fused combine + next norm."""
+    x, Z, row_of, w, e = case_combine()
+    e = e.copy()
+    e[2] = -1
+    return x, Z, row_of, w, e, case_rmsnorm()[2]

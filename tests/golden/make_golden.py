@@ -129,6 +129,9 @@ def main():
     xc, Z, row_of, wt, e = gi.case_combine()
     out["fast_combine_x"] = ref.moe_combine_fast(xc, Z, row_of, wt)
 
+    # the fast path's fused combine + next norm: the REFERENCE's moe_combine_rmsnorm_kernel (kernels/moe_ep.hpp)
+    out["fast_combine_norm_x"], out["fast_combine_norm_bits"] = ref.moe_combine_rmsnorm(*gi.case_combine_norm())
+
     for j, (e, E) in enumerate(gi.case_group()):
         off, rp, pr = ref.moe_group(e, E)
         out[f"group{j}_offsets"], out[f"group{j}_row_pair"], out[f"group{j}_pair_row"] = off, rp, pr

@@ -569,6 +569,15 @@ def test_golden_vectors_through_the_gpu(gpu, golden):
     pkg.moe_combine(6, xb, d.put(Z), pkg.F32, d.put(row_of), d.put(w), d.put(e), 4, gi.H)
     assert rel_err(xb.get(), golden["fast_combine_x"]) <= 1e-6
 
+    # ... and its fused combine + next norm (moe_combine_rmsnorm_kernel), one token finished
+    xc2, Z2, row_of2, w2, e2, gain2 = gi.case_combine_norm()
+    xb, o16 = d.put_inout(xc2), d.out(xc2.shape, pkg.BF16)
+    pkg.moe_combine(6, xb, d.put(Z2), pkg.F32, d.put(row_of2), d.put(w2), d.put(e2), 4, gi.H, norm_w=d.put(gain2),
+                    out=o16, out_dtype=pkg.BF16)
+    assert rel_err(xb.get(), golden["fast_combine_norm_x"]) <= 1e-6
+    assert n_bit_diff(xb.get()[2], xc2[2]) == 0
+    assert bf16_ulps_apart(o16.get(as_f32=False), golden["fast_combine_norm_bits"]) <= 1
+
     # the engine's rotation + cache write in one launch (in place, one position, one slot): the bits of the
     # reference's rope_kv_bf16_kernel -- queries in the rows, keys, codes and scales in the caches
     rows, p_, slots, slot = gi.case_rope_kv()

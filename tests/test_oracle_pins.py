@@ -531,6 +531,32 @@ def test_ref_fast_kernels_sit_inside_the_bf16_tolerance(orc, ref, golden):
     assert rel(got, orc.combine_rows(xc, Z, row_of, wt, e, gi.E20)) <= 1e-5
 
 
+def test_ref_fused_fast_kernels_give_their_unfused_pairs_bits(ref, golden):
+    """add_rmsnorm_bf16_kernel (kernels/fast_misc.hpp:237-256) and moe_combine_rmsnorm_kernel
+    (kernels/moe_ep.hpp:479-515), run on host threads (a block barrier, then shuffles inside each
+    64-wide wave, for the row sum): the reference says each equals its unfused pair bit for bit,
+    and run here they do -- which also checks the emulated shuffles.  A finished token keeps its
+    x and still gets its norm."""
+    if not (ref.has_fused_kernels and ref.has_fast_kernels):
+        pytest.skip("reference library built without the fast path's fused kernels")
+    x, delta, gain = gi.case_rmsnorm()
+    xa, bits = ref.add_rmsnorm_bf16(x, delta, gain)
+    assert_bit_equal(xa, (x + delta).astype(np.float32), "x + delta")
+    assert np.array_equal(bits, ref.rmsnorm_bf16(xa, gain)) and np.array_equal(bits, golden["fast_norm_bits"])
+    xc, Z, row_of, wt, e, gain = gi.case_combine_norm()
+    x2, bits2 = ref.moe_combine_rmsnorm(xc, Z, row_of, wt, e, gain)
+    unfused = ref.moe_combine_fast(xc, Z, row_of, wt)
+    unfused[2] = xc[2]
+    assert_bit_equal(x2, unfused, "combine")
+    assert np.array_equal(bits2, ref.rmsnorm_bf16(x2, gain))
+    assert_bit_equal(x2, golden["fast_combine_norm_x"], "golden x")
+    assert np.array_equal(bits2, golden["fast_combine_norm_bits"])
+    r = np.random.default_rng(59)   # an odd width takes the launchers' general instantiations
+    xo, yo, go = (r.standard_normal((3, 1000)).astype(np.float32) for _ in range(3))
+    xa, bits = ref.add_rmsnorm_bf16(xo, yo, go[0])
+    assert np.array_equal(bits, ref.rmsnorm_bf16(xa, go[0]))
+
+
 def test_argmax_key_header_is_the_reference_key(ref, tmp_path):
     """include/gptoss_argmax_key.cuh, compiled for the host (tests/cpp/argmax_key_host.cpp), against
     the reference's argmax_key (kernels/fast_gemm.hpp:94-104): the same 64-bit word for every
